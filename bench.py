@@ -1,0 +1,366 @@
+#!/usr/bin/env python3
+"""Benchmark of the vindex FFN walk on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload NAME] [--batch B]
+
+A step is one token batch through every layer of the workload (h <- h + walk_l(rmsnorm(h))).
+Default workload: the Llama-3-70B-shaped Q4_K walk (hidden 8192, 28672 features, 80 layers,
+top-K 4096, batch 1), which fits one GPU and is the configuration the multi-GPU metric is
+quoted on.  Weights are seeded N(0, 0.02) generated and Q4_K-quantised on the device by the
+library's own encoder; inputs are seeded N(0, 1) residuals.
+
+Prints ONE JSON line (rank 0).  `value` is device-resident throughput (CUDA graph replay,
+CUDA events on the launching stream); `e2e` goes through the host-pointer C-ABI call per
+layer with host<->device copies of the activations inside the timed region; `roofline`
+is the gate-scan kernel against the measured HBM copy bandwidth; `cpu_baseline` is the CPU
+oracle (a restatement of the reference CPU backend) timed on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: hidden, features, top_k, layers
+    "llama70b_q4k": dict(hidden=8192, features=28672, top_k=4096, layers=80),
+    "gemma12b_q4k": dict(hidden=3840, features=15360, top_k=1024, layers=48),
+    "qwen06b_q4k": dict(hidden=1024, features=3072, top_k=512, layers=1),
+}
+Q4K_BPE = 144.0 / 256.0
+
+
+def algorithmic_bytes_per_token_layer(hidden: int, features: int, top_k: int) -> int:
+    row = hidden // 256 * 144
+    return features * row + 2 * top_k * row + 8 * hidden
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.05)
+
+    def __enter__(self):
+        if self.nv:
+            self._thr = threading.Thread(target=self._run, daemon=True)
+            self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thr:
+            self._thr.join()
+
+    def summary(self):
+        return {"sm_mhz": float(np.median(self.samples)) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def physical_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+# ------------------------------------------------------------------ reference arm
+def host_layer(wl, layer: int):
+    """One layer's gate/up/down quantised on the host with the oracle's encoder."""
+    import oracle
+    mats = []
+    for j in range(3):
+        rng = np.random.Generator(np.random.PCG64(0x1A2B0000 + 8 * layer + j))
+        w = rng.standard_normal((wl["features"], wl["hidden"]), dtype=np.float32)
+        w *= np.float32(0.02)
+        mats.append(oracle.quantize_matrix(oracle.FMT_Q4_K, w))
+        del w
+    return mats
+
+
+def cpu_walk_layers_per_s(mats, wl, batch: int, budget_s: float, threads: int):
+    """Times the oracle's threaded walk (one layer, `batch` tokens per call) for ~budget_s."""
+    import oracle
+    xs = [oracle.rms_norm(np.random.Generator(np.random.PCG64(0x5EED0000 + q)).standard_normal(
+        wl["hidden"], dtype=np.float32)) for q in range(4)]
+    oracle.walk_token_mt(*mats, xs[0], wl["top_k"], threads)  # warm
+    n, t0 = 0, time.perf_counter()
+    while True:
+        for b in range(batch):
+            oracle.walk_token_mt(*mats, xs[(n + b) % 4], wl["top_k"], threads)
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt >= budget_s or n >= 64:
+            return n / dt, n, dt
+
+
+def run_reference(args, wl):
+    import oracle
+    threads = oracle.host_threads()
+    mats = host_layer(wl, 0)
+    xs = [oracle.rms_norm(np.random.Generator(np.random.PCG64(0x5EED0000 + q)).standard_normal(
+        wl["hidden"], dtype=np.float32)) for q in range(4)]
+    for i in range(args.warmup):
+        oracle.walk_token_mt(*mats, xs[i % 4], wl["top_k"], threads)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        for b in range(args.batch):
+            oracle.walk_token_mt(*mats, xs[(i + b) % 4], wl["top_k"], threads)
+    dt = time.perf_counter() - t0
+    ms_layer = dt / args.steps * 1e3
+    tok_s = args.batch / (ms_layer * 1e-3 * wl["layers"])
+    sample = (f"each step = 1 of {wl['layers']} layers x {args.batch} token(s) (layer 0 weights, oracle "
+              f"walk_token_mt); tokens/s extrapolated over {wl['layers']} layers")
+    line = {
+        "impl": "reference", "metric": "walk_ffn_tokens_per_s", "value": tok_s, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_layer * wl["layers"],
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_of(args, wl),
+        "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def config_of(args, wl):
+    return {"workload": f"{args.workload}: hidden {wl['hidden']}, features {wl['features']}, top_k {wl['top_k']}, "
+                        f"{wl['layers']} layers, Q4_K gate/up/down N(0,0.02), batch {args.batch}",
+            "batch": args.batch, "layers": wl["layers"],
+            "l2": "inputs larger than L2: every layer streams its own 132 MB+ of weights"
+                  if wl["features"] * wl["hidden"] * Q4K_BPE * wl["layers"] > 3 * 126e6 else
+                  "weights rotate over copies larger than L2",
+            "parallelism": f"features sharded over {args.gpus} GPU(s)" if args.gpus > 1 else "single GPU"}
+
+
+# ------------------------------------------------------------------------ our arm
+def run_ours(args, wl):
+    import torch
+    import torch.distributed as dist
+
+    import larql_b200
+
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    be = larql_b200.CudaBackend(local)
+    ext = torch.cuda.ExternalStream(be.stream(), device=dev)
+
+    H, N, K, L, B = wl["hidden"], wl["features"], wl["top_k"], wl["layers"], args.batch
+    if world > 1:
+        raise SystemExit("multi-GPU sharded walk: not wired into the benchmark yet")
+    row = H // 256 * 144
+    # Small workloads rotate over enough distinct weight copies to exceed L2 between reuses.
+    copies = 1
+    per_layer = 3 * N * row
+    if per_layer * L < 3 * 126e6:
+        copies = int(np.ceil(3 * 126e6 / (per_layer * L)))
+    layers = []
+    gen = torch.Generator(device=dev)
+    tmp = torch.empty(N * H, dtype=torch.float32, device=dev)
+    for l in range(L * copies):
+        mats = []
+        for j in range(3):
+            gen.manual_seed(0x1A2B0000 + 8 * l + j)
+            tmp.normal_(0.0, 0.02, generator=gen)
+            q = torch.empty(N * row, dtype=torch.uint8, device=dev)
+            torch.cuda.synchronize()
+            be.dev_quantize_q4k(tmp.data_ptr(), N * H, q.data_ptr())
+            be.synchronize()
+            mats.append(larql_b200.DeviceMatrix(larql_b200.FMT_Q4_K, N, H, q.data_ptr(), q.numel(), keepalive=q))
+        layers.append(mats)
+    del tmp
+    torch.cuda.empty_cache()
+
+    launches0 = be.launch_count()
+    stacks = []
+    for c in range(copies):
+        ls = layers[c * L:(c + 1) * L]
+        stacks.append(be.stack_create([m[0] for m in ls], [m[1] for m in ls], [m[2] for m in ls], B, K,
+                                      larql_b200.WALK_FORCE_SPARSE))
+    launches_per_step = (be.launch_count() - launches0) // (2 * copies)
+
+    n_in = 8
+    gen.manual_seed(0x5EED0000)
+    h_in = torch.randn(n_in, B, H, dtype=torch.float32, device=dev, generator=gen)
+    h_out = torch.empty(B, H, dtype=torch.float32, device=dev)
+    torch.cuda.synchronize()
+
+    def step(i):
+        be.stack_run(stacks[i % copies], h_in[i % n_in].data_ptr(), h_out.data_ptr())
+
+    for i in range(args.warmup):
+        step(i)
+    be.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(physical_gpu_index(local)) as clk:
+        torch.cuda.synchronize()
+        ev0.record(ext)
+        for i in range(args.steps):
+            step(i)
+        ev1.record(ext)
+        be.synchronize()
+    ms_total = ev0.elapsed_time(ev1)
+    ms_step = ms_total / args.steps
+    tok_s = B / (ms_step * 1e-3)
+    alg_bytes = algorithmic_bytes_per_token_layer(H, N, K) * L  # per token (gate read once per token at batch 1)
+    walk_gbs = alg_bytes * B / (ms_step * 1e-3) / 1e9
+
+    # Per-kernel device time (CUDA events between phases on the launching stream), all layers.
+    phase = np.zeros(6)
+    n_prof = 0
+    flags = larql_b200.WALK_RMSNORM | larql_b200.WALK_RESIDUAL | larql_b200.WALK_FORCE_SPARSE
+    scratch = torch.empty(H, dtype=torch.float32, device=dev)
+    for rep in range(2):
+        for l in range(L * copies):
+            ms = be.profile_walk(*layers[l], h_in[(rep + l) % n_in, 0].data_ptr(), K, flags, scratch.data_ptr())
+            if rep > 0 or L * copies == 1:
+                phase += np.array(ms)
+                n_prof += 1
+    phase /= max(n_prof, 1)
+    scan_ms = float(phase[1])
+    peak, peak_kind = measured_peaks()
+    gate_bytes = N * row
+    achieved = gate_bytes / (scan_ms * 1e-3) / 1e9 if scan_ms > 0 else 0.0
+
+    # End to end through the host-pointer C-ABI call, one call per layer: H2D of the layer
+    # input and D2H of its output inside the timed region.
+    e2e_steps = max(1, min(args.steps, 5))
+    hp_in = torch.randn(n_in, B, H, dtype=torch.float32).pin_memory()
+    hp_a = torch.empty(B, H, dtype=torch.float32).pin_memory()
+    lib = larql_b200.load_library()
+    import ctypes as C
+    cm = [[m.c() for m in mats] for mats in layers]
+
+    def e2e_step(i):
+        src = hp_in[i % n_in].data_ptr()
+        base = (i % copies) * L
+        for l in range(L):
+            g, u, d = cm[base + l]
+            rc = lib.lq_walk_ffn(be._h, C.byref(g), C.byref(u), C.byref(d), src, B, K, flags, hp_a.data_ptr(),
+                                 None, None)
+            if rc != 0:
+                raise RuntimeError(f"lq_walk_ffn status {rc}")
+            src = hp_a.data_ptr()
+
+    e2e_step(0)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(i + 1)
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) / e2e_steps * 1e3
+    e2e_tok_s = B / (e2e_ms * 1e-3)
+
+    # CPU baseline: the oracle's threaded walk on layer 0's weights copied back to the host.
+    import oracle
+    threads = oracle.host_threads()
+    host_mats = [oracle.Matrix(oracle.FMT_Q4_K, N, H, m.keepalive.cpu().numpy()) for m in layers[0]]
+    lps, n_calls, dt = cpu_walk_layers_per_s(host_mats, wl, B, args.cpu_budget, threads)
+    cpu_tok_s = lps * B / L
+
+    line = {
+        "metric": "walk_ffn_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_of(args, wl),
+        "walk_gbs": walk_gbs, "walk_frac_of_measured_hbm": walk_gbs / peak,
+        "algorithmic_bytes_per_token": alg_bytes,
+        "phase_ms_per_layer": {k: float(v) for k, v in zip(
+            ["prepare", "gate_scan", "select", "rescore_final", "gather", "finish"], phase)},
+        "roofline": {"kernel": "scan_q4k_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
+                     "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "algorithmic_bytes_per_launch": gate_bytes, "avg_launch_ms": scan_ms},
+        "cpu_baseline": {"value": cpu_tok_s, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": f"{n_calls} calls of one layer x {B} token(s) on layer 0 in {dt:.1f}s, "
+                                   f"extrapolated over {L} layers"},
+        "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": B * H * 4 * L, "d2h_bytes_per_step": B * H * 4 * L,
+                "path": "lq_walk_ffn per layer, pinned host activations, resident weights"},
+        "gpu_launches": int(launches_per_step * args.steps),
+        "clocks": clk.summary(),
+    }
+    if rank == 0:
+        print(json.dumps(line))
+    for s in stacks:
+        be.stack_destroy(s)
+    be.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="llama70b_q4k", choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU baseline work")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", 0)) == 0:
+            run_reference(args, wl)
+        return
+    run_ours(args, wl)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,187 @@
+/*
+ * larql_cuda.h — C ABI of the B200 (sm_100a) backend for LARQL's vindex FFN walk.
+ *
+ * This is the boundary a `larql-compute-cuda` crate binds (extern "C", plain
+ * pointers and sizes).  Every entry point names the reference trait method or
+ * function it stands in for (paths relative to the reference repository).
+ *
+ * Conventions
+ *   - Status: 0 = ok.  > 0 = refusal, which the Rust shim maps to `None` ("cannot
+ *     compute this": bad geometry, unsupported format) — never a wrong or zero-filled
+ *     answer (crates/larql-compute/src/backend/quant_matvec.rs:378-427,
+ *     crates/larql-compute/src/cpu/ops/kernel_shape.rs:1-17).  < 0 = device / runtime
+ *     error; lq_last_error() has the text.
+ *   - Host entry points (lq_*) take HOST pointers.  Weights are long-lived, immutable
+ *     byte ranges (mmap slices in the reference, backend/mod.rs:68-89); they are
+ *     uploaded once and cached by (address, length) exactly like the reference's GPU
+ *     backend does (crates/larql-compute-metal/src/buffers/mod.rs:107-160).
+ *     Activations are copied per call; outputs are written to caller memory.
+ *   - Device entry points (lq_dev_*) take DEVICE pointers, enqueue on the context's
+ *     stream and do not synchronise; call lq_synchronize() to wait and collect errors.
+ *   - There is no CPU fallback anywhere: without a CUDA device lq_create fails.
+ *   - A context is used by one thread at a time (the reference serialises device
+ *     calls behind a mutex, crates/larql-vindex/src/format/vindex3/opplan/exec/device.rs:39-42).
+ */
+#ifndef LARQL_CUDA_H
+#define LARQL_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LQ_API __attribute__((visibility("default")))
+
+typedef struct lq_ctx lq_ctx;
+
+enum lq_status {
+    LQ_OK = 0,
+    LQ_REFUSED_SHAPE = 1,       /* geometry does not describe the operands (-> None) */
+    LQ_REFUSED_UNSUPPORTED = 2, /* no kernel for this format / size (-> None) */
+    LQ_ERR_NAN_SCORE = 3,       /* a gate score is NaN: the reference's top_k_by_abs panics */
+    LQ_ERR_CUDA = -1,
+    LQ_ERR_TIMEOUT = -2,        /* a bounded device-side wait ran out */
+    LQ_ERR_ARGUMENT = -3,
+};
+
+/* Weight formats (layouts as in the reference):
+ *   Q4_K  : 144-byte super-blocks of 256 (crates/larql-models/src/quant/ggml/q4_k.rs:9-21)
+ *   Q8_0  : ggml 34-byte blocks of 32    (crates/larql-compute/src/cpu/kquant_gemv.rs:1-10)
+ *   MXFP4 : packed [rows,K/32,16] + e8m0 scales [rows,K/32] (crates/larql-models/src/quant/mxfp4.rs:1-9)
+ *   NVFP4 : packed [rows,K/16,8] + e4m3 scales [rows,K/16] + f32 tensor scale
+ *           (crates/larql-models/src/quant/nvfp4.rs:24-36)                              */
+enum lq_format { LQ_FMT_Q4_K = 0, LQ_FMT_Q8_0 = 1, LQ_FMT_MXFP4 = 2, LQ_FMT_NVFP4 = 3 };
+/* OR-ed into lq_matrix.fmt: data/scales are DEVICE pointers already (resident weights handed to
+ * a host-pointer entry point; activations and outputs stay host memory). */
+#define LQ_MAT_DEVICE 0x100
+
+typedef struct lq_matrix {
+    int32_t fmt;          /* enum lq_format */
+    const void* data;     /* blocks (Q4_K/Q8_0) or packed codes (MXFP4/NVFP4) */
+    size_t data_len;      /* bytes */
+    const void* scales;   /* MXFP4/NVFP4 scale stream, else NULL */
+    size_t scales_len;
+    float tensor_scale;   /* NVFP4 only */
+    int64_t rows, cols;
+} lq_matrix;
+
+/* Walk flags. */
+#define LQ_WALK_RMSNORM 1u      /* input is the raw residual: RMS-normalise it first (unit weight,
+                                   eps 1e-6; crates/larql-compute/src/residual.rs:56-78) */
+#define LQ_WALK_RESIDUAL 2u     /* out = input + walk(...)  (run_ffn,
+                                   crates/larql-compute/src/forward/layer.rs:109-124) */
+#define LQ_WALK_FORCE_SPARSE 4u /* keep the sparse walk even when K >= 80% of the features
+                                   (WalkFfnConfig::force_walk; default rewrites to dense,
+                                   crates/larql-inference/src/vindex/walk_ffn/helpers.rs:18-30) */
+
+/* ---- context ----------------------------------------------------------------- */
+/* BackendCtor for BackendKind::Cuda (crates/larql-compute/src/backend/factory.rs:127-130):
+ * a non-zero return means "no device" and the registry entry yields None. */
+LQ_API int lq_create(int device, lq_ctx** out);
+LQ_API void lq_destroy(lq_ctx* ctx);
+/* Text of the last failure on this context ("" if none). */
+LQ_API const char* lq_last_error(lq_ctx* ctx);
+/* ComputeBackend::device_info (backend/mod.rs:54-56). */
+LQ_API int lq_device_info(lq_ctx* ctx, char* buf, size_t cap);
+/* QuantMatVec::supports_quant (backend/quant_matvec.rs:367-370): 1 or 0. */
+LQ_API int lq_supports_quant(lq_ctx* ctx, int fmt);
+/* Waits for the context's stream and reports any device-side error recorded since the last call. */
+LQ_API int lq_synchronize(lq_ctx* ctx);
+/* The context's cudaStream_t (for callers that enqueue their own work around lq_dev_* calls). */
+LQ_API void* lq_stream(lq_ctx* ctx);
+/* MatMul::submission_clock (backend/matmul.rs:25-42,209-218): kernel launches issued by this context. */
+LQ_API uint64_t lq_launch_count(lq_ctx* ctx);
+
+/* ---- weight residency ---------------------------------------------------------- */
+/* ComputeBackend::register_weight_region / seal_weight_regions (backend/mod.rs:68-89) and
+ * MatMul::wire_resident (backend/matmul.rs:207): upload a host byte range once.  Any later
+ * host-pointer call whose weight slice lies inside a registered range uses the device copy. */
+LQ_API int lq_register_weight_region(lq_ctx* ctx, const void* host, size_t len);
+LQ_API int lq_seal_weight_regions(lq_ctx* ctx);
+LQ_API int lq_drop_weight_regions(lq_ctx* ctx);
+/* Device address of a registered host range (NULL if not resident). */
+LQ_API const void* lq_device_ptr(lq_ctx* ctx, const void* host, size_t len);
+
+/* ---- dense quantised matvec / matmul (host pointers) --------------------------- */
+/* QuantMatVec::q4k_matvec (backend/quant_matvec.rs:252-260) -> CpuBackend::q4k_matvec
+ * (crates/larql-compute/src/cpu/mod.rs:95-114).  Shape rule = KernelShapeError::check:
+ * out_len == num_rows, x_len == hidden, hidden % 256 == 0, w_len >= needed. */
+LQ_API int lq_q4k_matvec(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len,
+                         size_t num_rows, size_t hidden, float* out, size_t out_len);
+/* QuantMatVec::q4k_matmul (backend/quant_matvec.rs:324-333): x [seq,hidden] -> out [seq,num_rows]. */
+LQ_API int lq_q4k_matmul(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len,
+                         size_t num_rows, size_t hidden, size_t seq_len, float* out, size_t out_len);
+/* The same matvec in the reference's exact f32 order (bit-identical to the CPU backend);
+ * slower, used to resolve top-K boundary cases and by the parity tests.  No trait counterpart. */
+LQ_API int lq_q4k_matvec_exact(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len,
+                               size_t num_rows, size_t hidden, float* out, size_t out_len);
+
+/* top_k_by_abs (crates/larql-vindex/src/index/compute/gate_knn/mod.rs:50-108): the top_k largest
+ * |score|, ties to the lower index, sorted by |score| descending then index.  *count = min(top_k, n).
+ * LQ_ERR_NAN_SCORE if a score is NaN. */
+LQ_API int lq_topk_abs(lq_ctx* ctx, const float* scores, size_t n, size_t top_k, uint32_t* idx_out,
+                       float* val_out, size_t* count);
+
+/* rms_norm_eps with unit weight (crates/larql-compute/src/residual.rs:56-78): x,out [rows,cols]. */
+LQ_API int lq_rms_norm(lq_ctx* ctx, const float* x, size_t rows, size_t cols, double eps, float* out);
+
+/* Block decoders on the device, for the bit-exact weight check: dequantize_q4_k
+ * (crates/larql-models/src/quant/ggml/q4_k.rs:286-338), dequantize_q8_0 (ggml/legacy.rs:68-83),
+ * mxfp4::dequantize_expert (quant/mxfp4.rs:42-95), nvfp4::dequantize_into (quant/nvfp4.rs:192-222).
+ * out holds rows*cols floats. */
+LQ_API int lq_dequantize(lq_ctx* ctx, const lq_matrix* m, float* out, size_t out_len);
+
+/* ---- the walk (host pointers) --------------------------------------------------- */
+/* One FFN layer for `batch` tokens: gate scan -> top-K by |score| -> SiLU-gated up/down
+ * accumulate; WalkFfn::forward (crates/larql-inference/src/vindex/walk_ffn/mod.rs:535-542) ->
+ * walk_ffn_sparse (…/walk_ffn/sparse.rs:60-306).  gate, up: [features, hidden];
+ * down_fm: feature-major [features, hidden] (…/write_kquant/feature_major_down.rs:46-90).
+ * x, out: [batch, hidden].  idx_out (optional): [batch, min(top_k, features)] selected feature
+ * ids per token (certain rows ascending, then resolved boundary rows); count_out (optional):
+ * hits per token. */
+LQ_API int lq_walk_ffn(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const lq_matrix* down_fm,
+                       const float* x, size_t batch, size_t top_k, uint32_t flags, float* out,
+                       uint32_t* idx_out, uint32_t* count_out);
+
+/* ---- device-pointer variants (async on the context's stream) --------------------- */
+LQ_API int lq_dev_q4k_matvec(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t num_rows,
+                             size_t hidden, float* out);
+LQ_API int lq_dev_walk_ffn(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const lq_matrix* down_fm,
+                           const float* x, size_t batch, size_t top_k, uint32_t flags, float* out,
+                           uint32_t* idx_out, uint32_t* count_out);
+
+/* A stack of walk layers run back to back on the device, h <- h + walk_l(rmsnorm(h)) for
+ * l = 0..n_layers (run_ffn per layer, forward/layer.rs:61-127), replayed from a CUDA graph.
+ * Matrices are DEVICE resident.  h_in/h_out: [batch, hidden] device pointers. */
+typedef struct lq_stack lq_stack;
+LQ_API int lq_stack_create(lq_ctx* ctx, const lq_matrix* gates, const lq_matrix* ups, const lq_matrix* downs_fm,
+                           size_t n_layers, size_t batch, size_t top_k, uint32_t flags, lq_stack** out);
+LQ_API int lq_stack_run(lq_ctx* ctx, lq_stack* stack, const float* h_in, float* h_out);
+LQ_API void lq_stack_destroy(lq_ctx* ctx, lq_stack* stack);
+
+/* quantize_q4_k (crates/larql-compute/src/cpu/ops/q4_common/quantize.rs:89-189) on the device:
+ * src [n_elems] f32 (n_elems % 256 == 0) -> dst [n_elems/256*144] bytes, byte-identical to the CPU
+ * encoder.  Device pointers, dst 16-byte aligned.  Builds synthetic layers directly in HBM. */
+LQ_API int lq_dev_quantize_q4k(lq_ctx* ctx, const float* src, size_t n_elems, uint8_t* dst);
+
+/* One token of lq_dev_walk_ffn with CUDA events between the phases; ms[6] receives the device
+ * time of {prepare, gate scan, select, exact re-score + final pick, gather, finish}.  Synchronises.
+ * No trait counterpart (the reference's equivalent is PhaseTimingsHandle,
+ * crates/larql-inference/src/vindex/walk_ffn/timings.rs:12-33). */
+LQ_API int lq_profile_walk(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const lq_matrix* down_fm,
+                           const float* x, size_t top_k, uint32_t flags, float* out, float* ms);
+
+/* Diagnostics of the last walk on this context (token 0): rows certainly selected, rows in the
+ * boundary band that were re-scored exactly, threshold and error bound. */
+typedef struct lq_walk_stats {
+    int32_t n_certain, n_band, n_hits, need;
+    float tau, bound;
+} lq_walk_stats;
+LQ_API int lq_last_walk_stats(lq_ctx* ctx, lq_walk_stats* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LARQL_CUDA_H */

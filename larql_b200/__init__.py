@@ -1,0 +1,323 @@
+"""larql_b200 — B200 (sm_100a) backend for LARQL's vindex FFN walk.
+
+The product is ``liblarql_b200.so`` (hand-written CUDA behind the C ABI in
+``include/larql_cuda.h``).  This package is the thin host-side binding used by the
+tests and the benchmark: :class:`CudaBackend` mirrors the method names, argument
+meaning and refusal behaviour of the reference's ``ComputeBackend`` /
+``QuantMatVec`` / ``MatMul`` traits for the walk path (``None`` = "cannot compute
+this", never a wrong answer).
+
+There is no CPU fallback: importing works anywhere, but constructing a backend
+without the built library or without a CUDA device raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "liblarql_b200.so"
+
+FMT_Q4_K, FMT_Q8_0, FMT_MXFP4, FMT_NVFP4 = 0, 1, 2, 3
+MAT_DEVICE = 0x100  # OR-ed into a matrix format: data/scales are device pointers
+WALK_RMSNORM, WALK_RESIDUAL, WALK_FORCE_SPARSE = 1, 2, 4
+
+LQ_OK = 0
+LQ_REFUSED_SHAPE, LQ_REFUSED_UNSUPPORTED, LQ_ERR_NAN_SCORE = 1, 2, 3
+LQ_ERR_CUDA, LQ_ERR_TIMEOUT, LQ_ERR_ARGUMENT = -1, -2, -3
+
+# Every symbol include/larql_cuda.h declares (checked by the CPU test-suite).
+EXPORTS = [
+    "lq_create", "lq_destroy", "lq_last_error", "lq_device_info", "lq_supports_quant", "lq_synchronize",
+    "lq_stream", "lq_launch_count", "lq_register_weight_region", "lq_seal_weight_regions",
+    "lq_drop_weight_regions", "lq_device_ptr", "lq_q4k_matvec", "lq_q4k_matmul", "lq_q4k_matvec_exact",
+    "lq_topk_abs", "lq_rms_norm", "lq_dequantize", "lq_walk_ffn", "lq_dev_q4k_matvec", "lq_dev_walk_ffn",
+    "lq_stack_create", "lq_stack_run", "lq_stack_destroy", "lq_last_walk_stats", "lq_dev_quantize_q4k",
+    "lq_profile_walk",
+]
+
+
+class BackendError(RuntimeError):
+    """A device/runtime failure (negative status) or the reference's panic cases."""
+
+
+class LqMatrix(C.Structure):
+    _fields_ = [("fmt", C.c_int32), ("data", C.c_void_p), ("data_len", C.c_size_t), ("scales", C.c_void_p),
+                ("scales_len", C.c_size_t), ("tensor_scale", C.c_float), ("rows", C.c_int64), ("cols", C.c_int64)]
+
+
+class WalkStats(C.Structure):
+    _fields_ = [("n_certain", C.c_int32), ("n_band", C.c_int32), ("n_hits", C.c_int32), ("need", C.c_int32),
+                ("tau", C.c_float), ("bound", C.c_float)]
+
+
+_lib = None
+
+
+def load_library() -> C.CDLL:
+    """dlopen the built CUDA library; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise BackendError(f"{LIB_PATH} is missing: run `python -m larql_b200.build` (no CPU fallback exists)")
+    lib = C.CDLL(str(LIB_PATH))
+    vp, sz, u32p, f32p = C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p
+    mp = C.POINTER(LqMatrix)
+    sig = {
+        "lq_create": (C.c_int, [C.c_int, C.POINTER(vp)]),
+        "lq_destroy": (None, [vp]),
+        "lq_last_error": (C.c_char_p, [vp]),
+        "lq_device_info": (C.c_int, [vp, C.c_char_p, sz]),
+        "lq_supports_quant": (C.c_int, [vp, C.c_int]),
+        "lq_synchronize": (C.c_int, [vp]),
+        "lq_stream": (vp, [vp]),
+        "lq_launch_count": (C.c_uint64, [vp]),
+        "lq_register_weight_region": (C.c_int, [vp, vp, sz]),
+        "lq_seal_weight_regions": (C.c_int, [vp]),
+        "lq_drop_weight_regions": (C.c_int, [vp]),
+        "lq_device_ptr": (vp, [vp, vp, sz]),
+        "lq_q4k_matvec": (C.c_int, [vp, vp, sz, f32p, sz, sz, sz, f32p, sz]),
+        "lq_q4k_matvec_exact": (C.c_int, [vp, vp, sz, f32p, sz, sz, sz, f32p, sz]),
+        "lq_q4k_matmul": (C.c_int, [vp, vp, sz, f32p, sz, sz, sz, sz, f32p, sz]),
+        "lq_topk_abs": (C.c_int, [vp, f32p, sz, sz, u32p, f32p, C.POINTER(sz)]),
+        "lq_rms_norm": (C.c_int, [vp, f32p, sz, sz, C.c_double, f32p]),
+        "lq_dequantize": (C.c_int, [vp, mp, f32p, sz]),
+        "lq_walk_ffn": (C.c_int, [vp, mp, mp, mp, f32p, sz, sz, C.c_uint32, f32p, u32p, u32p]),
+        "lq_dev_q4k_matvec": (C.c_int, [vp, vp, sz, f32p, sz, sz, f32p]),
+        "lq_dev_walk_ffn": (C.c_int, [vp, mp, mp, mp, f32p, sz, sz, C.c_uint32, f32p, u32p, u32p]),
+        "lq_stack_create": (C.c_int, [vp, mp, mp, mp, sz, sz, sz, C.c_uint32, C.POINTER(vp)]),
+        "lq_stack_run": (C.c_int, [vp, vp, f32p, f32p]),
+        "lq_stack_destroy": (None, [vp, vp]),
+        "lq_last_walk_stats": (C.c_int, [vp, C.POINTER(WalkStats)]),
+        "lq_dev_quantize_q4k": (C.c_int, [vp, f32p, sz, vp]),
+        "lq_profile_walk": (C.c_int, [vp, mp, mp, mp, f32p, sz, C.c_uint32, f32p, f32p]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _u8(a):
+    return np.ascontiguousarray(a, dtype=np.uint8)
+
+
+def _ptr(a):
+    return a.ctypes.data if a is not None and a.size else None
+
+
+class HostMatrix:
+    """A quantised [rows, cols] matrix held in host memory (numpy), as the reference's mmap slices are."""
+
+    def __init__(self, fmt: int, rows: int, cols: int, data, scales=None, tensor_scale: float = 1.0):
+        self.fmt, self.rows, self.cols = int(fmt), int(rows), int(cols)
+        self.data = _u8(data)
+        self.scales = _u8(scales) if scales is not None else None
+        self.tensor_scale = float(tensor_scale)
+
+    def c(self) -> LqMatrix:
+        return LqMatrix(self.fmt, _ptr(self.data), self.data.size, _ptr(self.scales) if self.scales is not None else None,
+                        self.scales.size if self.scales is not None else 0, self.tensor_scale, self.rows, self.cols)
+
+
+class DeviceMatrix:
+    """A quantised matrix resident in device memory (raw device pointers, e.g. from torch tensors)."""
+
+    def __init__(self, fmt: int, rows: int, cols: int, data_ptr: int, data_len: int, scales_ptr: int = 0,
+                 scales_len: int = 0, tensor_scale: float = 1.0, keepalive=None):
+        self.fmt, self.rows, self.cols = int(fmt), int(rows), int(cols)
+        self.data_ptr, self.data_len, self.scales_ptr, self.scales_len = data_ptr, data_len, scales_ptr, scales_len
+        self.tensor_scale = float(tensor_scale)
+        self.keepalive = keepalive
+
+    def c(self) -> LqMatrix:
+        return LqMatrix(self.fmt | MAT_DEVICE, self.data_ptr, self.data_len, self.scales_ptr or None,
+                        self.scales_len, self.tensor_scale, self.rows, self.cols)
+
+
+class CudaBackend:
+    """Host-side mirror of the reference's backend trait for the walk path.
+
+    Method names and argument meaning follow ``QuantMatVec`` / ``MatMul``
+    (crates/larql-compute/src/backend/quant_matvec.rs, matmul.rs).  Methods return
+    ``None`` on a refusal (bad geometry, unsupported format) and raise
+    :class:`BackendError` on device errors and on the reference's panic cases.
+    """
+
+    def __init__(self, device: int = 0):
+        self._lib = load_library()
+        h = C.c_void_p()
+        rc = self._lib.lq_create(device, C.byref(h))
+        if rc != 0 or not h.value:
+            raise BackendError(f"lq_create(device={device}) failed with status {rc}: no usable CUDA device "
+                               f"(there is no CPU fallback)")
+        self._h = h
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.lq_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- plumbing ------------------------------------------------------------
+    def _status(self, rc: int):
+        """0 -> True, refusal -> None... returns True when ok, False when refused, raises otherwise."""
+        if rc == LQ_OK:
+            return True
+        msg = self._lib.lq_last_error(self._h).decode()
+        if rc in (LQ_REFUSED_SHAPE, LQ_REFUSED_UNSUPPORTED):
+            self.last_refusal = msg
+            return False
+        raise BackendError(f"status {rc}: {msg}")
+
+    def name(self) -> str:
+        return "cuda-b200"
+
+    def device_info(self) -> str:
+        buf = C.create_string_buffer(512)
+        self._lib.lq_device_info(self._h, buf, 512)
+        return buf.value.decode()
+
+    def supports_quant(self, fmt: int) -> bool:
+        return bool(self._lib.lq_supports_quant(self._h, fmt))
+
+    def synchronize(self):
+        self._status(self._lib.lq_synchronize(self._h))
+
+    def stream(self) -> int:
+        return self._lib.lq_stream(self._h)
+
+    def launch_count(self) -> int:
+        return int(self._lib.lq_launch_count(self._h))
+
+    def register_weight_region(self, arr: np.ndarray):
+        self._status(self._lib.lq_register_weight_region(self._h, arr.ctypes.data, arr.nbytes))
+
+    def seal_weight_regions(self):
+        self._status(self._lib.lq_seal_weight_regions(self._h))
+
+    def drop_weight_regions(self):
+        self._status(self._lib.lq_drop_weight_regions(self._h))
+
+    def device_ptr(self, arr: np.ndarray):
+        return self._lib.lq_device_ptr(self._h, arr.ctypes.data, arr.nbytes)
+
+    # -- QuantMatVec ----------------------------------------------------------
+    def q4k_matvec(self, q4k_data, x, num_rows: int, hidden: int, exact: bool = False):
+        w, x = _u8(q4k_data), _f32(x)
+        out = np.empty(num_rows, np.float32)
+        fn = self._lib.lq_q4k_matvec_exact if exact else self._lib.lq_q4k_matvec
+        ok = self._status(fn(self._h, _ptr(w), w.size, _ptr(x), x.size, num_rows, hidden, _ptr(out), out.size))
+        return out if ok else None
+
+    def q4k_matmul(self, q4k_data, x, num_rows: int, hidden: int, seq_len: int):
+        w, x = _u8(q4k_data), _f32(x)
+        out = np.empty(seq_len * num_rows, np.float32)
+        ok = self._status(self._lib.lq_q4k_matmul(self._h, _ptr(w), w.size, _ptr(x), x.size, num_rows, hidden,
+                                                  seq_len, _ptr(out), out.size))
+        return out.reshape(seq_len, num_rows) if ok else None
+
+    def quant_matvec(self, fmt: int, weights, x, num_rows: int, hidden: int):
+        """Format-dispatched matvec (quant_matvec.rs:50-98): Q4_K only through this signature."""
+        if fmt == FMT_Q4_K:
+            return self.q4k_matvec(weights, x, num_rows, hidden)
+        return None
+
+    # -- selection, norm, decode ----------------------------------------------
+    def top_k_by_abs(self, scores, top_k: int):
+        s = _f32(scores).reshape(-1)
+        k = min(int(top_k), s.size)
+        idx = np.empty(max(k, 1), np.uint32)
+        val = np.empty(max(k, 1), np.float32)
+        cnt = C.c_size_t(0)
+        self._status(self._lib.lq_topk_abs(self._h, _ptr(s), s.size, int(top_k), idx.ctypes.data, val.ctypes.data,
+                                           C.byref(cnt)))
+        return idx[:cnt.value].copy(), val[:cnt.value].copy()
+
+    def rms_norm(self, x, eps: float = 1e-6):
+        x = _f32(x)
+        x2 = x.reshape(-1, x.shape[-1])
+        out = np.empty_like(x2)
+        ok = self._status(self._lib.lq_rms_norm(self._h, _ptr(x2), x2.shape[0], x2.shape[1], eps, _ptr(out)))
+        return out.reshape(x.shape) if ok else None
+
+    def dequantize(self, m: HostMatrix):
+        out = np.empty(m.rows * m.cols, np.float32)
+        mc = m.c()
+        ok = self._status(self._lib.lq_dequantize(self._h, C.byref(mc), _ptr(out), out.size))
+        return out.reshape(m.rows, m.cols) if ok else None
+
+    # -- the walk -------------------------------------------------------------
+    def walk_ffn(self, gate: HostMatrix, up: HostMatrix, down_fm: HostMatrix, x, top_k: int, flags: int = 0,
+                 want_idx: bool = True):
+        """One layer for x [batch, hidden] (host). Returns (out, idx_list) or None on refusal."""
+        x = _f32(x)
+        x2 = x.reshape(-1, gate.cols) if gate.cols else x.reshape(x.shape[0] if x.ndim > 1 else 1, 0)
+        batch = x2.shape[0]
+        n = gate.rows
+        k_eff = n if (not (flags & WALK_FORCE_SPARSE) and top_k >= (n * 4) // 5) else min(top_k, n)
+        out = np.empty_like(x2)
+        idx = np.zeros((batch, max(k_eff, 1)), np.uint32)
+        cnt = np.zeros(batch, np.uint32)
+        g, u, d = gate.c(), up.c(), down_fm.c()
+        ok = self._status(self._lib.lq_walk_ffn(self._h, C.byref(g), C.byref(u), C.byref(d), _ptr(x2), batch,
+                                                int(top_k), flags, _ptr(out), idx.ctypes.data if want_idx else None,
+                                                cnt.ctypes.data if want_idx else None))
+        if not ok:
+            return None
+        hits = [idx[t, :cnt[t]].copy() for t in range(batch)] if want_idx else None
+        return out.reshape(x.shape), hits
+
+    def last_walk_stats(self) -> WalkStats:
+        s = WalkStats()
+        self._lib.lq_last_walk_stats(self._h, C.byref(s))
+        return s
+
+    # -- device-pointer API (torch tensors or raw pointers) --------------------
+    def dev_q4k_matvec(self, w_ptr: int, w_len: int, x_ptr: int, num_rows: int, hidden: int, out_ptr: int):
+        return self._status(self._lib.lq_dev_q4k_matvec(self._h, w_ptr, w_len, x_ptr, num_rows, hidden, out_ptr))
+
+    def dev_walk_ffn(self, gate: DeviceMatrix, up: DeviceMatrix, down_fm: DeviceMatrix, x_ptr: int, batch: int,
+                     top_k: int, flags: int, out_ptr: int, idx_ptr: int = 0, count_ptr: int = 0):
+        g, u, d = gate.c(), up.c(), down_fm.c()
+        return self._status(self._lib.lq_dev_walk_ffn(self._h, C.byref(g), C.byref(u), C.byref(d), x_ptr, batch,
+                                                      int(top_k), flags, out_ptr, idx_ptr or None, count_ptr or None))
+
+    def dev_quantize_q4k(self, src_ptr: int, n_elems: int, dst_ptr: int):
+        return self._status(self._lib.lq_dev_quantize_q4k(self._h, src_ptr, n_elems, dst_ptr))
+
+    def profile_walk(self, gate, up, down_fm, x_ptr: int, top_k: int, flags: int, out_ptr: int):
+        """Per-phase device milliseconds of one token: prepare, scan, select, re-score, gather, finish."""
+        ms = (C.c_float * 6)()
+        g, u, d = gate.c(), up.c(), down_fm.c()
+        ok = self._status(self._lib.lq_profile_walk(self._h, C.byref(g), C.byref(u), C.byref(d), x_ptr, int(top_k),
+                                                    flags, out_ptr, ms))
+        return list(ms) if ok else None
+
+    def stack_create(self, gates, ups, downs, batch: int, top_k: int, flags: int = 0):
+        n = len(gates)
+        arr = (LqMatrix * n)
+        ga, ua, da = arr(*[m.c() for m in gates]), arr(*[m.c() for m in ups]), arr(*[m.c() for m in downs])
+        h = C.c_void_p()
+        ok = self._status(self._lib.lq_stack_create(self._h, ga, ua, da, n, batch, int(top_k), flags, C.byref(h)))
+        return h if ok else None
+
+    def stack_run(self, stack, h_in_ptr: int, h_out_ptr: int):
+        return self._status(self._lib.lq_stack_run(self._h, stack, h_in_ptr, h_out_ptr))
+
+    def stack_destroy(self, stack):
+        self._lib.lq_stack_destroy(self._h, stack)

@@ -1,0 +1,773 @@
+// C ABI of the backend: context, weight residency cache, workspace, and the entry
+// points declared in include/larql_cuda.h.  Host-side policy only; all arithmetic is
+// in the kernels.  There is deliberately no CPU path here: a missing device is an
+// error, an unsupported case is a refusal status.
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/larql_cuda.h"
+#include "kernels.h"
+
+using namespace lq;
+
+namespace lq {
+cudaError_t launch_final_pick(TokenWs ws, int* err, cudaStream_t st);
+cudaError_t launch_topk_abs_sorted(const float* scores, int n, int top_k, TokenWs ws, uint32_t* idx_out,
+                                   float* val_out, int* count_out, unsigned long long* sort_buf, int* err,
+                                   cudaStream_t st);
+cudaError_t launch_dequantize(const lq_matrix& m, float* out, cudaStream_t st);
+cudaError_t launch_quantize_q4k(const float* data, size_t n_elems, uint8_t* out, cudaStream_t st);
+}  // namespace lq
+
+struct lq_stack {
+    std::vector<lq_matrix> gates, ups, downs;
+    size_t batch = 0, top_k = 0;
+    uint32_t flags = 0;
+    int hidden = 0;
+    float *h_in = nullptr, *h_out = nullptr, *h_buf[2] = {nullptr, nullptr};
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+};
+
+struct lq_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int sm_count = 0;
+    std::string last_error;
+    std::string info;
+    int* d_err = nullptr;
+    uint64_t launches = 0;
+
+    struct Region {
+        const uint8_t* host;
+        size_t len;
+        uint8_t* dev;
+    };
+    std::vector<Region> regions;
+    bool sealed = false;
+
+    // workspace (grown on demand, never during graph capture)
+    size_t ws_batch = 0, ws_hidden = 0, ws_feat = 0;
+    uint8_t* ws_raw = nullptr;
+    std::vector<TokenWs> tok;
+    float* partials = nullptr;
+    int gather_grid = 0;
+    unsigned long long* sort_buf = nullptr;
+    size_t sort_cap = 0;
+    // staging for the host-pointer API
+    uint8_t* stage = nullptr;
+    size_t stage_cap = 0;
+    lq_walk_stats stats = {};
+};
+
+namespace {
+
+int fail(lq_ctx* c, int code, const std::string& msg) {
+    if (c) c->last_error = msg;
+    return code;
+}
+int cuda_fail(lq_ctx* c, cudaError_t e, const char* what) {
+    return fail(c, LQ_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+#define CK(call)                                             \
+    do {                                                     \
+        cudaError_t e__ = (call);                            \
+        if (e__ != cudaSuccess) return cuda_fail(ctx, e__, #call); \
+    } while (0)
+
+size_t a256(size_t v) { return (v + 255) / 256 * 256; }
+
+size_t row_bytes_of(int fmt, int64_t cols) {
+    switch (fmt) {
+        case LQ_FMT_Q4_K: return (size_t)(cols / 256) * 144;
+        case LQ_FMT_Q8_0: return (size_t)(cols / 32) * 34;
+        case LQ_FMT_MXFP4: return (size_t)(cols / 32) * 16;
+        case LQ_FMT_NVFP4: return (size_t)(cols / 16) * 8;
+    }
+    return 0;
+}
+
+// Shape rule per format; mirrors KernelShapeError::check (>= for Q4_K) and the exact-length
+// checks of q8_0_gemv / nvfp4_gemv.
+int check_matrix(lq_ctx* ctx, const lq_matrix* m, const char* name) {
+    if (!m || m->rows < 0 || m->cols < 0) return fail(ctx, LQ_ERR_ARGUMENT, std::string(name) + ": null/negative");
+    const int64_t r = m->rows, k = m->cols;
+    switch (m->fmt & 0xff) {
+        case LQ_FMT_Q4_K:
+            if (k % 256 != 0 || m->data_len < (size_t)r * row_bytes_of(LQ_FMT_Q4_K, k))
+                return fail(ctx, LQ_REFUSED_SHAPE, std::string(name) + ": Q4_K geometry");
+            break;
+        case LQ_FMT_Q8_0:
+            if (k == 0 || k % 32 != 0 || m->data_len != (size_t)r * row_bytes_of(LQ_FMT_Q8_0, k))
+                return fail(ctx, LQ_REFUSED_SHAPE, std::string(name) + ": Q8_0 geometry");
+            break;
+        case LQ_FMT_MXFP4:
+            if (k % 32 != 0 || m->data_len < (size_t)r * row_bytes_of(LQ_FMT_MXFP4, k) ||
+                m->scales_len < (size_t)r * (size_t)(k / 32) || !m->scales)
+                return fail(ctx, LQ_REFUSED_SHAPE, std::string(name) + ": MXFP4 geometry");
+            break;
+        case LQ_FMT_NVFP4:
+            if (k == 0 || k % 16 != 0 || m->data_len != (size_t)r * row_bytes_of(LQ_FMT_NVFP4, k) ||
+                m->scales_len != (size_t)r * (size_t)(k / 16) || !m->scales)
+                return fail(ctx, LQ_REFUSED_SHAPE, std::string(name) + ": NVFP4 geometry");
+            break;
+        default: return fail(ctx, LQ_REFUSED_UNSUPPORTED, std::string(name) + ": unknown format");
+    }
+    if (r > 0 && k > 0 && !m->data) return fail(ctx, LQ_ERR_ARGUMENT, std::string(name) + ": null data");
+    return LQ_OK;
+}
+
+int ensure_ws(lq_ctx* ctx, size_t batch, size_t hidden, size_t feat) {
+    if (batch <= ctx->ws_batch && hidden <= ctx->ws_hidden && feat <= ctx->ws_feat) return LQ_OK;
+    cudaStreamCaptureStatus cs;
+    CK(cudaStreamIsCapturing(ctx->stream, &cs));
+    if (cs != cudaStreamCaptureStatusNone) return fail(ctx, LQ_ERR_ARGUMENT, "workspace growth during capture");
+    CK(cudaStreamSynchronize(ctx->stream));
+    batch = std::max(batch, ctx->ws_batch);
+    hidden = std::max(hidden, ctx->ws_hidden);
+    feat = std::max(feat, ctx->ws_feat);
+    if (ctx->ws_raw) CK(cudaFree(ctx->ws_raw));
+    ctx->ws_raw = nullptr;
+    const size_t H = (hidden + 255) / 256 * 256, N = (feat + 31) / 32 * 32;
+    const size_t per_tok = a256(H * 4) + 2 * a256(H) + 3 * a256(H / 32 * 4) + 2 * a256(N * 4) + 256 + 4 * a256(N * 4);
+    ctx->gather_grid = ctx->sm_count;
+    const size_t part_bytes = a256((size_t)ctx->gather_grid * H * 4);
+    const size_t total = batch * per_tok + part_bytes;
+    CK(cudaMalloc(&ctx->ws_raw, total));
+    CK(cudaMemsetAsync(ctx->ws_raw, 0, total, ctx->stream));
+    uint8_t* p = ctx->ws_raw;
+    auto take = [&](size_t bytes) {
+        uint8_t* r = p;
+        p += a256(bytes);
+        return r;
+    };
+    ctx->tok.assign(batch, TokenWs{});
+    for (size_t t = 0; t < batch; ++t) {
+        TokenWs& w = ctx->tok[t];
+        w.xn = (float*)take(H * 4);
+        w.xa = (uint32_t*)take(H);
+        w.xb = (uint32_t*)take(H);
+        w.bscale = (float*)take(H / 32 * 4);
+        w.bsum = (float*)take(H / 32 * 4);
+        w.babs = (float*)take(H / 32 * 4);
+        w.scores = (float*)take(N * 4);
+        w.bounds = (float*)take(N * 4);
+        w.sel = (SelHeader*)take(256);
+        w.hit_idx = (uint32_t*)take(N * 4);
+        w.hit_score = (float*)take(N * 4);
+        w.band_idx = (uint32_t*)take(N * 4);
+        w.band_exact = (float*)take(N * 4);
+    }
+    ctx->partials = (float*)take((size_t)ctx->gather_grid * H * 4);
+    ctx->ws_batch = batch;
+    ctx->ws_hidden = hidden;
+    ctx->ws_feat = feat;
+    return LQ_OK;
+}
+
+int ensure_stage(lq_ctx* ctx, size_t bytes) {
+    if (bytes <= ctx->stage_cap) return LQ_OK;
+    CK(cudaStreamSynchronize(ctx->stream));
+    if (ctx->stage) CK(cudaFree(ctx->stage));
+    ctx->stage = nullptr;
+    ctx->stage_cap = 0;
+    CK(cudaMalloc(&ctx->stage, a256(bytes)));
+    ctx->stage_cap = a256(bytes);
+    return LQ_OK;
+}
+
+int ensure_sort(lq_ctx* ctx, size_t n) {
+    size_t pad = 1;
+    while (pad < n) pad <<= 1;
+    if (pad <= ctx->sort_cap) return LQ_OK;
+    CK(cudaStreamSynchronize(ctx->stream));
+    if (ctx->sort_buf) CK(cudaFree(ctx->sort_buf));
+    ctx->sort_buf = nullptr;
+    CK(cudaMalloc(&ctx->sort_buf, pad * 8));
+    ctx->sort_cap = pad;
+    return LQ_OK;
+}
+
+// Device copy of a host weight range: inside a registered region, else cached on first use
+// by (address, length) — the reference GPU backend's buffer-cache rule.
+int resolve(lq_ctx* ctx, const void* host, size_t len, const uint8_t** dev) {
+    *dev = nullptr;
+    if (len == 0) return LQ_OK;
+    const uint8_t* h = (const uint8_t*)host;
+    for (auto& r : ctx->regions)
+        if (h >= r.host && h + len <= r.host + r.len) {
+            *dev = r.dev + (h - r.host);
+            return LQ_OK;
+        }
+    if (ctx->sealed) return fail(ctx, LQ_ERR_ARGUMENT, "weight range outside the sealed regions");
+    uint8_t* d = nullptr;
+    CK(cudaMalloc(&d, a256(len) + 256));  // slack: bulk copies may round a ragged tail up to 16 B
+    cudaError_t e = cudaMemcpyAsync(d, host, len, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        cudaFree(d);
+        return cuda_fail(ctx, e, "weight upload");
+    }
+    ctx->regions.push_back({h, len, d});
+    *dev = d;
+    return LQ_OK;
+}
+
+int resolve_matrix(lq_ctx* ctx, const lq_matrix* m, lq_matrix* out) {
+    *out = *m;
+    out->fmt = m->fmt & 0xff;
+    if (m->fmt & LQ_MAT_DEVICE) return LQ_OK;  // already device pointers
+    const uint8_t* d = nullptr;
+    int rc = resolve(ctx, m->data, m->data_len, &d);
+    if (rc) return rc;
+    out->data = d;
+    if (m->scales && m->scales_len) {
+        rc = resolve(ctx, m->scales, m->scales_len, &d);
+        if (rc) return rc;
+        out->scales = d;
+    }
+    return LQ_OK;
+}
+
+int check_device_err(lq_ctx* ctx) {
+    int h = 0;
+    CK(cudaMemcpyAsync(&h, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    CK(cudaStreamSynchronize(ctx->stream));
+    if (h == DEV_OK) return LQ_OK;
+    CK(cudaMemsetAsync(ctx->d_err, 0, sizeof(int), ctx->stream));
+    if (h == DEV_ERR_NAN_SCORE) return fail(ctx, LQ_ERR_NAN_SCORE, "NaN gate score or non-finite activation");
+    if (h == DEV_ERR_TMA_TIMEOUT) return fail(ctx, LQ_ERR_TIMEOUT, "a bounded device-side wait ran out");
+    return fail(ctx, LQ_ERR_CUDA, "device-side internal error");
+}
+
+XPrep xprep_of(const TokenWs& w) { return XPrep{w.xn, w.xa, w.xb, w.bscale, w.bsum, w.babs}; }
+
+// Rounding-count constant of the score error bound: the reference's sum_x-form row has at
+// most 43 + nsb roundings on any term's path (product, 32-term chain, scale multiply,
+// subtract, 8 group adds, nsb super-block adds) and the fast path at most 64.
+float bound_c1(int hidden) {
+    const double u = std::ldexp(1.0, -24);
+    const double n = 43.0 + hidden / 256 + 64.0;
+    return (float)(n * u / (1.0 - n * u) * 1.01);
+}
+
+// Enqueue the walk of one prepared token.
+int enqueue_walk_token(lq_ctx* ctx, const lq_matrix& gate, const lq_matrix& up, const lq_matrix& down, size_t t,
+                       size_t top_k, const float* residual, float* out) {
+    if (gate.fmt != LQ_FMT_Q4_K || up.fmt != LQ_FMT_Q4_K || down.fmt != LQ_FMT_Q4_K)
+        return fail(ctx, LQ_REFUSED_UNSUPPORTED, "walk: format not implemented");
+    TokenWs& w = ctx->tok[t];
+    const int N = (int)gate.rows, H = (int)gate.cols;
+    const Q4kMat g{(const uint8_t*)gate.data, N, H}, u{(const uint8_t*)up.data, N, H},
+        d{(const uint8_t*)down.data, N, H};
+    const XPrep xp = xprep_of(w);
+    const int k = (int)std::min<size_t>(top_k, (size_t)N);
+    CK(launch_scan_q4k(g, xp, w.scores, w.bounds, bound_c1(H), ctx->d_err, ctx->sm_count, ctx->stream));
+    CK(launch_select(w.scores, w.bounds, N, k, w, ctx->d_err, ctx->stream));
+    ctx->launches += 2;
+    if (k < N) {
+        CK(launch_rescore_q4k(g, w.xn, w.band_idx, &w.sel->n_band, 0, w.band_exact, w, k, 1, ctx->d_err,
+                              ctx->sm_count, ctx->stream));
+        ctx->launches += 1;
+    }
+    CK(launch_gather_q4k(u, d, xp, w.hit_idx, w.hit_score, &w.sel->n_sel, k, ctx->partials, ctx->gather_grid,
+                         ctx->d_err, ctx->stream));
+    CK(launch_finish(ctx->partials, ctx->gather_grid, H, residual, out, ctx->stream));
+    ctx->launches += 2;
+    return LQ_OK;
+}
+
+size_t effective_k(size_t top_k, size_t n, uint32_t flags) {
+    // K >= 80% of the features runs dense (all features) unless the walk is forced
+    // (crates/larql-inference/src/vindex/walk_ffn/helpers.rs:18-30, thresholds.rs:29-31).
+    if (!(flags & LQ_WALK_FORCE_SPARSE) && top_k >= (n * 4) / 5) return n;
+    return std::min(top_k, n);
+}
+
+int dev_walk(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const lq_matrix* down, const float* x,
+             size_t batch, size_t top_k, uint32_t flags, float* out, uint32_t* idx_out, uint32_t* count_out) {
+    const size_t N = (size_t)gate->rows, H = (size_t)gate->cols;
+    if (up->rows != gate->rows || down->rows != gate->rows || up->cols != gate->cols || down->cols != gate->cols)
+        return fail(ctx, LQ_REFUSED_SHAPE, "walk: gate/up/down shapes differ");
+    if (batch == 0 || H == 0) return LQ_OK;
+    if (H > 16384) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "walk: hidden > 16384");
+    int rc = ensure_ws(ctx, batch, H, N);
+    if (rc) return rc;
+    const size_t k = effective_k(top_k, N, flags);
+    TokenWs& w0 = ctx->tok[0];
+    // Token workspaces are laid out with a constant byte stride; prep takes it in 4-byte words.
+    const size_t tok_stride_f =
+        batch > 1 ? (size_t)((uint8_t*)ctx->tok[1].xn - (uint8_t*)ctx->tok[0].xn) / sizeof(float) : 0;
+    launch_prep(x, (int)batch, (int)H, (flags & LQ_WALK_RMSNORM) ? 1 : 0, 1e-6, w0.xn, w0.xa, w0.xb, w0.bscale,
+                w0.bsum, w0.babs, tok_stride_f, ctx->d_err, ctx->stream);
+    CK(cudaGetLastError());
+    ctx->launches += 1;
+    for (size_t t = 0; t < batch; ++t) {
+        if (N == 0) {
+            if (flags & LQ_WALK_RESIDUAL)
+                CK(cudaMemcpyAsync(out + t * H, x + t * H, H * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+            else
+                CK(cudaMemsetAsync(out + t * H, 0, H * 4, ctx->stream));
+            continue;
+        }
+        rc = enqueue_walk_token(ctx, *gate, *up, *down, t, k, (flags & LQ_WALK_RESIDUAL) ? x + t * H : nullptr,
+                                out + t * H);
+        if (rc) return rc;
+        if (idx_out)
+            CK(cudaMemcpyAsync(idx_out + t * k, ctx->tok[t].hit_idx, k * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+        if (count_out)
+            CK(cudaMemcpyAsync(count_out + t, &ctx->tok[t].sel->n_sel, 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    }
+    return LQ_OK;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------ context ----
+extern "C" {
+
+int lq_create(int device, lq_ctx** out) {
+    if (!out) return LQ_ERR_ARGUMENT;
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0 || device < 0 || device >= n) return LQ_ERR_CUDA;
+    if (cudaSetDevice(device) != cudaSuccess) return LQ_ERR_CUDA;
+    cudaDeviceProp p;
+    if (cudaGetDeviceProperties(&p, device) != cudaSuccess) return LQ_ERR_CUDA;
+    if (p.major < 10) return LQ_REFUSED_UNSUPPORTED;  // kernels are built for sm_100a only
+    lq_ctx* ctx = new lq_ctx();
+    ctx->device = device;
+    ctx->sm_count = p.multiProcessorCount;
+    char buf[512];
+    snprintf(buf, sizeof buf, "cuda:%d %s sm_%d%d %d SMs %.0f GB", device, p.name, p.major, p.minor,
+             p.multiProcessorCount, (double)p.totalGlobalMem / 1e9);
+    ctx->info = buf;
+    if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaMalloc(&ctx->d_err, 256) != cudaSuccess || cudaMemset(ctx->d_err, 0, 256) != cudaSuccess) {
+        delete ctx;
+        return LQ_ERR_CUDA;
+    }
+    *out = ctx;
+    return LQ_OK;
+}
+
+void lq_destroy(lq_ctx* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (auto& r : ctx->regions) cudaFree(r.dev);
+    cudaFree(ctx->ws_raw);
+    cudaFree(ctx->stage);
+    cudaFree(ctx->sort_buf);
+    cudaFree(ctx->d_err);
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+const char* lq_last_error(lq_ctx* ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
+
+int lq_device_info(lq_ctx* ctx, char* buf, size_t cap) {
+    if (!ctx || !buf || cap == 0) return LQ_ERR_ARGUMENT;
+    snprintf(buf, cap, "%s", ctx->info.c_str());
+    return LQ_OK;
+}
+
+int lq_supports_quant(lq_ctx* ctx, int fmt) {
+    (void)ctx;
+    return fmt == LQ_FMT_Q4_K ? 1 : 0;
+}
+
+int lq_synchronize(lq_ctx* ctx) {
+    if (!ctx) return LQ_ERR_ARGUMENT;
+    CK(cudaStreamSynchronize(ctx->stream));
+    return check_device_err(ctx);
+}
+
+void* lq_stream(lq_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+uint64_t lq_launch_count(lq_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int lq_register_weight_region(lq_ctx* ctx, const void* host, size_t len) {
+    if (!ctx || (!host && len)) return LQ_ERR_ARGUMENT;
+    if (ctx->sealed) return fail(ctx, LQ_ERR_ARGUMENT, "regions are sealed");
+    const uint8_t* d;
+    return resolve(ctx, host, len, &d);
+}
+int lq_seal_weight_regions(lq_ctx* ctx) {
+    if (!ctx) return LQ_ERR_ARGUMENT;
+    ctx->sealed = true;
+    return LQ_OK;
+}
+int lq_drop_weight_regions(lq_ctx* ctx) {
+    if (!ctx) return LQ_ERR_ARGUMENT;
+    CK(cudaStreamSynchronize(ctx->stream));
+    for (auto& r : ctx->regions) cudaFree(r.dev);
+    ctx->regions.clear();
+    ctx->sealed = false;
+    return LQ_OK;
+}
+const void* lq_device_ptr(lq_ctx* ctx, const void* host, size_t len) {
+    if (!ctx) return nullptr;
+    const uint8_t* h = (const uint8_t*)host;
+    for (auto& r : ctx->regions)
+        if (h >= r.host && h + len <= r.host + r.len) return r.dev + (h - r.host);
+    return nullptr;
+}
+
+// ------------------------------------------------------------ matvec / matmul ----
+int lq_dev_q4k_matvec(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t num_rows, size_t hidden,
+                      float* out) {
+    if (!ctx) return LQ_ERR_ARGUMENT;
+    if (hidden % 256 != 0 || w_len < num_rows * (hidden / 256) * 144)
+        return fail(ctx, LQ_REFUSED_SHAPE, "q4k_matvec: geometry");
+    if (num_rows == 0) return LQ_OK;
+    if (hidden == 0) {
+        CK(cudaMemsetAsync(out, 0, num_rows * 4, ctx->stream));
+        return LQ_OK;
+    }
+    if (hidden > 16384) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "q4k_matvec: hidden > 16384");
+    if (((uintptr_t)w & 15) != 0) return fail(ctx, LQ_ERR_ARGUMENT, "q4k_matvec: weights not 16-byte aligned");
+    int rc = ensure_ws(ctx, 1, hidden, 32);
+    if (rc) return rc;
+    TokenWs& t = ctx->tok[0];
+    launch_prep(x, 1, (int)hidden, 0, 0.0, t.xn, t.xa, t.xb, t.bscale, t.bsum, t.babs, 0, nullptr, ctx->stream);
+    CK(cudaGetLastError());
+    const Q4kMat m{w, (int)num_rows, (int)hidden};
+    CK(launch_scan_q4k(m, xprep_of(t), out, nullptr, 0.0f, ctx->d_err, ctx->sm_count, ctx->stream));
+    ctx->launches += 2;
+    return LQ_OK;
+}
+
+static int q4k_host_common(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len,
+                           size_t num_rows, size_t hidden, size_t seq, float* out, size_t out_len, int exact) {
+    if (!ctx) return LQ_ERR_ARGUMENT;
+    const size_t needed = (hidden / 256) * 144 * num_rows;
+    if (!(out_len == num_rows * seq && x_len == hidden * seq && hidden % 256 == 0 && w_len >= needed))
+        return fail(ctx, LQ_REFUSED_SHAPE, "q4k matvec/matmul: shape (KernelShapeError)");
+    if (num_rows == 0 || seq == 0) return LQ_OK;
+    if (hidden == 0) {
+        memset(out, 0, out_len * 4);
+        return LQ_OK;
+    }
+    if (hidden > 16384) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "q4k: hidden > 16384");
+    const uint8_t* dw;
+    int rc = resolve(ctx, w, needed, &dw);
+    if (rc) return rc;
+    rc = ensure_stage(ctx, (x_len + out_len) * 4 + 512);
+    if (rc) return rc;
+    float* dx = (float*)ctx->stage;
+    float* dout = (float*)(ctx->stage + a256(x_len * 4));
+    CK(cudaMemcpyAsync(dx, x, x_len * 4, cudaMemcpyHostToDevice, ctx->stream));
+    for (size_t s = 0; s < seq; ++s) {
+        if (exact) {
+            rc = ensure_ws(ctx, 1, hidden, 32);
+            if (rc) return rc;
+            const Q4kMat m{dw, (int)num_rows, (int)hidden};
+            CK(launch_rescore_q4k(m, dx + s * hidden, nullptr, nullptr, (int)num_rows, dout + s * num_rows,
+                                  ctx->tok[0], 0, 0, ctx->d_err, ctx->sm_count, ctx->stream));
+            ctx->launches += 1;
+        } else {
+            rc = lq_dev_q4k_matvec(ctx, dw, needed, dx + s * hidden, num_rows, hidden, dout + s * num_rows);
+            if (rc) return rc;
+        }
+    }
+    CK(cudaMemcpyAsync(out, dout, out_len * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return lq_synchronize(ctx);
+}
+
+int lq_q4k_matvec(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t num_rows,
+                  size_t hidden, float* out, size_t out_len) {
+    return q4k_host_common(ctx, w, w_len, x, x_len, num_rows, hidden, 1, out, out_len, 0);
+}
+int lq_q4k_matvec_exact(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t num_rows,
+                        size_t hidden, float* out, size_t out_len) {
+    return q4k_host_common(ctx, w, w_len, x, x_len, num_rows, hidden, 1, out, out_len, 1);
+}
+int lq_q4k_matmul(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t num_rows,
+                  size_t hidden, size_t seq_len, float* out, size_t out_len) {
+    return q4k_host_common(ctx, w, w_len, x, x_len, num_rows, hidden, seq_len, out, out_len, 0);
+}
+
+int lq_topk_abs(lq_ctx* ctx, const float* scores, size_t n, size_t top_k, uint32_t* idx_out, float* val_out,
+                size_t* count) {
+    if (!ctx || !count) return LQ_ERR_ARGUMENT;
+    *count = 0;
+    if (n == 0 || top_k == 0) return LQ_OK;
+    if (n > (1u << 30)) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "topk: n too large");
+    const size_t k = std::min(n, top_k);
+    int rc = ensure_ws(ctx, 1, 256, n);
+    if (rc) return rc;
+    rc = ensure_sort(ctx, k);
+    if (rc) return rc;
+    rc = ensure_stage(ctx, n * 4 + k * 8 + 1024);
+    if (rc) return rc;
+    float* ds = (float*)ctx->stage;
+    uint32_t* di = (uint32_t*)(ctx->stage + a256(n * 4));
+    float* dv = (float*)(ctx->stage + a256(n * 4) + a256(k * 4));
+    CK(cudaMemcpyAsync(ds, scores, n * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CK(launch_topk_abs_sorted(ds, (int)n, (int)k, ctx->tok[0], di, dv, nullptr, ctx->sort_buf, ctx->d_err,
+                              ctx->stream));
+    ctx->launches += 3;
+    CK(cudaMemcpyAsync(idx_out, di, k * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CK(cudaMemcpyAsync(val_out, dv, k * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    rc = lq_synchronize(ctx);
+    if (rc) return rc;
+    *count = k;
+    return LQ_OK;
+}
+
+int lq_rms_norm(lq_ctx* ctx, const float* x, size_t rows, size_t cols, double eps, float* out) {
+    if (!ctx) return LQ_ERR_ARGUMENT;
+    if (rows == 0 || cols == 0) return LQ_OK;
+    if (cols % 32 != 0 || cols > 16384) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "rms_norm: cols % 32 != 0");
+    int rc = ensure_ws(ctx, 1, cols, 32);
+    if (rc) return rc;
+    rc = ensure_stage(ctx, cols * 4);
+    if (rc) return rc;
+    TokenWs& t = ctx->tok[0];
+    for (size_t r = 0; r < rows; ++r) {
+        CK(cudaMemcpyAsync(ctx->stage, x + r * cols, cols * 4, cudaMemcpyHostToDevice, ctx->stream));
+        launch_prep((const float*)ctx->stage, 1, (int)cols, 1, eps, t.xn, t.xa, t.xb, t.bscale, t.bsum, t.babs, 0,
+                    nullptr, ctx->stream);
+        CK(cudaGetLastError());
+        ctx->launches += 1;
+        CK(cudaMemcpyAsync(out + r * cols, t.xn, cols * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    return lq_synchronize(ctx);
+}
+
+int lq_dequantize(lq_ctx* ctx, const lq_matrix* m, float* out, size_t out_len) {
+    if (!ctx) return LQ_ERR_ARGUMENT;
+    int rc = check_matrix(ctx, m, "dequantize");
+    if (rc) return rc;
+    const size_t n = (size_t)m->rows * (size_t)m->cols;
+    if (out_len != n) return fail(ctx, LQ_REFUSED_SHAPE, "dequantize: out_len != rows*cols");
+    if (n == 0) return LQ_OK;
+    lq_matrix dm;
+    rc = resolve_matrix(ctx, m, &dm);
+    if (rc) return rc;
+    rc = ensure_stage(ctx, n * 4);
+    if (rc) return rc;
+    CK(launch_dequantize(dm, (float*)ctx->stage, ctx->stream));
+    ctx->launches += 1;
+    CK(cudaMemcpyAsync(out, ctx->stage, n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return lq_synchronize(ctx);
+}
+
+// ------------------------------------------------------------------ the walk ----
+int lq_dev_walk_ffn(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const lq_matrix* down_fm,
+                    const float* x, size_t batch, size_t top_k, uint32_t flags, float* out, uint32_t* idx_out,
+                    uint32_t* count_out) {
+    if (!ctx) return LQ_ERR_ARGUMENT;
+    int rc;
+    if ((rc = check_matrix(ctx, gate, "gate")) || (rc = check_matrix(ctx, up, "up")) ||
+        (rc = check_matrix(ctx, down_fm, "down")))
+        return rc;
+    lq_matrix g = *gate, u = *up, d = *down_fm;
+    g.fmt &= 0xff;
+    u.fmt &= 0xff;
+    d.fmt &= 0xff;
+    return dev_walk(ctx, &g, &u, &d, x, batch, top_k, flags, out, idx_out, count_out);
+}
+
+int lq_walk_ffn(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const lq_matrix* down_fm, const float* x,
+                size_t batch, size_t top_k, uint32_t flags, float* out, uint32_t* idx_out, uint32_t* count_out) {
+    if (!ctx) return LQ_ERR_ARGUMENT;
+    int rc;
+    if ((rc = check_matrix(ctx, gate, "gate")) || (rc = check_matrix(ctx, up, "up")) ||
+        (rc = check_matrix(ctx, down_fm, "down")))
+        return rc;
+    lq_matrix g, u, d;
+    if ((rc = resolve_matrix(ctx, gate, &g)) || (rc = resolve_matrix(ctx, up, &u)) ||
+        (rc = resolve_matrix(ctx, down_fm, &d)))
+        return rc;
+    const size_t H = (size_t)gate->cols, N = (size_t)gate->rows;
+    const size_t k = effective_k(top_k, N, flags);
+    const size_t xb = a256(batch * H * 4), ib = a256(batch * std::max<size_t>(k, 1) * 4), cb = a256(batch * 4);
+    rc = ensure_stage(ctx, 2 * xb + ib + cb);
+    if (rc) return rc;
+    float* dx = (float*)ctx->stage;
+    float* dout = (float*)(ctx->stage + xb);
+    uint32_t* didx = (uint32_t*)(ctx->stage + 2 * xb);
+    uint32_t* dcnt = (uint32_t*)(ctx->stage + 2 * xb + ib);
+    if (batch * H) CK(cudaMemcpyAsync(dx, x, batch * H * 4, cudaMemcpyHostToDevice, ctx->stream));
+    rc = dev_walk(ctx, &g, &u, &d, dx, batch, top_k, flags, dout, idx_out ? didx : nullptr,
+                  count_out ? dcnt : nullptr);
+    if (rc) return rc;
+    if (batch * H) CK(cudaMemcpyAsync(out, dout, batch * H * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (idx_out && batch * k) CK(cudaMemcpyAsync(idx_out, didx, batch * k * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (count_out && batch) {
+        if (N == 0) memset(count_out, 0, batch * 4);
+        else CK(cudaMemcpyAsync(count_out, dcnt, batch * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    rc = lq_synchronize(ctx);
+    if (rc) return rc;
+    if (N && batch && H) {
+        SelHeader h;
+        CK(cudaMemcpy(&h, ctx->tok[0].sel, sizeof h, cudaMemcpyDeviceToHost));
+        ctx->stats = lq_walk_stats{h.n_in, h.n_band, h.n_sel, h.need, h.tau, h.bound};
+    }
+    return LQ_OK;
+}
+
+int lq_last_walk_stats(lq_ctx* ctx, lq_walk_stats* out) {
+    if (!ctx || !out) return LQ_ERR_ARGUMENT;
+    *out = ctx->stats;
+    return LQ_OK;
+}
+
+int lq_dev_quantize_q4k(lq_ctx* ctx, const float* src, size_t n_elems, uint8_t* dst) {
+    if (!ctx) return LQ_ERR_ARGUMENT;
+    if (n_elems % 256 != 0) return fail(ctx, LQ_REFUSED_SHAPE, "quantize_q4k: length % 256 != 0");
+    if (((uintptr_t)dst & 15) != 0) return fail(ctx, LQ_ERR_ARGUMENT, "quantize_q4k: dst not 16-byte aligned");
+    CK(launch_quantize_q4k(src, n_elems, dst, ctx->stream));
+    ctx->launches += 1;
+    return LQ_OK;
+}
+
+int lq_profile_walk(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const lq_matrix* down_fm,
+                    const float* x, size_t top_k, uint32_t flags, float* out, float* ms) {
+    if (!ctx || !ms) return LQ_ERR_ARGUMENT;
+    int rc;
+    if ((rc = check_matrix(ctx, gate, "gate")) || (rc = check_matrix(ctx, up, "up")) ||
+        (rc = check_matrix(ctx, down_fm, "down")))
+        return rc;
+    if ((gate->fmt & 0xff) != LQ_FMT_Q4_K) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "profile: Q4_K only");
+    const int N = (int)gate->rows, H = (int)gate->cols;
+    if (N == 0 || H == 0) return fail(ctx, LQ_REFUSED_SHAPE, "profile: empty layer");
+    rc = ensure_ws(ctx, 1, H, N);
+    if (rc) return rc;
+    cudaEvent_t ev[7];
+    for (auto& e : ev) CK(cudaEventCreate(&e));
+    TokenWs& w = ctx->tok[0];
+    const Q4kMat g{(const uint8_t*)gate->data, N, H}, u{(const uint8_t*)up->data, N, H},
+        d{(const uint8_t*)down_fm->data, N, H};
+    const XPrep xp = xprep_of(w);
+    const int k = (int)effective_k(top_k, (size_t)N, flags);
+    cudaStream_t st = ctx->stream;
+    CK(cudaEventRecord(ev[0], st));
+    launch_prep(x, 1, H, (flags & LQ_WALK_RMSNORM) ? 1 : 0, 1e-6, w.xn, w.xa, w.xb, w.bscale, w.bsum, w.babs, 0,
+                ctx->d_err, st);
+    CK(cudaEventRecord(ev[1], st));
+    CK(launch_scan_q4k(g, xp, w.scores, w.bounds, bound_c1(H), ctx->d_err, ctx->sm_count, st));
+    CK(cudaEventRecord(ev[2], st));
+    CK(launch_select(w.scores, w.bounds, N, k, w, ctx->d_err, st));
+    CK(cudaEventRecord(ev[3], st));
+    if (k < N)
+        CK(launch_rescore_q4k(g, w.xn, w.band_idx, &w.sel->n_band, 0, w.band_exact, w, k, 1, ctx->d_err,
+                              ctx->sm_count, st));
+    CK(cudaEventRecord(ev[4], st));
+    CK(launch_gather_q4k(u, d, xp, w.hit_idx, w.hit_score, &w.sel->n_sel, k, ctx->partials, ctx->gather_grid,
+                         ctx->d_err, st));
+    CK(cudaEventRecord(ev[5], st));
+    CK(launch_finish(ctx->partials, ctx->gather_grid, H, (flags & LQ_WALK_RESIDUAL) ? x : nullptr, out, st));
+    CK(cudaEventRecord(ev[6], st));
+    ctx->launches += 6;
+    rc = lq_synchronize(ctx);
+    for (int i = 0; i < 6; ++i) {
+        float t = 0.0f;
+        cudaEventElapsedTime(&t, ev[i], ev[i + 1]);
+        ms[i] = t;
+    }
+    for (auto& e : ev) cudaEventDestroy(e);
+    return rc;
+}
+
+// ----------------------------------------------------------------- layer stack ----
+static int stack_enqueue(lq_ctx* ctx, lq_stack* s) {
+    const size_t L = s->gates.size();
+    const float* cur = s->h_in;
+    for (size_t l = 0; l < L; ++l) {
+        float* nxt = (l + 1 == L) ? s->h_out : s->h_buf[l & 1];
+        int rc = dev_walk(ctx, &s->gates[l], &s->ups[l], &s->downs[l], cur, s->batch, s->top_k, s->flags, nxt,
+                          nullptr, nullptr);
+        if (rc) return rc;
+        cur = nxt;
+    }
+    return LQ_OK;
+}
+
+int lq_stack_create(lq_ctx* ctx, const lq_matrix* gates, const lq_matrix* ups, const lq_matrix* downs_fm,
+                    size_t n_layers, size_t batch, size_t top_k, uint32_t flags, lq_stack** out) {
+    if (!ctx || !out || !n_layers || !batch) return LQ_ERR_ARGUMENT;
+    *out = nullptr;
+    int rc;
+    for (size_t l = 0; l < n_layers; ++l) {
+        if ((rc = check_matrix(ctx, &gates[l], "gate")) || (rc = check_matrix(ctx, &ups[l], "up")) ||
+            (rc = check_matrix(ctx, &downs_fm[l], "down")))
+            return rc;
+        if (gates[l].cols != gates[0].cols) return fail(ctx, LQ_REFUSED_SHAPE, "stack: hidden differs per layer");
+    }
+    lq_stack* s = new lq_stack();
+    s->gates.assign(gates, gates + n_layers);
+    s->ups.assign(ups, ups + n_layers);
+    s->downs.assign(downs_fm, downs_fm + n_layers);
+    for (size_t l = 0; l < n_layers; ++l) {
+        s->gates[l].fmt &= 0xff;
+        s->ups[l].fmt &= 0xff;
+        s->downs[l].fmt &= 0xff;
+    }
+    s->batch = batch;
+    s->top_k = top_k;
+    s->flags = flags | LQ_WALK_RMSNORM | LQ_WALK_RESIDUAL;
+    s->hidden = (int)gates[0].cols;
+    const size_t bytes = a256(batch * s->hidden * 4);
+    uint8_t* raw = nullptr;
+    cudaError_t e = cudaMalloc(&raw, 4 * bytes);
+    if (e != cudaSuccess) {
+        delete s;
+        return cuda_fail(ctx, e, "stack buffers");
+    }
+    s->h_in = (float*)raw;
+    s->h_out = (float*)(raw + bytes);
+    s->h_buf[0] = (float*)(raw + 2 * bytes);
+    s->h_buf[1] = (float*)(raw + 3 * bytes);
+    // One eager pass on a harmless input grows the workspace and sets kernel attributes,
+    // neither of which may happen inside a capture.
+    cudaMemsetAsync(s->h_in, 0x3f, bytes, ctx->stream);
+    rc = stack_enqueue(ctx, s);
+    if (!rc) rc = lq_synchronize(ctx);
+    if (!rc) {
+        e = cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal);
+        if (e == cudaSuccess) {
+            rc = stack_enqueue(ctx, s);
+            cudaError_t e2 = cudaStreamEndCapture(ctx->stream, &s->graph);
+            if (!rc && e2 != cudaSuccess) rc = cuda_fail(ctx, e2, "end capture");
+            if (!rc) {
+                e2 = cudaGraphInstantiate(&s->exec, s->graph, 0);
+                if (e2 != cudaSuccess) rc = cuda_fail(ctx, e2, "graph instantiate");
+            }
+        } else
+            rc = cuda_fail(ctx, e, "begin capture");
+    }
+    if (rc) {
+        lq_stack_destroy(ctx, s);
+        return rc;
+    }
+    *out = s;
+    return LQ_OK;
+}
+
+int lq_stack_run(lq_ctx* ctx, lq_stack* s, const float* h_in, float* h_out) {
+    if (!ctx || !s || !s->exec) return LQ_ERR_ARGUMENT;
+    const size_t bytes = s->batch * s->hidden * 4;
+    CK(cudaMemcpyAsync(s->h_in, h_in, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    CK(cudaGraphLaunch(s->exec, ctx->stream));
+    CK(cudaMemcpyAsync(h_out, s->h_out, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    return LQ_OK;
+}
+
+void lq_stack_destroy(lq_ctx* ctx, lq_stack* s) {
+    if (!s) return;
+    if (ctx) cudaStreamSynchronize(ctx->stream);
+    if (s->exec) cudaGraphExecDestroy(s->exec);
+    if (s->graph) cudaGraphDestroy(s->graph);
+    if (s->h_in) cudaFree(s->h_in);
+    delete s;
+}
+
+}  // extern "C"

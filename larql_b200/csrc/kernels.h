@@ -1,0 +1,78 @@
+// Internal launch interface between the C-ABI layer and the kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace lq {
+
+// Per-token selection record written by the select kernels.
+struct SelHeader {
+    int n_in;      // rows certainly in the top-K (fast |score| above the band)
+    int n_band;    // rows whose membership needs the exact reference score
+    int n_sel;     // final number of hits (min(K, N))
+    int need;      // K - n_in: how many band rows make it
+    float tau;     // K-th largest fast |score|
+    float bound;   // B = max row error bound; band is |s| in [tau-2B, tau+2B]
+    int done_ctr;  // rescore CTAs finished (last one runs the final pick)
+    int pad;
+};
+
+// Per-token workspace views (device pointers).
+struct TokenWs {
+    float* xn;
+    uint32_t* xa;
+    uint32_t* xb;
+    float* bscale;
+    float* bsum;
+    float* babs;
+    float* scores;      // [N] fast gate scores
+    float* bounds;      // [N] per-row error bound of the fast score vs the reference score
+    SelHeader* sel;
+    uint32_t* hit_idx;  // [N] final hits: certain rows (ascending), then picked band rows (ascending)
+    float* hit_score;   // [N] gate score per hit (exact for band rows)
+    uint32_t* band_idx; // [N]
+    float* band_exact;  // [N] exact reference-order score per band row
+};
+
+struct Q4kMat {
+    const uint8_t* w;  // [rows][cols/256*144]
+    int rows;
+    int cols;
+};
+
+// prep.cu
+void launch_prep(const float* x_in, int batch, int hidden, int apply_norm, double eps, float* xn, uint32_t* xa,
+                 uint32_t* xb, float* bscale, float* bsum, float* babs, size_t token_stride_f, int* err,
+                 cudaStream_t st);
+
+// scan_q4k.cu
+int scan_q4k_smem_bytes(int hidden);
+// Fast scores (+ per-row bounds when bounds != nullptr) of every row for one token.
+cudaError_t launch_scan_q4k(const Q4kMat& m, const XPrep& xp, float* scores, float* bounds, float c1, int* err,
+                            int sm_count, cudaStream_t st);
+// Exact reference-order (sum_x form) scores for the rows listed in rows_idx[0..*n_rows), or for
+// all rows when rows_idx == nullptr.  When sel != nullptr the last CTA to finish runs the final pick.
+cudaError_t launch_rescore_q4k(const Q4kMat& m, const float* xn, const uint32_t* rows_idx, const int* n_rows_dev,
+                               int n_rows_host, float* out, TokenWs ws, int top_k, int run_final, int* err,
+                               int sm_count, cudaStream_t st);
+
+// select.cu
+cudaError_t launch_select(const float* scores, const float* bounds, int n, int top_k, TokenWs ws, int* err,
+                          cudaStream_t st);
+// Stand-alone exact top-K by |score| (ties -> lower index), sorted (|v| desc, idx asc).
+cudaError_t launch_topk_abs_sorted(const float* scores, int n, int top_k, uint32_t* idx_out, float* val_out,
+                                   int* count_out, void* scratch, int* err, cudaStream_t st);
+
+// gather_q4k.cu
+int gather_q4k_grid(int sm_count);
+cudaError_t launch_gather_q4k(const Q4kMat& up, const Q4kMat& down, const XPrep& xp, const uint32_t* hit_idx,
+                              const float* hit_score, const int* n_hits_dev, int max_hits, float* partials,
+                              int grid, int* err, cudaStream_t st);
+// out[h] = (residual ? residual[h] : 0) + sum_c partials[c][h]   (fixed order)
+cudaError_t launch_finish(const float* partials, int n_partials, int hidden, const float* residual, float* out,
+                          cudaStream_t st);
+
+}  // namespace lq

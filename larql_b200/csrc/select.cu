@@ -1,0 +1,186 @@
+// Selection kernels: threshold + band classification of the fast gate scores, the
+// final pick kernel, and the stand-alone sorted top-K by |score|.
+#include "select.cuh"
+
+namespace lq {
+
+namespace {
+
+constexpr int SEL_T = 1024;
+constexpr int SEL_SMEM_VALS_MAX = 40 * 1024;  // floats cached in shared memory (160 KB)
+
+// Classifies every row of one token against the K-th largest fast |score| tau and
+// the error bound B = max_r bounds[r]:
+//   |s| >  tau + 2B  -> certainly in the reference's top-K        (hit list, ascending)
+//   |s| >= tau - 2B  -> membership depends on the reference bits  (band list, ascending)
+//   else             -> certainly out.
+// Proof sketch: |s_ref - s| <= B for every row, so a row above tau + 2B beats, in
+// reference scores, every row at or below tau (fewer than K rows are above tau); a
+// row below tau - 2B is beaten by the >= K rows at or above tau.
+__global__ void __launch_bounds__(SEL_T, 1)
+select_kernel(const float* __restrict__ scores, const float* __restrict__ bounds, int n, int top_k, TokenWs ws,
+              int* err, int use_smem) {
+    extern __shared__ __align__(16) float s_vals[];
+    __shared__ SelectSmem<SEL_T> sm;
+    __shared__ float s_red[SEL_T / 32];
+    __shared__ int s_nan;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) s_nan = 0;
+    __syncthreads();
+
+    float bmax = 0.0f;
+    bool nan = false;
+    for (int i = tid; i < n; i += SEL_T) {
+        const float v = scores[i];
+        nan |= (v != v);
+        if (use_smem) s_vals[i] = v;
+        if (bounds) bmax = fmaxf(bmax, bounds[i]);
+    }
+    for (int o = 16; o > 0; o >>= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
+    if (lane == 0) s_red[warp] = bmax;
+    if (nan) s_nan = 1;
+    __syncthreads();
+    if (warp == 0) {
+        float t = s_red[lane];
+        for (int o = 16; o > 0; o >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
+        if (lane == 0) sm.fbcast[0] = t;
+    }
+    __syncthreads();
+    const float B = sm.fbcast[0];
+    if (s_nan) set_err(err, DEV_ERR_NAN_SCORE);
+    const float* vals = use_smem ? s_vals : scores;
+
+    if (top_k <= 0 || n <= 0) {
+        if (tid == 0) *ws.sel = SelHeader{0, 0, 0, 0, 0.0f, B, 0, 0};
+        return;
+    }
+    if (top_k >= n) {
+        for (int i = tid; i < n; i += SEL_T) {
+            ws.hit_idx[i] = (uint32_t)i;
+            ws.hit_score[i] = vals[i];
+        }
+        if (tid == 0) *ws.sel = SelHeader{n, 0, n, 0, 0.0f, B, 0, 0};
+        return;
+    }
+
+    uint32_t tau_key;
+    int cnt_gt, need_eq;
+    block_kth_largest<SEL_T>(vals, n, top_k, sm, tau_key, cnt_gt, need_eq);
+    const float tau = __uint_as_float(tau_key);
+    const float two_b = __fmul_ru(2.0f, B);
+    const float hi = __fadd_ru(tau, two_b), lo = __fadd_rd(tau, -two_b);
+
+    int na, nb;
+    block_compact2<SEL_T>(
+        n, sm, n,
+        [&](int i) {
+            const float a = fabsf(vals[i]);
+            return a > hi ? 1 : (a >= lo ? 2 : 0);
+        },
+        [&](int pos, int i) {
+            ws.hit_idx[pos] = (uint32_t)i;
+            ws.hit_score[pos] = vals[i];
+        },
+        [&](int pos, int i) {
+            ws.band_idx[pos] = (uint32_t)i;
+            ws.band_exact[pos] = vals[i];  // replaced by the exact score when a re-score runs
+        },
+        na, nb);
+    if (tid == 0) *ws.sel = SelHeader{na, nb, top_k, top_k - na, tau, B, 0, 0};
+}
+
+__global__ void __launch_bounds__(256) final_pick_kernel(TokenWs ws, int* err) {
+    __shared__ SelectSmem<256> sm;
+    final_pick_block<256>(ws, err, sm);
+}
+
+// Sort the hit list by (|v| desc, idx asc) with a bitonic network over 64-bit keys
+// (~|v| bits, row) held in `buf` (shared memory, or global scratch for very large K),
+// n_pad a power of two >= count; writes the sorted rows and their signed scores.
+__global__ void __launch_bounds__(1024) sort_hits_kernel(const uint32_t* hit_idx, const float* hit_val,
+                                                        const SelHeader* sel, const float* scores,
+                                                        unsigned long long* gbuf, int n_pad, int use_smem,
+                                                        uint32_t* idx_out, float* val_out, int* count_out) {
+    extern __shared__ __align__(16) unsigned long long s_buf[];
+    unsigned long long* buf = use_smem ? s_buf : gbuf;
+    const int count = sel->n_sel;
+    const int tid = threadIdx.x;
+    for (int i = tid; i < n_pad; i += 1024) {
+        unsigned long long k = ~0ull;  // pads sort to the end
+        if (i < count) k = ((unsigned long long)(~abs_key(hit_val[i])) << 32) | (unsigned long long)hit_idx[i];
+        buf[i] = k;
+    }
+    __syncthreads();
+    for (int size = 2; size <= n_pad; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int t = tid; t < n_pad / 2; t += 1024) {
+                const int lo = 2 * t - (t & (stride - 1));
+                const int hi = lo + stride;
+                const bool up = ((lo & size) == 0);
+                const unsigned long long a = buf[lo], b = buf[hi];
+                if ((a > b) == up) {
+                    buf[lo] = b;
+                    buf[hi] = a;
+                }
+            }
+            __syncthreads();
+        }
+    }
+    for (int i = tid; i < count; i += 1024) {
+        const uint32_t r = (uint32_t)(buf[i] & 0xffffffffull);
+        idx_out[i] = r;
+        val_out[i] = scores[r];
+    }
+    if (tid == 0 && count_out) *count_out = count;
+}
+
+}  // namespace
+
+cudaError_t launch_select(const float* scores, const float* bounds, int n, int top_k, TokenWs ws, int* err,
+                          cudaStream_t st) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             SEL_SMEM_VALS_MAX * 4);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    const int use_smem = n <= SEL_SMEM_VALS_MAX;
+    const size_t smem = use_smem ? (size_t)((n + 3) / 4 * 4) * sizeof(float) : 0;
+    select_kernel<<<1, SEL_T, smem, st>>>(scores, bounds, n, top_k, ws, err, use_smem);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_final_pick(TokenWs ws, int* err, cudaStream_t st) {
+    final_pick_kernel<<<1, 256, 0, st>>>(ws, err);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_topk_abs_sorted(const float* scores, int n, int top_k, TokenWs ws, uint32_t* idx_out,
+                                   float* val_out, int* count_out, unsigned long long* sort_buf, int* err,
+                                   cudaStream_t st) {
+    cudaError_t e = launch_select(scores, nullptr, n, top_k, ws, err, st);
+    if (e != cudaSuccess) return e;
+    e = launch_final_pick(ws, err, st);
+    if (e != cudaSuccess) return e;
+    const int count = top_k < n ? top_k : n;
+    if (count <= 0) {
+        if (count_out) return cudaMemsetAsync(count_out, 0, sizeof(int), st);
+        return cudaSuccess;
+    }
+    int n_pad = 1;
+    while (n_pad < count) n_pad <<= 1;
+    static bool attr_set = false;
+    if (!attr_set) {
+        e = cudaFuncSetAttribute(sort_hits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 8);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    const int use_smem = n_pad <= 16384;
+    sort_hits_kernel<<<1, 1024, use_smem ? (size_t)n_pad * 8 : 0, st>>>(ws.hit_idx, ws.hit_score, ws.sel, scores,
+                                                                        sort_buf, n_pad, use_smem, idx_out, val_out,
+                                                                        count_out);
+    return cudaGetLastError();
+}
+
+}  // namespace lq
