@@ -139,7 +139,7 @@ def cpu_walk_layers_per_s(mats, wl, batch: int, budget_s: float, threads: int):
             oracle.walk_token_mt(*mats, xs[(n + b) % 4], wl["top_k"], threads)
         n += 1
         dt = time.perf_counter() - t0
-        if dt >= budget_s or n >= 64:
+        if dt >= budget_s:
             return n / dt, n, dt
 
 
@@ -353,8 +353,11 @@ def main():
     ap.add_argument("--workload", default="llama70b_q4k", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU baseline work")
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (small profiling cases)")
     args = ap.parse_args()
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.layers > 0:
+        wl["layers"] = args.layers
     if args.impl == "reference":
         if int(os.environ.get("RANK", 0)) == 0:
             run_reference(args, wl)
