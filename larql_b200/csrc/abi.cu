@@ -134,7 +134,8 @@ int ensure_ws(lq_ctx* ctx, size_t batch, size_t hidden, size_t feat) {
     if (ctx->ws_raw) CK(cudaFree(ctx->ws_raw));
     ctx->ws_raw = nullptr;
     const size_t H = (hidden + 255) / 256 * 256, N = (feat + 31) / 32 * 32;
-    const size_t per_tok = a256(H * 4) + 2 * a256(H) + 3 * a256(H / 32 * 4) + 2 * a256(N * 4) + 256 + 4 * a256(N * 4);
+    const size_t per_tok = a256(H * 4) + 2 * a256(H) + 3 * a256(H / 32 * 4) + a256(N * 4) + a256(LQ_HIST_BINS * 4) + 256 +
+                           4 * a256(N * 4);
     ctx->gather_grid = ctx->sm_count;
     const size_t part_bytes = a256((size_t)ctx->gather_grid * H * 4);
     const size_t total = batch * per_tok + part_bytes;
@@ -156,7 +157,7 @@ int ensure_ws(lq_ctx* ctx, size_t batch, size_t hidden, size_t feat) {
         w.bsum = (float*)take(H / 32 * 4);
         w.babs = (float*)take(H / 32 * 4);
         w.scores = (float*)take(N * 4);
-        w.bounds = (float*)take(N * 4);
+        w.hist = (uint32_t*)take(LQ_HIST_BINS * 4);
         w.sel = (SelHeader*)take(256);
         w.hit_idx = (uint32_t*)take(N * 4);
         w.hit_score = (float*)take(N * 4);
@@ -267,10 +268,19 @@ int enqueue_walk_token(lq_ctx* ctx, const lq_matrix& gate, const lq_matrix& up, 
         d{(const uint8_t*)down.data, N, H};
     const XPrep xp = xprep_of(w);
     const int k = (int)std::min<size_t>(top_k, (size_t)N);
-    CK(launch_scan_q4k(g, xp, w.scores, w.bounds, bound_c1(H), ctx->d_err, ctx->sm_count, ctx->stream));
-    CK(launch_select(w.scores, w.bounds, N, k, w, ctx->d_err, ctx->stream));
+    if (k == 0) {  // empty selection: zero contribution
+        CK(cudaMemsetAsync(w.sel, 0, sizeof(SelHeader), ctx->stream));
+        if (residual) CK(cudaMemcpyAsync(out, residual, (size_t)H * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+        else CK(cudaMemsetAsync(out, 0, (size_t)H * 4, ctx->stream));
+        return LQ_OK;
+    }
+    const bool sparse = k < N;
+    CK(launch_scan_q4k(g, xp, w.scores, sparse ? w.hist : nullptr, &w.sel->bound_bits, bound_c1(H), ctx->d_err,
+                       ctx->sm_count, ctx->stream));
+    if (sparse) CK(launch_classify(w.scores, N, k, w, ctx->d_err, ctx->stream));
+    else CK(launch_select(w.scores, N, k, w, ctx->d_err, ctx->stream));
     ctx->launches += 2;
-    if (k < N) {
+    if (sparse) {
         CK(launch_rescore_q4k(g, w.xn, w.band_idx, &w.sel->n_band, 0, w.band_exact, w, k, 1, ctx->d_err,
                               ctx->sm_count, ctx->stream));
         ctx->launches += 1;
@@ -437,7 +447,7 @@ int lq_dev_q4k_matvec(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* 
     launch_prep(x, 1, (int)hidden, 0, 0.0, t.xn, t.xa, t.xb, t.bscale, t.bsum, t.babs, 0, nullptr, ctx->stream);
     CK(cudaGetLastError());
     const Q4kMat m{w, (int)num_rows, (int)hidden};
-    CK(launch_scan_q4k(m, xprep_of(t), out, nullptr, 0.0f, ctx->d_err, ctx->sm_count, ctx->stream));
+    CK(launch_scan_q4k(m, xprep_of(t), out, nullptr, nullptr, 0.0f, ctx->d_err, ctx->sm_count, ctx->stream));
     ctx->launches += 2;
     return LQ_OK;
 }
@@ -653,9 +663,11 @@ int lq_profile_walk(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, con
     launch_prep(x, 1, H, (flags & LQ_WALK_RMSNORM) ? 1 : 0, 1e-6, w.xn, w.xa, w.xb, w.bscale, w.bsum, w.babs, 0,
                 ctx->d_err, st);
     CK(cudaEventRecord(ev[1], st));
-    CK(launch_scan_q4k(g, xp, w.scores, w.bounds, bound_c1(H), ctx->d_err, ctx->sm_count, st));
+    CK(launch_scan_q4k(g, xp, w.scores, k < N ? w.hist : nullptr, &w.sel->bound_bits, bound_c1(H), ctx->d_err,
+                       ctx->sm_count, st));
     CK(cudaEventRecord(ev[2], st));
-    CK(launch_select(w.scores, w.bounds, N, k, w, ctx->d_err, st));
+    if (k < N) CK(launch_classify(w.scores, N, k, w, ctx->d_err, st));
+    else CK(launch_select(w.scores, N, k, w, ctx->d_err, st));
     CK(cudaEventRecord(ev[3], st));
     if (k < N)
         CK(launch_rescore_q4k(g, w.xn, w.band_idx, &w.sel->n_band, 0, w.band_exact, w, k, 1, ctx->d_err,

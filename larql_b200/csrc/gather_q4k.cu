@@ -211,7 +211,9 @@ gather_q4k_kernel(const uint8_t* __restrict__ Wup, const uint8_t* __restrict__ W
     float* out_s = reinterpret_cast<float*>(buf0);
     for (int p = 0; p < P; ++p) {
         if (active && prow == p) {
-            float* o_lo = out_s + s * 256 + (2 * g) * 32;
+            // 64-float chunks at a stride of 65 floats: neighbouring lanes' chunks start one
+            // bank apart, so the unrolled element loop is conflict-free
+            float* o_lo = out_s + c * 65;
             float* o_hi = o_lo + 32;
 #pragma unroll
             for (int l = 0; l < 32; ++l) {
@@ -228,7 +230,7 @@ gather_q4k_kernel(const uint8_t* __restrict__ Wup, const uint8_t* __restrict__ W
         __syncthreads();
     }
     float* dst = partials + (size_t)blockIdx.x * hidden;
-    for (int i = tid; i < hidden; i += GATHER_THREADS) dst[i] = out_s[i];
+    for (int i = tid; i < hidden; i += GATHER_THREADS) dst[i] = out_s[(i >> 6) * 65 + (i & 63)];
 }
 
 // out[h] = residual[h] + sum_p partials[p][h], p ascending inside each of 8 interleaved

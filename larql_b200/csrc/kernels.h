@@ -17,7 +17,7 @@ struct SelHeader {
     float tau;     // K-th largest fast |score|
     float bound;   // B = max row error bound; band is |s| in [tau-2B, tau+2B]
     int done_ctr;  // rescore CTAs finished (last one runs the final pick)
-    int pad;
+    uint32_t bound_bits;  // running max of the scan's row error bounds (f32 bits; consumed by classify)
 };
 
 // Per-token workspace views (device pointers).
@@ -29,13 +29,17 @@ struct TokenWs {
     float* bsum;
     float* babs;
     float* scores;      // [N] fast gate scores
-    float* bounds;      // [N] per-row error bound of the fast score vs the reference score
+    uint32_t* hist;     // [LQ_HIST_BINS] histogram of fast |score| keys >> LQ_HIST_SHIFT (zero between uses)
     SelHeader* sel;
     uint32_t* hit_idx;  // [N] final hits: certain rows (ascending), then picked band rows (ascending)
     float* hit_score;   // [N] gate score per hit (exact for band rows)
     uint32_t* band_idx; // [N]
     float* band_exact;  // [N] exact reference-order score per band row
 };
+
+// Coarse histogram of |score| bit patterns: 8 exponent + 6 mantissa bits.
+#define LQ_HIST_SHIFT 17
+#define LQ_HIST_BINS 16384
 
 struct Q4kMat {
     const uint8_t* w;  // [rows][cols/256*144]
@@ -50,9 +54,11 @@ void launch_prep(const float* x_in, int batch, int hidden, int apply_norm, doubl
 
 // scan_q4k.cu
 int scan_q4k_smem_bytes(int hidden);
-// Fast scores (+ per-row bounds when bounds != nullptr) of every row for one token.
-cudaError_t launch_scan_q4k(const Q4kMat& m, const XPrep& xp, float* scores, float* bounds, float c1, int* err,
-                            int sm_count, cudaStream_t st);
+// Fast scores of every row for one token.  When hist != nullptr the kernel also adds every
+// row's |score| key to the coarse histogram and folds the largest row error bound into
+// *bound_bits (atomic max on the f32 bit pattern).
+cudaError_t launch_scan_q4k(const Q4kMat& m, const XPrep& xp, float* scores, uint32_t* hist, uint32_t* bound_bits,
+                            float c1, int* err, int sm_count, cudaStream_t st);
 // Exact reference-order (sum_x form) scores for the rows listed in rows_idx[0..*n_rows), or for
 // all rows when rows_idx == nullptr.  When sel != nullptr the last CTA to finish runs the final pick.
 cudaError_t launch_rescore_q4k(const Q4kMat& m, const float* xn, const uint32_t* rows_idx, const int* n_rows_dev,
@@ -60,8 +66,9 @@ cudaError_t launch_rescore_q4k(const Q4kMat& m, const float* xn, const uint32_t*
                                int sm_count, cudaStream_t st);
 
 // select.cu
-cudaError_t launch_select(const float* scores, const float* bounds, int n, int top_k, TokenWs ws, int* err,
-                          cudaStream_t st);
+cudaError_t launch_select(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st);
+// Band classification from the scan's coarse histogram (walk path).
+cudaError_t launch_classify(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st);
 // Stand-alone exact top-K by |score| (ties -> lower index), sorted (|v| desc, idx asc).
 cudaError_t launch_topk_abs_sorted(const float* scores, int n, int top_k, uint32_t* idx_out, float* val_out,
                                    int* count_out, void* scratch, int* err, cudaStream_t st);

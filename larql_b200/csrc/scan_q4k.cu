@@ -65,7 +65,7 @@ __host__ inline bool scan_geom(int hidden, ScanGeom& g) {
 
 __global__ void __launch_bounds__(SCAN_THREADS, 1)
 scan_q4k_kernel(const uint8_t* __restrict__ W, int n_rows, ScanGeom gm, XPrep xp, float* __restrict__ scores,
-                float* __restrict__ bounds, float c1, int* err) {
+                uint32_t* __restrict__ hist, uint32_t* __restrict__ bound_bits, float c1, int* err) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     float* part = reinterpret_cast<float*>(smem + 128);  // [2 buffers][2 kinds][R*G]
@@ -118,6 +118,7 @@ scan_q4k_kernel(const uint8_t* __restrict__ W, int n_rows, ScanGeom gm, XPrep xp
     }
 
     bool timed_out = false;
+    float bmax = 0.0f;  // largest row bound seen by this warp's lane 0
     for (int k = 0; k < my_count; ++k) {
         const int stg = k % gm.stages;
         const uint32_t parity = (uint32_t)((k / gm.stages) & 1);
@@ -178,10 +179,15 @@ scan_q4k_kernel(const uint8_t* __restrict__ W, int n_rows, ScanGeom gm, XPrep xp
             }
             if (lane == 0) {
                 scores[row0 + r] = a;
-                if (bounds) bounds[row0 + r] = b;
+                if (hist) {
+                    if (a != a) set_err(err, DEV_ERR_NAN_SCORE);
+                    atomicAdd(&hist[__float_as_uint(fabsf(a)) >> LQ_HIST_SHIFT], 1u);
+                    bmax = fmaxf(bmax, b);
+                }
             }
         }
     }
+    if (hist && lane == 0 && bmax > 0.0f) atomicMax(bound_bits, __float_as_uint(bmax));
     if (__syncthreads_or(timed_out ? 1 : 0)) {
         set_err(err, DEV_ERR_TMA_TIMEOUT);
         // Give copies already issued a last bounded chance to land before the CTA's
@@ -196,7 +202,9 @@ scan_q4k_kernel(const uint8_t* __restrict__ W, int n_rows, ScanGeom gm, XPrep xp
 // ------------------------------------------------------------------ exact ----
 constexpr int RESCORE_THREADS = 256;  // 8 warps, one row per warp at a time
 
-__device__ __forceinline__ float exact_row_q4k(const uint8_t* __restrict__ row, const float* __restrict__ xn, int nsb,
+// xs: the activation in shared memory, 64-float chunks at a stride of 68 floats so that the
+// eight lanes of a 128-bit load phase (chunks 64 floats apart) fall in different banks.
+__device__ __forceinline__ float exact_row_q4k(const uint8_t* __restrict__ row, const float* __restrict__ xs, int nsb,
                                                float* sb_part /* [nsb] per-warp scratch */, int lane) {
     const int g = lane & 3;
     for (int s0 = 0; s0 < nsb; s0 += 8) {
@@ -208,7 +216,7 @@ __device__ __forceinline__ float exact_row_q4k(const uint8_t* __restrict__ row, 
             const uint4 q0 = *reinterpret_cast<const uint4*>(cell + 16 + g * 32);
             const uint4 q1 = *reinterpret_cast<const uint4*>(cell + 32 + g * 32);
             const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-            const float* x_lo = xn + (size_t)s * 256 + (2 * g) * 32;
+            const float* x_lo = xs + (s * 4 + g) * 68;
             const float* x_hi = x_lo + 32;
             float dot_lo = 0.0f, dot_hi = 0.0f, sum_lo = 0.0f, sum_hi = 0.0f;
 #pragma unroll
@@ -259,13 +267,18 @@ rescore_q4k_kernel(const uint8_t* __restrict__ W, int n_rows_total, int nsb, con
                    float* __restrict__ out, TokenWs ws, int top_k, int run_final, int* err) {
     extern __shared__ __align__(128) uint8_t smem[];
     float* sb_part_all = reinterpret_cast<float*>(smem);  // [8 warps][nsb]
+    float* xs = sb_part_all + (RESCORE_THREADS / 32) * nsb; // [4*nsb chunks][68]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int n_rows = n_rows_dev ? min(*n_rows_dev, n_rows_total) : n_rows_host;
     const int row_bytes = nsb * 144;
     const int warps_total = gridDim.x * (RESCORE_THREADS / 32);
+    if ((int)blockIdx.x * (RESCORE_THREADS / 32) < n_rows) {
+        for (int i = threadIdx.x; i < nsb * 256; i += RESCORE_THREADS) xs[(i >> 6) * 68 + (i & 63)] = xn[i];
+    }
+    __syncthreads();
     for (int i = blockIdx.x * (RESCORE_THREADS / 32) + warp; i < n_rows; i += warps_total) {
         const uint32_t r = rows_idx ? rows_idx[i] : (uint32_t)i;
-        const float v = exact_row_q4k(W + (size_t)r * row_bytes, xn, nsb, sb_part_all + warp * nsb, lane);
+        const float v = exact_row_q4k(W + (size_t)r * row_bytes, xs, nsb, sb_part_all + warp * nsb, lane);
         if (lane == 0) out[i] = v;
     }
     if (run_final) {
@@ -277,7 +290,7 @@ rescore_q4k_kernel(const uint8_t* __restrict__ W, int n_rows_total, int nsb, con
         __syncthreads();
         if (s_last) {
             __threadfence();
-            final_pick_block<RESCORE_THREADS>(ws, err, sel_sm);
+            final_pick_block<RESCORE_THREADS>(ws, err, sel_sm, xs, 4 * nsb * 68);
         }
     }
 }
@@ -289,8 +302,8 @@ int scan_q4k_smem_bytes(int hidden) {
     return scan_geom(hidden, g) ? g.smem_bytes : -1;
 }
 
-cudaError_t launch_scan_q4k(const Q4kMat& m, const XPrep& xp, float* scores, float* bounds, float c1, int* err,
-                            int sm_count, cudaStream_t st) {
+cudaError_t launch_scan_q4k(const Q4kMat& m, const XPrep& xp, float* scores, uint32_t* hist, uint32_t* bound_bits,
+                            float c1, int* err, int sm_count, cudaStream_t st) {
     ScanGeom g;
     if (!scan_geom(m.cols, g)) return cudaErrorInvalidValue;
     if (m.rows == 0) return cudaSuccess;
@@ -303,7 +316,7 @@ cudaError_t launch_scan_q4k(const Q4kMat& m, const XPrep& xp, float* scores, flo
     }
     const int n_tiles = (m.rows + g.R - 1) / g.R;
     const int grid = n_tiles < sm_count ? n_tiles : sm_count;
-    scan_q4k_kernel<<<grid, SCAN_THREADS, g.smem_bytes, st>>>(m.w, m.rows, g, xp, scores, bounds, c1, err);
+    scan_q4k_kernel<<<grid, SCAN_THREADS, g.smem_bytes, st>>>(m.w, m.rows, g, xp, scores, hist, bound_bits, c1, err);
     return cudaGetLastError();
 }
 
@@ -319,7 +332,13 @@ cudaError_t launch_rescore_q4k(const Q4kMat& m, const float* xn, const uint32_t*
         if (grid > sm_count * 8) grid = sm_count * 8;
         if (grid < 1) grid = 1;
     }
-    const size_t smem = (size_t)(RESCORE_THREADS / 32) * nsb * sizeof(float);
+    const size_t smem = ((size_t)(RESCORE_THREADS / 32) * nsb + (size_t)4 * nsb * 68) * sizeof(float);
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(rescore_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
     rescore_q4k_kernel<<<grid, RESCORE_THREADS, smem, st>>>(m.w, m.rows, nsb, xn, rows_idx, n_rows_dev, n_rows_host,
                                                            out, ws, top_k, run_final, err);
     return cudaGetLastError();

@@ -18,8 +18,7 @@ constexpr int SEL_SMEM_VALS_MAX = 40 * 1024;  // floats cached in shared memory 
 // reference scores, every row at or below tau (fewer than K rows are above tau); a
 // row below tau - 2B is beaten by the >= K rows at or above tau.
 __global__ void __launch_bounds__(SEL_T, 1)
-select_kernel(const float* __restrict__ scores, const float* __restrict__ bounds, int n, int top_k, TokenWs ws,
-              int* err, int use_smem) {
+select_kernel(const float* __restrict__ scores, int n, int top_k, TokenWs ws, int* err, int use_smem) {
     extern __shared__ __align__(16) float s_vals[];
     __shared__ SelectSmem<SEL_T> sm;
     __shared__ float s_red[SEL_T / 32];
@@ -34,7 +33,6 @@ select_kernel(const float* __restrict__ scores, const float* __restrict__ bounds
         const float v = scores[i];
         nan |= (v != v);
         if (use_smem) s_vals[i] = v;
-        if (bounds) bmax = fmaxf(bmax, bounds[i]);
     }
     for (int o = 16; o > 0; o >>= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
     if (lane == 0) s_red[warp] = bmax;
@@ -89,6 +87,79 @@ select_kernel(const float* __restrict__ scores, const float* __restrict__ bounds
     if (tid == 0) *ws.sel = SelHeader{na, nb, top_k, top_k - na, tau, B, 0, 0};
 }
 
+// Walk-path classification from the coarse histogram the scan kernel filled: the bucket
+// [t_lo, t_hi) that holds the K-th largest fast |score| is found with one suffix scan
+// over the bins; with B the scan's bound on |fast - reference| per row,
+//   |s| >  t_hi + 2B  -> certainly in the reference's top-K   (fewer than K rows reach t_hi)
+//   |s| >= t_lo - 2B  -> needs the reference's exact score    (band)
+//   else              -> certainly out                        (at least K rows reach t_lo).
+// The histogram and the bound word are cleared for the next scan.
+__global__ void __launch_bounds__(SEL_T, 1)
+classify_kernel(const float* __restrict__ scores_g, int n, int top_k, TokenWs ws, int* err, int use_smem) {
+    extern __shared__ __align__(16) float s_vals[];
+    __shared__ SelectSmem<SEL_T> sm;
+    __shared__ uint32_t s_wsum[SEL_T / 32];
+    constexpr int PER = LQ_HIST_BINS / SEL_T;  // bins per thread, contiguous
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // stage the scores in shared memory (independent loads), so the two compaction passes
+    // do not pay a global-memory round trip per element
+    if (use_smem)
+        for (int i = tid; i < n; i += SEL_T) s_vals[i] = scores_g[i];
+    const float* scores = use_smem ? s_vals : scores_g;
+    uint32_t bins[PER];
+    uint32_t own = 0;
+#pragma unroll
+    for (int b = 0; b < PER; ++b) {
+        bins[b] = ws.hist[tid * PER + b];
+        own += bins[b];
+        ws.hist[tid * PER + b] = 0;
+    }
+    // inclusive suffix sum over threads (higher thread = larger keys)
+    uint32_t suf = own;
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t v = __shfl_down_sync(0xffffffffu, suf, o);
+        if (lane + o < 32) suf += v;
+    }
+    if (lane == 0) s_wsum[warp] = suf;
+    __syncthreads();
+    uint32_t higher = 0;
+    for (int w = warp + 1; w < SEL_T / 32; ++w) higher += s_wsum[w];
+    suf += higher;
+    const uint32_t above = suf - own;
+    if (above < (uint32_t)top_k && (uint32_t)top_k <= suf) {
+        uint32_t acc = above;
+        int b = PER - 1;
+        for (; b >= 0; --b) {
+            if (acc + bins[b] >= (uint32_t)top_k) break;
+            acc += bins[b];
+        }
+        sm.bcast[0] = tid * PER + b;
+    }
+    __syncthreads();
+    const uint32_t bstar = (uint32_t)sm.bcast[0];
+    const float B = __uint_as_float(ws.sel->bound_bits);
+    const float t_lo = __uint_as_float(bstar << LQ_HIST_SHIFT);
+    const uint32_t hi_bits = (bstar + 1u) << LQ_HIST_SHIFT;
+    const float t_hi = __uint_as_float(hi_bits > 0x7F800000u ? 0x7F800000u : hi_bits);
+    const float two_b = __fmul_ru(2.0f, B);
+    const float hi = __fadd_ru(t_hi, two_b), lo = __fadd_rd(t_lo, -two_b);
+    __syncthreads();
+    int na, nb;
+    block_compact2<SEL_T>(
+        n, sm, n,
+        [&](int i) {
+            const float a = fabsf(scores[i]);
+            return a > hi ? 1 : (a >= lo ? 2 : 0);
+        },
+        [&](int pos, int i) {
+            ws.hit_idx[pos] = (uint32_t)i;
+            ws.hit_score[pos] = scores[i];
+        },
+        [&](int pos, int i) { ws.band_idx[pos] = (uint32_t)i; }, na, nb);
+    if (tid == 0) *ws.sel = SelHeader{na, nb, top_k, top_k - na, t_lo, B, 0, 0u};
+    (void)err;
+}
+
 __global__ void __launch_bounds__(256) final_pick_kernel(TokenWs ws, int* err) {
     __shared__ SelectSmem<256> sm;
     final_pick_block<256>(ws, err, sm);
@@ -136,8 +207,7 @@ __global__ void __launch_bounds__(1024) sort_hits_kernel(const uint32_t* hit_idx
 
 }  // namespace
 
-cudaError_t launch_select(const float* scores, const float* bounds, int n, int top_k, TokenWs ws, int* err,
-                          cudaStream_t st) {
+cudaError_t launch_select(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st) {
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -147,7 +217,21 @@ cudaError_t launch_select(const float* scores, const float* bounds, int n, int t
     }
     const int use_smem = n <= SEL_SMEM_VALS_MAX;
     const size_t smem = use_smem ? (size_t)((n + 3) / 4 * 4) * sizeof(float) : 0;
-    select_kernel<<<1, SEL_T, smem, st>>>(scores, bounds, n, top_k, ws, err, use_smem);
+    select_kernel<<<1, SEL_T, smem, st>>>(scores, n, top_k, ws, err, use_smem);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_classify(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(classify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             SEL_SMEM_VALS_MAX * 4);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    const int use_smem = n <= SEL_SMEM_VALS_MAX;
+    const size_t smem = use_smem ? (size_t)((n + 3) / 4 * 4) * sizeof(float) : 0;
+    classify_kernel<<<1, SEL_T, smem, st>>>(scores, n, top_k, ws, err, use_smem);
     return cudaGetLastError();
 }
 
@@ -159,7 +243,7 @@ cudaError_t launch_final_pick(TokenWs ws, int* err, cudaStream_t st) {
 cudaError_t launch_topk_abs_sorted(const float* scores, int n, int top_k, TokenWs ws, uint32_t* idx_out,
                                    float* val_out, int* count_out, unsigned long long* sort_buf, int* err,
                                    cudaStream_t st) {
-    cudaError_t e = launch_select(scores, nullptr, n, top_k, ws, err, st);
+    cudaError_t e = launch_select(scores, n, top_k, ws, err, st);
     if (e != cudaSuccess) return e;
     e = launch_final_pick(ws, err, st);
     if (e != cudaSuccess) return e;

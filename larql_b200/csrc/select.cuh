@@ -31,21 +31,57 @@ __device__ __forceinline__ int warp_chunk(int n, int n_warps) {
 
 // Finds the k-th largest key among vals[0..n) (1 <= k <= n).  Outputs the key, how
 // many keys are strictly greater, and how many of the equal ones are still needed.
+// The radix passes start at the highest bit in which the keys differ (found with a
+// min/max reduction), so keys that share their leading bits - scores of similar
+// magnitude, or a narrow band of near-ties - spread over the 256 bins of the first
+// pass instead of colliding in one.
 template <int T>
 __device__ void block_kth_largest(const float* vals, int n, int k, SelectSmem<T>& sm, uint32_t& tau_key, int& cnt_gt,
                                   int& need_eq) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int chunk = warp_chunk(n, T / 32);
     const int beg = warp * chunk, end = min(n, beg + chunk);
-    uint32_t prefix = 0, mask = 0;
+    // key range
+    uint32_t kmin = 0xffffffffu, kmax = 0u;
+    for (int i = beg + lane; i < end; i += 32) {
+        const uint32_t key = abs_key(vals[i]);
+        kmin = min(kmin, key);
+        kmax = max(kmax, key);
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, o));
+        kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+    }
+    if (lane == 0) {
+        sm.wcnt_a[warp] = (int)kmin;
+        sm.wcnt_b[warp] = (int)kmax;
+    }
+    __syncthreads();
+    kmin = 0xffffffffu;
+    kmax = 0u;
+    for (int w = 0; w < T / 32; ++w) {
+        kmin = min(kmin, (uint32_t)sm.wcnt_a[w]);
+        kmax = max(kmax, (uint32_t)sm.wcnt_b[w]);
+    }
+    __syncthreads();
+    if (kmin == kmax) {  // every key equal
+        tau_key = kmin;
+        cnt_gt = 0;
+        need_eq = k;
+        return;
+    }
+    int hi_bit = 32 - __clz(kmin ^ kmax);  // bits [hi_bit, 32) are common to all keys
+    uint32_t prefix = hi_bit < 32 ? (kmax >> hi_bit) << hi_bit : 0u;
     int remaining = k;
-    for (int pass = 0; pass < 4; ++pass) {
-        const int shift = 24 - 8 * pass;
+    while (hi_bit > 0) {
+        const int lo_bit = max(hi_bit - 8, 0);
+        const uint32_t dmask = (1u << (hi_bit - lo_bit)) - 1u;
         for (int i = tid; i < (T / 32) * 256; i += T) (&sm.whist[0][0])[i] = 0;
         __syncthreads();
         for (int i = beg + lane; i < end; i += 32) {
             const uint32_t key = abs_key(vals[i]);
-            if ((key & mask) == prefix) atomicAdd(&sm.whist[warp][(key >> shift) & 255u], 1u);
+            const bool match = hi_bit >= 32 ? true : ((key >> hi_bit) == (prefix >> hi_bit));
+            if (match) atomicAdd(&sm.whist[warp][(key >> lo_bit) & dmask], 1u);
         }
         __syncthreads();
         if (tid < 256) {
@@ -76,13 +112,12 @@ __device__ void block_kth_largest(const float* vals, int n, int k, SelectSmem<T>
                 }
                 sm.bcast[0] = 8 * lane + b;
                 sm.bcast[1] = remaining - (int)acc;
-                sm.bcast[2] = (int)sm.total[8 * lane + b];
             }
         }
         __syncthreads();
-        prefix |= ((uint32_t)sm.bcast[0]) << shift;
-        mask |= 255u << shift;
+        prefix |= ((uint32_t)sm.bcast[0]) << lo_bit;
         remaining = sm.bcast[1];
+        hi_bit = lo_bit;
         __syncthreads();
     }
     tau_key = prefix;
@@ -153,16 +188,22 @@ __device__ void block_compact2(int n, SelectSmem<T>& sm, int limit_b, Cls cls, E
 // Final pick: of the n_band rows whose exact scores are in ws.band_exact, the `need`
 // best under (|v| desc, index asc) are appended to the hit list after the n_in
 // certain rows.  Runs in one CTA of T threads.
+// `stage` (optional, stage_cap floats of shared memory) caches the exact scores so the
+// passes below do not wait on global memory each time.
 template <int T>
-__device__ void final_pick_block(TokenWs ws, int* err, SelectSmem<T>& sm) {
+__device__ void final_pick_block(TokenWs ws, int* err, SelectSmem<T>& sm, float* stage = nullptr, int stage_cap = 0) {
     const int n_in = ws.sel->n_in, n_band = ws.sel->n_band;
     int need = ws.sel->need;
     if (need <= 0 || n_band <= 0) return;
     // NaN in an exact score: the reference panics.
+    const bool staged = stage != nullptr && n_band <= stage_cap;
     for (int i = threadIdx.x; i < n_band; i += T) {
         const float v = ws.band_exact[i];
         if (v != v) set_err(err, DEV_ERR_NAN_SCORE);
+        if (staged) stage[i] = v;
     }
+    const float* ex = staged ? stage : ws.band_exact;
+    __syncthreads();
     if (need >= n_band) {
         for (int i = threadIdx.x; i < n_band; i += T) {
             ws.hit_idx[n_in + i] = ws.band_idx[i];
@@ -172,7 +213,7 @@ __device__ void final_pick_block(TokenWs ws, int* err, SelectSmem<T>& sm) {
     }
     uint32_t tau_key;
     int cnt_gt, need_eq;
-    block_kth_largest<T>(ws.band_exact, n_band, need, sm, tau_key, cnt_gt, need_eq);
+    block_kth_largest<T>(ex, n_band, need, sm, tau_key, cnt_gt, need_eq);
     // Ordered compaction: strictly-greater rows and the first need_eq equal rows, merged
     // in index order.  Two passes keep it simple: class 1 = greater, class 2 = equal.
     // Positions: greater rows and equal rows interleave by index, so emit both through
@@ -183,19 +224,19 @@ __device__ void final_pick_block(TokenWs ws, int* err, SelectSmem<T>& sm) {
     __syncthreads();
     int na, nb;
     block_compact2<T>(
-        n_band, sm, need_eq, [&](int i) { return abs_key(ws.band_exact[i]) == tau_key ? 2 : 0; },
+        n_band, sm, need_eq, [&](int i) { return abs_key(ex[i]) == tau_key ? 2 : 0; },
         [&](int, int) {}, [&](int pos, int i) { if (pos == need_eq - 1) s_cut = i + 1; }, na, nb);
     __syncthreads();
     const int cut = s_cut;
     block_compact2<T>(
         n_band, sm, 0,
         [&](int i) {
-            const uint32_t key = abs_key(ws.band_exact[i]);
+            const uint32_t key = abs_key(ex[i]);
             return (key > tau_key || (key == tau_key && i < cut)) ? 1 : 0;
         },
         [&](int pos, int i) {
             ws.hit_idx[n_in + pos] = ws.band_idx[i];
-            ws.hit_score[n_in + pos] = ws.band_exact[i];
+            ws.hit_score[n_in + pos] = ex[i];
         },
         [&](int, int) {}, na, nb);
 }
