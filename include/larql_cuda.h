@@ -139,7 +139,7 @@ LQ_API int lq_dequantize(lq_ctx* ctx, const lq_matrix* m, float* out, size_t out
  * walk_ffn_sparse (…/walk_ffn/sparse.rs:60-306).  gate, up: [features, hidden];
  * down_fm: feature-major [features, hidden] (…/write_kquant/feature_major_down.rs:46-90).
  * x, out: [batch, hidden].  idx_out (optional): [batch, min(top_k, features)] selected feature
- * ids per token (certain rows ascending, then resolved boundary rows); count_out (optional):
+ * ids per token, in no particular order (the SET is the reference's); count_out (optional):
  * hits per token. */
 LQ_API int lq_walk_ffn(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const lq_matrix* down_fm,
                        const float* x, size_t batch, size_t top_k, uint32_t flags, float* out,
@@ -180,6 +180,11 @@ typedef struct lq_walk_stats {
     float tau, bound;
 } lq_walk_stats;
 LQ_API int lq_last_walk_stats(lq_ctx* ctx, lq_walk_stats* out);
+
+/* Phase times (microseconds, CTA 0, last layer) of the last fused persistent walk: prepare, scan,
+ * barrier, classify, re-score, gather, barrier, pick, gather of band winners, merge, barrier, finish.
+ * The reference's counterpart is PhaseTimingsHandle (crates/larql-inference/src/vindex/walk_ffn/timings.rs:12-33). */
+LQ_API int lq_fused_phase_us(lq_ctx* ctx, float* us, size_t n);
 
 #ifdef __cplusplus
 }

@@ -35,7 +35,7 @@ EXPORTS = [
     "lq_drop_weight_regions", "lq_device_ptr", "lq_q4k_matvec", "lq_q4k_matmul", "lq_q4k_matvec_exact",
     "lq_topk_abs", "lq_rms_norm", "lq_dequantize", "lq_walk_ffn", "lq_dev_q4k_matvec", "lq_dev_walk_ffn",
     "lq_stack_create", "lq_stack_run", "lq_stack_destroy", "lq_last_walk_stats", "lq_dev_quantize_q4k",
-    "lq_profile_walk",
+    "lq_profile_walk", "lq_fused_phase_us",
 ]
 
 
@@ -94,6 +94,7 @@ def load_library() -> C.CDLL:
         "lq_last_walk_stats": (C.c_int, [vp, C.POINTER(WalkStats)]),
         "lq_dev_quantize_q4k": (C.c_int, [vp, f32p, sz, vp]),
         "lq_profile_walk": (C.c_int, [vp, mp, mp, mp, f32p, sz, C.c_uint32, f32p, f32p]),
+        "lq_fused_phase_us": (C.c_int, [vp, f32p, sz]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -281,6 +282,11 @@ class CudaBackend:
             return None
         hits = [idx[t, :cnt[t]].copy() for t in range(batch)] if want_idx else None
         return out.reshape(x.shape), hits
+
+    def fused_phase_us(self):
+        us = (C.c_float * 12)()
+        ok = self._status(self._lib.lq_fused_phase_us(self._h, us, 12))
+        return list(us) if ok else None
 
     def last_walk_stats(self) -> WalkStats:
         s = WalkStats()

@@ -6,6 +6,7 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -22,6 +23,10 @@ cudaError_t launch_topk_abs_sorted(const float* scores, int n, int top_k, TokenW
                                    cudaStream_t st);
 cudaError_t launch_dequantize(const lq_matrix& m, float* out, cudaStream_t st);
 cudaError_t launch_quantize_q4k(const float* data, size_t n_elems, uint8_t* out, cudaStream_t st);
+cudaError_t launch_walk_fused_q4k(const void* layers_dev, const uint8_t* const* single, int n_layers, int n_rows,
+                                  int hidden, int top_k, uint32_t flags, float c1, const float* h_in, float* h_out,
+                                  uint8_t* ws, uint32_t* hit_out, uint32_t* count_out, lq_walk_stats* stats_dev,
+                                  int* err, int sm_count, cudaStream_t st);
 }  // namespace lq
 
 struct lq_stack {
@@ -32,6 +37,8 @@ struct lq_stack {
     float *h_in = nullptr, *h_out = nullptr, *h_buf[2] = {nullptr, nullptr};
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
+    void* layers_dev = nullptr;  // fused path: n_layers x {gate, up, down}
+    bool fused = false;
 };
 
 struct lq_ctx {
@@ -63,6 +70,12 @@ struct lq_ctx {
     uint8_t* stage = nullptr;
     size_t stage_cap = 0;
     lq_walk_stats stats = {};
+    // fused persistent walk: control block + partials + residual ping-pong (zero-initialised)
+    uint8_t* fws = nullptr;
+    size_t fws_cap = 0;
+    lq_walk_stats* stats_dev = nullptr;
+    bool use_fused = true;
+    bool last_fused = false;
 };
 
 namespace {
@@ -171,6 +184,33 @@ int ensure_ws(lq_ctx* ctx, size_t batch, size_t hidden, size_t feat) {
     return LQ_OK;
 }
 
+int ensure_fused(lq_ctx* ctx, size_t hidden, size_t feat) {
+    const size_t need = fused_q4k_ws_bytes((int)hidden, (int)feat, ctx->sm_count);
+    if (need <= ctx->fws_cap) return LQ_OK;
+    cudaStreamCaptureStatus cs;
+    CK(cudaStreamIsCapturing(ctx->stream, &cs));
+    if (cs != cudaStreamCaptureStatusNone) return fail(ctx, LQ_ERR_ARGUMENT, "workspace growth during capture");
+    CK(cudaStreamSynchronize(ctx->stream));
+    if (ctx->fws) CK(cudaFree(ctx->fws));
+    ctx->fws = nullptr;
+    ctx->fws_cap = 0;
+    CK(cudaMalloc(&ctx->fws, need));
+    CK(cudaMemsetAsync(ctx->fws, 0, need, ctx->stream));
+    ctx->fws_cap = need;
+    if (!ctx->stats_dev) {
+        CK(cudaMalloc(&ctx->stats_dev, 256));
+        CK(cudaMemsetAsync(ctx->stats_dev, 0, 256, ctx->stream));
+    }
+    return LQ_OK;
+}
+
+bool fused_ok(lq_ctx* ctx, const lq_matrix& gate, const lq_matrix& up, const lq_matrix& down, size_t k) {
+    if (!ctx->use_fused) return false;
+    if (gate.fmt != LQ_FMT_Q4_K || up.fmt != LQ_FMT_Q4_K || down.fmt != LQ_FMT_Q4_K) return false;
+    if ((((uintptr_t)gate.data | (uintptr_t)up.data | (uintptr_t)down.data) & 15) != 0) return false;
+    return fused_q4k_supported((int)gate.cols, (int)gate.rows, (int)k, ctx->sm_count);
+}
+
 int ensure_stage(lq_ctx* ctx, size_t bytes) {
     if (bytes <= ctx->stage_cap) return LQ_OK;
     CK(cudaStreamSynchronize(ctx->stream));
@@ -241,6 +281,8 @@ int check_device_err(lq_ctx* ctx) {
     CK(cudaStreamSynchronize(ctx->stream));
     if (h == DEV_OK) return LQ_OK;
     CK(cudaMemsetAsync(ctx->d_err, 0, sizeof(int), ctx->stream));
+    // a failed fused launch may leave its histogram / counters dirty
+    if (ctx->fws) CK(cudaMemsetAsync(ctx->fws, 0, (size_t)2 * LQ_HIST_BINS * 4 + 256, ctx->stream));
     if (h == DEV_ERR_NAN_SCORE) return fail(ctx, LQ_ERR_NAN_SCORE, "NaN gate score or non-finite activation");
     if (h == DEV_ERR_TMA_TIMEOUT) return fail(ctx, LQ_ERR_TIMEOUT, "a bounded device-side wait ran out");
     return fail(ctx, LQ_ERR_CUDA, "device-side internal error");
@@ -309,6 +351,21 @@ int dev_walk(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const lq_m
     int rc = ensure_ws(ctx, batch, H, N);
     if (rc) return rc;
     const size_t k = effective_k(top_k, N, flags);
+    if (N > 0 && fused_ok(ctx, *gate, *up, *down, k)) {
+        rc = ensure_fused(ctx, H, N);
+        if (rc) return rc;
+        const uint8_t* single[3] = {(const uint8_t*)gate->data, (const uint8_t*)up->data, (const uint8_t*)down->data};
+        for (size_t t = 0; t < batch; ++t) {
+            CK(launch_walk_fused_q4k(nullptr, single, 1, (int)N, (int)H, (int)k, flags, bound_c1((int)H), x + t * H,
+                                     out + t * H, ctx->fws, idx_out ? idx_out + t * k : nullptr,
+                                     count_out ? count_out + t : nullptr, t == 0 ? ctx->stats_dev : nullptr,
+                                     ctx->d_err, ctx->sm_count, ctx->stream));
+            ctx->launches += 1;
+        }
+        ctx->last_fused = true;
+        return LQ_OK;
+    }
+    ctx->last_fused = false;
     TokenWs& w0 = ctx->tok[0];
     // Token workspaces are laid out with a constant byte stride; prep takes it in 4-byte words.
     const size_t tok_stride_f =
@@ -362,6 +419,7 @@ int lq_create(int device, lq_ctx** out) {
         delete ctx;
         return LQ_ERR_CUDA;
     }
+    if (const char* e = getenv("LARQL_B200_NO_FUSED")) ctx->use_fused = !(e[0] && e[0] != '0');
     *out = ctx;
     return LQ_OK;
 }
@@ -372,6 +430,8 @@ void lq_destroy(lq_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     for (auto& r : ctx->regions) cudaFree(r.dev);
     cudaFree(ctx->ws_raw);
+    cudaFree(ctx->fws);
+    cudaFree(ctx->stats_dev);
     cudaFree(ctx->stage);
     cudaFree(ctx->sort_buf);
     cudaFree(ctx->d_err);
@@ -617,10 +677,27 @@ int lq_walk_ffn(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const l
     rc = lq_synchronize(ctx);
     if (rc) return rc;
     if (N && batch && H) {
-        SelHeader h;
-        CK(cudaMemcpy(&h, ctx->tok[0].sel, sizeof h, cudaMemcpyDeviceToHost));
-        ctx->stats = lq_walk_stats{h.n_in, h.n_band, h.n_sel, h.need, h.tau, h.bound};
+        if (ctx->last_fused) {
+            CK(cudaMemcpy(&ctx->stats, ctx->stats_dev, sizeof(lq_walk_stats), cudaMemcpyDeviceToHost));
+        } else {
+            SelHeader h;
+            CK(cudaMemcpy(&h, ctx->tok[0].sel, sizeof h, cudaMemcpyDeviceToHost));
+            ctx->stats = lq_walk_stats{h.n_in, h.n_band, h.n_sel, h.need, h.tau, h.bound};
+        }
     }
+    return LQ_OK;
+}
+
+int lq_fused_phase_us(lq_ctx* ctx, float* us, size_t n) {
+    if (!ctx || !us) return LQ_ERR_ARGUMENT;
+    if (!ctx->stats_dev) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "no fused walk has run");
+    CK(cudaStreamSynchronize(ctx->stream));
+    int khz = 0;
+    CK(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx->device));
+    const double clk_mhz = khz > 0 ? khz * 1e-3 : 1965.0;  // stamps are SM cycles
+    unsigned long long t[16];
+    CK(cudaMemcpy(t, (uint8_t*)ctx->stats_dev + 64, sizeof t, cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < n && i < 12; ++i) us[i] = (float)((double)(t[i + 1] - t[i]) / clk_mhz);
     return LQ_OK;
 }
 
@@ -692,6 +769,18 @@ int lq_profile_walk(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, con
 // ----------------------------------------------------------------- layer stack ----
 static int stack_enqueue(lq_ctx* ctx, lq_stack* s) {
     const size_t L = s->gates.size();
+    if (s->fused) {
+        const int N = (int)s->gates[0].rows, H = s->hidden;
+        const size_t k = effective_k(s->top_k, (size_t)N, s->flags);
+        for (size_t t = 0; t < s->batch; ++t) {
+            CK(launch_walk_fused_q4k(s->layers_dev, nullptr, (int)L, N, H, (int)k, s->flags, bound_c1(H),
+                                     s->h_in + t * H, s->h_out + t * H, ctx->fws, nullptr, nullptr,
+                                     t == 0 ? ctx->stats_dev : nullptr, ctx->d_err,
+                                     ctx->sm_count, ctx->stream));
+            ctx->launches += 1;
+        }
+        return LQ_OK;
+    }
     const float* cur = s->h_in;
     for (size_t l = 0; l < L; ++l) {
         float* nxt = (l + 1 == L) ? s->h_out : s->h_buf[l & 1];
@@ -738,12 +827,42 @@ int lq_stack_create(lq_ctx* ctx, const lq_matrix* gates, const lq_matrix* ups, c
     s->h_out = (float*)(raw + bytes);
     s->h_buf[0] = (float*)(raw + 2 * bytes);
     s->h_buf[1] = (float*)(raw + 3 * bytes);
+    // Fused path: every layer the same shape and Q4_K -> one cooperative launch per token.
+    {
+        bool same = true;
+        for (size_t l = 0; l < n_layers; ++l)
+            same = same && gates[l].rows == gates[0].rows && gates[l].cols == gates[0].cols;
+        const size_t k = effective_k(top_k, (size_t)gates[0].rows, s->flags);
+        bool ok = same;
+        for (size_t l = 0; ok && l < n_layers; ++l) ok = fused_ok(ctx, s->gates[l], s->ups[l], s->downs[l], k);
+        if (ok) {
+            rc = ensure_fused(ctx, (size_t)s->hidden, (size_t)gates[0].rows);
+            if (rc) {
+                lq_stack_destroy(ctx, s);
+                return rc;
+            }
+            std::vector<const void*> ptrs(3 * n_layers);
+            for (size_t l = 0; l < n_layers; ++l) {
+                ptrs[3 * l] = s->gates[l].data;
+                ptrs[3 * l + 1] = s->ups[l].data;
+                ptrs[3 * l + 2] = s->downs[l].data;
+            }
+            e = cudaMalloc(&s->layers_dev, ptrs.size() * sizeof(void*));
+            if (e == cudaSuccess)
+                e = cudaMemcpy(s->layers_dev, ptrs.data(), ptrs.size() * sizeof(void*), cudaMemcpyHostToDevice);
+            if (e != cudaSuccess) {
+                lq_stack_destroy(ctx, s);
+                return cuda_fail(ctx, e, "stack layer table");
+            }
+            s->fused = true;
+        }
+    }
     // One eager pass on a harmless input grows the workspace and sets kernel attributes,
     // neither of which may happen inside a capture.
     cudaMemsetAsync(s->h_in, 0x3f, bytes, ctx->stream);
     rc = stack_enqueue(ctx, s);
     if (!rc) rc = lq_synchronize(ctx);
-    if (!rc) {
+    if (!rc && !s->fused) {
         e = cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal);
         if (e == cudaSuccess) {
             rc = stack_enqueue(ctx, s);
@@ -765,10 +884,14 @@ int lq_stack_create(lq_ctx* ctx, const lq_matrix* gates, const lq_matrix* ups, c
 }
 
 int lq_stack_run(lq_ctx* ctx, lq_stack* s, const float* h_in, float* h_out) {
-    if (!ctx || !s || !s->exec) return LQ_ERR_ARGUMENT;
+    if (!ctx || !s || (!s->exec && !s->fused)) return LQ_ERR_ARGUMENT;
     const size_t bytes = s->batch * s->hidden * 4;
     CK(cudaMemcpyAsync(s->h_in, h_in, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
-    CK(cudaGraphLaunch(s->exec, ctx->stream));
+    if (s->fused) {
+        int rc = stack_enqueue(ctx, s);
+        if (rc) return rc;
+    } else
+        CK(cudaGraphLaunch(s->exec, ctx->stream));
     CK(cudaMemcpyAsync(h_out, s->h_out, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
     return LQ_OK;
 }
@@ -779,6 +902,7 @@ void lq_stack_destroy(lq_ctx* ctx, lq_stack* s) {
     if (s->exec) cudaGraphExecDestroy(s->exec);
     if (s->graph) cudaGraphDestroy(s->graph);
     if (s->h_in) cudaFree(s->h_in);
+    if (s->layers_dev) cudaFree(s->layers_dev);
     delete s;
 }
 

@@ -82,4 +82,7 @@ cudaError_t launch_gather_q4k(const Q4kMat& up, const Q4kMat& down, const XPrep&
 cudaError_t launch_finish(const float* partials, int n_partials, int hidden, const float* residual, float* out,
                           cudaStream_t st);
 
+// walk_fused_q4k.cu — the fused persistent walk (one token, all layers, one cooperative launch)
+bool fused_q4k_supported(int hidden, int n_rows, int top_k, int sm_count);
+size_t fused_q4k_ws_bytes(int hidden, int n_rows, int sm_count);
 }  // namespace lq

@@ -1,0 +1,68 @@
+// One Q4_K row in the reference CPU backend's exact f32 order (Association A:
+// process_q4k_superblock, crates/larql-compute/src/cpu/ops/q4_common/matvec_f32.rs:116-155,
+// with the scalar q4_dual_dot_32, .../q4_common/dual.rs:186-198), computed by one warp.
+#pragma once
+#include "common.cuh"
+
+namespace lq {
+
+// xs: the activation in shared memory, 64-float chunks at a stride of 68 floats so that the
+// eight lanes of a 128-bit load phase (chunks 64 floats apart) fall in different banks.
+__device__ __forceinline__ float exact_row_q4k(const uint8_t* __restrict__ row, const float* __restrict__ xs, int nsb,
+                                               float* sb_part /* [nsb] per-warp scratch */, int lane) {
+    const int g = lane & 3;
+    for (int s0 = 0; s0 < nsb; s0 += 8) {
+        const int s = s0 + (lane >> 2);
+        float u_lo = 0.0f, u_hi = 0.0f;
+        if (s < nsb) {
+            const uint8_t* cell = row + (size_t)s * 144;
+            const uint4 hdr = *reinterpret_cast<const uint4*>(cell);
+            const uint4 q0 = *reinterpret_cast<const uint4*>(cell + 16 + g * 32);
+            const uint4 q1 = *reinterpret_cast<const uint4*>(cell + 32 + g * 32);
+            const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+            const float* x_lo = xs + (s * 4 + g) * 68;
+            const float* x_hi = x_lo + 32;
+            float dot_lo = 0.0f, dot_hi = 0.0f, sum_lo = 0.0f, sum_hi = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float4 xl = *reinterpret_cast<const float4*>(x_lo + 4 * j);
+                const float4 xh = *reinterpret_cast<const float4*>(x_hi + 4 * j);
+                const float xls[4] = {xl.x, xl.y, xl.z, xl.w}, xhs[4] = {xh.x, xh.y, xh.z, xh.w};
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const uint32_t byte = (qw[j] >> (8 * b)) & 0xffu;
+                    dot_lo = __fadd_rn(dot_lo, __fmul_rn((float)(byte & 0x0fu), xls[b]));
+                    dot_hi = __fadd_rn(dot_hi, __fmul_rn((float)(byte >> 4), xhs[b]));
+                    sum_lo = __fadd_rn(sum_lo, xls[b]);
+                    sum_hi = __fadd_rn(sum_hi, xhs[b]);
+                }
+            }
+            const float d = f16_bits_to_f32(hdr.x), dmin = f16_bits_to_f32(hdr.x >> 16);
+            uint32_t sc2, m2;
+            q4k_pair_scales(hdr.y, hdr.z, hdr.w, g, sc2, m2);
+            const float sc_lo = __fmul_rn(d, (float)(sc2 & 0xff)), sc_hi = __fmul_rn(d, (float)(sc2 >> 8));
+            const float mn_lo = __fmul_rn(dmin, (float)(m2 & 0xff)), mn_hi = __fmul_rn(dmin, (float)(m2 >> 8));
+            u_lo = __fsub_rn(__fmul_rn(sc_lo, dot_lo), __fmul_rn(mn_lo, sum_lo));
+            u_hi = __fsub_rn(__fmul_rn(sc_hi, dot_hi), __fmul_rn(mn_hi, sum_hi));
+        }
+        // Super-block partial: acc = 0; for g in 0..4 { acc += u_lo(g); acc += u_hi(g) }.
+        const int base = lane & ~3;
+        float acc = 0.0f;
+#pragma unroll
+        for (int gg = 0; gg < 4; ++gg) {
+            const float a = __shfl_sync(0xffffffffu, u_lo, base + gg);
+            const float b = __shfl_sync(0xffffffffu, u_hi, base + gg);
+            acc = __fadd_rn(acc, a);
+            acc = __fadd_rn(acc, b);
+        }
+        if (g == 0 && s < nsb) sb_part[s] = acc;
+    }
+    __syncwarp();
+    float total = 0.0f;
+    if (lane == 0)
+        for (int s = 0; s < nsb; ++s) total = __fadd_rn(total, sb_part[s]);
+    __syncwarp();
+    return total;  // valid on lane 0
+}
+
+}  // namespace lq

@@ -35,16 +35,22 @@ __device__ __forceinline__ int warp_chunk(int n, int n_warps) {
 // min/max reduction), so keys that share their leading bits - scores of similar
 // magnitude, or a narrow band of near-ties - spread over the 256 bins of the first
 // pass instead of colliding in one.
-template <int T>
-__device__ void block_kth_largest(const float* vals, int n, int k, SelectSmem<T>& sm, uint32_t& tau_key, int& cnt_gt,
-                                  int& need_eq) {
+// `keyf(i)` returns the 32-bit key of element i; the CTA's first T threads take part
+// (threadIdx.x < T), synchronising on named barrier `bar` (0 = the whole CTA).
+template <int T, int BAR = 0, typename KeyFn>
+__device__ void block_kth_largest_keys(KeyFn keyf, int n, int k, SelectSmem<T>& sm, uint32_t& tau_key, int& cnt_gt,
+                                       int& need_eq) {
+    auto bsync = [] {
+        if (BAR == 0) __syncthreads();
+        else asm volatile("bar.sync %0, %1;" ::"n"(BAR), "n"(T) : "memory");
+    };
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int chunk = warp_chunk(n, T / 32);
     const int beg = warp * chunk, end = min(n, beg + chunk);
     // key range
     uint32_t kmin = 0xffffffffu, kmax = 0u;
     for (int i = beg + lane; i < end; i += 32) {
-        const uint32_t key = abs_key(vals[i]);
+        const uint32_t key = keyf(i);
         kmin = min(kmin, key);
         kmax = max(kmax, key);
     }
@@ -56,14 +62,14 @@ __device__ void block_kth_largest(const float* vals, int n, int k, SelectSmem<T>
         sm.wcnt_a[warp] = (int)kmin;
         sm.wcnt_b[warp] = (int)kmax;
     }
-    __syncthreads();
+    bsync();
     kmin = 0xffffffffu;
     kmax = 0u;
     for (int w = 0; w < T / 32; ++w) {
         kmin = min(kmin, (uint32_t)sm.wcnt_a[w]);
         kmax = max(kmax, (uint32_t)sm.wcnt_b[w]);
     }
-    __syncthreads();
+    bsync();
     if (kmin == kmax) {  // every key equal
         tau_key = kmin;
         cnt_gt = 0;
@@ -77,20 +83,20 @@ __device__ void block_kth_largest(const float* vals, int n, int k, SelectSmem<T>
         const int lo_bit = max(hi_bit - 8, 0);
         const uint32_t dmask = (1u << (hi_bit - lo_bit)) - 1u;
         for (int i = tid; i < (T / 32) * 256; i += T) (&sm.whist[0][0])[i] = 0;
-        __syncthreads();
+        bsync();
         for (int i = beg + lane; i < end; i += 32) {
-            const uint32_t key = abs_key(vals[i]);
+            const uint32_t key = keyf(i);
             const bool match = hi_bit >= 32 ? true : ((key >> hi_bit) == (prefix >> hi_bit));
             if (match) atomicAdd(&sm.whist[warp][(key >> lo_bit) & dmask], 1u);
         }
-        __syncthreads();
+        bsync();
         if (tid < 256) {
             uint32_t t = 0;
 #pragma unroll 4
             for (int w = 0; w < T / 32; ++w) t += sm.whist[w][tid];
             sm.total[tid] = t;
         }
-        __syncthreads();
+        bsync();
         if (warp == 0) {
             // lane owns buckets 8*lane .. 8*lane+7; suffix sums over lanes from the top.
             uint32_t own = 0;
@@ -114,15 +120,21 @@ __device__ void block_kth_largest(const float* vals, int n, int k, SelectSmem<T>
                 sm.bcast[1] = remaining - (int)acc;
             }
         }
-        __syncthreads();
+        bsync();
         prefix |= ((uint32_t)sm.bcast[0]) << lo_bit;
         remaining = sm.bcast[1];
         hi_bit = lo_bit;
-        __syncthreads();
+        bsync();
     }
     tau_key = prefix;
     need_eq = remaining;
     cnt_gt = k - remaining;
+}
+
+template <int T>
+__device__ void block_kth_largest(const float* vals, int n, int k, SelectSmem<T>& sm, uint32_t& tau_key, int& cnt_gt,
+                                  int& need_eq) {
+    block_kth_largest_keys<T, 0>([vals](int i) { return abs_key(vals[i]); }, n, k, sm, tau_key, cnt_gt, need_eq);
 }
 
 // Index-ordered compaction of two classes over [0, n).  cls(i) returns 1 (list A),

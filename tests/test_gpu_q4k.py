@@ -164,7 +164,7 @@ def test_walk_config1_qwen_shape_many_queries(be):
     out, hits = _check_walk(be, gate, up, down, xs, 512)
     out2, hits2 = be.walk_ffn(host(gate), host(up), host(down), xs, 512, 4)
     assert np.array_equal(bits(out), bits(out2))  # run-to-run identical
-    assert all(a.tolist() == b.tolist() for a, b in zip(hits, hits2))
+    assert all(sorted(a.tolist()) == sorted(b.tolist()) for a, b in zip(hits, hits2))
 
 
 def test_walk_edge_cases(be):
@@ -242,7 +242,7 @@ def test_full_size_llama70b_layer_properties(be):
     assert len(np.unique(idx)) == k
     # idempotence / determinism
     out2, hits2 = be.walk_ffn(host(gate), host(up), host(down), x, k, larql_b200.WALK_FORCE_SPARSE)
-    assert np.array_equal(bits(out), bits(out2)) and hits2[0].tolist() == hits[0].tolist()
+    assert np.array_equal(bits(out), bits(out2)) and sorted(hits2[0].tolist()) == sorted(hits[0].tolist())
     # scaling the activation by 2 keeps the index set (scores scale exactly by a power of two)
     _, hits3 = be.walk_ffn(host(gate), host(up), host(down), 2.0 * x, k, larql_b200.WALK_FORCE_SPARSE)
     assert sorted(hits3[0].tolist()) == sorted(hits[0].tolist())
