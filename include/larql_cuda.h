@@ -186,6 +186,26 @@ LQ_API int lq_last_walk_stats(lq_ctx* ctx, lq_walk_stats* out);
  * The reference's counterpart is PhaseTimingsHandle (crates/larql-inference/src/vindex/walk_ffn/timings.rs:12-33). */
 LQ_API int lq_fused_phase_us(lq_ctx* ctx, float* us, size_t n);
 
+/* ---- allocation-free entry point ---------------------------------------------------- */
+/* Has no counterpart in the reference.  A Q4_K matvec (same arithmetic and kernels as
+ * lq_dev_q4k_matvec) for hosts that must not allocate device memory while running: processes
+ * that gave all free HBM to their own pools at start-up, plugins under a framework allocator
+ * that forbids raw cudaMalloc, loops that cannot take cudaMalloc's device-wide synchronisation.
+ * It needs no context and calls no cudaMalloc / cudaFree: its scratch (the prepared activation)
+ * is a fixed 128 KiB array inside the library's device image, one per GPU, kept until exit.
+ *   - w, x, out are DEVICE pointers (w 16-byte aligned); out[num_rows] = Q4_K[num_rows, hidden] . x.
+ *   - hidden must be a multiple of 256 and at most 16384 (LQ_REFUSED_UNSUPPORTED beyond that,
+ *     with the reason in errbuf).
+ *   - Enqueues on `stream` (a cudaStream_t, NULL = default stream), then waits for it: the
+ *     result is ready on return.
+ *   - The first call on a device looks up the array's device address; make that call outside
+ *     any stream capture.
+ *   - All calls on a GPU share the one array (it keeps the previous call's contents; the call
+ *     clears what must start at zero): calls that overlap on the same GPU race, serialise them.
+ *   - errbuf (optional, errcap bytes) receives the text of a failure. */
+LQ_API int lq_q4k_matvec_static(const uint8_t* w, size_t w_len, const float* x, size_t num_rows, size_t hidden,
+                                float* out, void* stream, char* errbuf, size_t errcap);
+
 #ifdef __cplusplus
 }
 #endif

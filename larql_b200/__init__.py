@@ -35,7 +35,7 @@ EXPORTS = [
     "lq_drop_weight_regions", "lq_device_ptr", "lq_q4k_matvec", "lq_q4k_matmul", "lq_q4k_matvec_exact",
     "lq_topk_abs", "lq_rms_norm", "lq_dequantize", "lq_walk_ffn", "lq_dev_q4k_matvec", "lq_dev_walk_ffn",
     "lq_stack_create", "lq_stack_run", "lq_stack_destroy", "lq_last_walk_stats", "lq_dev_quantize_q4k",
-    "lq_profile_walk", "lq_fused_phase_us",
+    "lq_profile_walk", "lq_fused_phase_us", "lq_q4k_matvec_static",
 ]
 
 
@@ -95,6 +95,7 @@ def load_library() -> C.CDLL:
         "lq_dev_quantize_q4k": (C.c_int, [vp, f32p, sz, vp]),
         "lq_profile_walk": (C.c_int, [vp, mp, mp, mp, f32p, sz, C.c_uint32, f32p, f32p]),
         "lq_fused_phase_us": (C.c_int, [vp, f32p, sz]),
+        "lq_q4k_matvec_static": (C.c_int, [vp, sz, f32p, sz, sz, f32p, vp, C.c_char_p, sz]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -143,6 +144,17 @@ class DeviceMatrix:
     def c(self) -> LqMatrix:
         return LqMatrix(self.fmt | MAT_DEVICE, self.data_ptr, self.data_len, self.scales_ptr or None,
                         self.scales_len, self.tensor_scale, self.rows, self.cols)
+
+
+def q4k_matvec_static(w_ptr: int, w_len: int, x_ptr: int, num_rows: int, hidden: int, out_ptr: int, stream: int = 0):
+    """The allocation-free Q4_K matvec (device pointers; no context, no cudaMalloc inside).
+
+    For hosts that cannot allocate device memory while running; scratch is a fixed 128 KiB array
+    in the library image, so hidden <= 16384.  Returns (status, message)."""
+    lib = load_library()
+    buf = C.create_string_buffer(256)
+    rc = lib.lq_q4k_matvec_static(w_ptr, w_len, x_ptr, num_rows, hidden, out_ptr, stream or None, buf, 256)
+    return rc, buf.value.decode()
 
 
 class CudaBackend:
