@@ -183,6 +183,142 @@ def config_of(args, wl):
 
 
 # ------------------------------------------------------------------------ our arm
+def run_sharded(args, wl, be, ext, dev, rank, world, local):
+    """N > 1: the intermediate (feature) dimension of every layer is split across the GPUs;
+    three NCCL collectives per layer (see larql_b200/sharded.py). Strong scaling: same workload."""
+    import torch
+    import torch.distributed as dist
+
+    import larql_b200
+    from larql_b200 import sharded
+
+    H, N, K, L, B = wl["hidden"], wl["features"], wl["top_k"], wl["layers"], args.batch
+    if B != 1:
+        raise SystemExit("the sharded benchmark runs batch 1")
+    row = H // 256 * 144
+    lo, hi = sharded.shard_rows(N, world, rank)
+    n_loc = hi - lo
+    gen = torch.Generator(device=dev)
+    tmp = torch.empty(N * H, dtype=torch.float32, device=dev)
+    layers = []
+    for l in range(L):
+        mats = []
+        for j in range(3):
+            gen.manual_seed(0x1A2B0000 + 8 * l + j)   # the same global matrix on every rank; keep own rows
+            tmp.normal_(0.0, 0.02, generator=gen)
+            q = torch.empty(n_loc * row, dtype=torch.uint8, device=dev)
+            torch.cuda.synchronize()
+            be.dev_quantize_q4k(tmp.data_ptr() + lo * H * 4, n_loc * H, q.data_ptr())
+            be.synchronize()
+            mats.append(larql_b200.DeviceMatrix(larql_b200.FMT_Q4_K, n_loc, H, q.data_ptr(), q.numel(), keepalive=q))
+        layers.append(mats)
+    del tmp
+    torch.cuda.empty_cache()
+
+    cap = 4096
+    flags = larql_b200.WALK_RMSNORM | larql_b200.WALK_FORCE_SPARSE
+    comp = sharded.CudaShardCompute(be, layers, rank, world, lo, K, cap, flags)
+    sw = sharded.ShardedWalk(comp, rank, world, H, cap, dev)
+    n_in = 8
+    gen.manual_seed(0x5EED0000)
+    h_in = torch.randn(n_in, H, dtype=torch.float32, device=dev, generator=gen)
+    h_static = torch.zeros(H, dtype=torch.float32, device=dev)
+    launches0 = be.launch_count()
+    graph, out_static = None, None
+    with torch.cuda.stream(ext):
+        h_static.copy_(h_in[0])
+        out = sw.token(h_static, L)        # eager pass: sizes the workspace, warms NCCL
+        be.synchronize()
+        launches_per_step = be.launch_count() - launches0
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=ext):
+                out_static = sw.token(h_static, L)
+            graph = g
+        except Exception as e:  # capture of the collectives can be unavailable: run eagerly
+            if rank == 0:
+                print(f"# CUDA-graph capture unavailable ({type(e).__name__}); running eagerly", file=sys.stderr)
+            graph = None
+    torch.cuda.synchronize()
+
+    def step(i):
+        with torch.cuda.stream(ext):
+            h_static.copy_(h_in[i % n_in])
+            if graph is not None:
+                graph.replay()
+                return out_static
+            return sw.token(h_static, L)
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(physical_gpu_index(local)) as clk:
+        torch.cuda.synchronize()
+        ev0.record(ext)
+        for i in range(args.steps):
+            step(i)
+        ev1.record(ext)
+        torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    tok_s = 1.0 / (ms_step * 1e-3)
+
+    # end to end: pinned host residual in, host result out, every step
+    hp_in = torch.randn(n_in, H, dtype=torch.float32).pin_memory()
+    hp_out = torch.empty(H, dtype=torch.float32).pin_memory()
+    e2e_steps = max(1, min(args.steps, 5))
+
+    def e2e_step(i):
+        with torch.cuda.stream(ext):
+            h_static.copy_(hp_in[i % n_in], non_blocking=True)
+            o = out_static if graph is not None else None
+            if graph is not None:
+                graph.replay()
+            else:
+                o = sw.token(h_static, L)
+            hp_out.copy_(o, non_blocking=True)
+        ext.synchronize()
+
+    e2e_step(0)
+    dist.barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(i + 1)
+    e2e_local = (time.perf_counter() - t0) / e2e_steps * 1e3
+    t = torch.tensor([e2e_local], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+
+    alg_bytes = algorithmic_bytes_per_token_layer(H, N, K) * L
+    peak, peak_kind = measured_peaks()
+    achieved = alg_bytes / world / (ms_step * 1e-3) / 1e9   # per GPU
+    line = {
+        "metric": "walk_ffn_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_of(args, wl),
+        "walk_gbs": alg_bytes / (ms_step * 1e-3) / 1e9, "algorithmic_bytes_per_token": alg_bytes,
+        "collectives_per_layer": 3, "cuda_graph": graph is not None,
+        "roofline": {"kernel": "scan_q4k_kernel + gather_q4k_kernel per rank", "bound": "hbm", "achieved": achieved,
+                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "note": "per GPU: algorithmic bytes / n_gpus / step time; batch-1 sharding is collective-latency bound"},
+        "cpu_baseline": None,
+        "e2e": {"value": 1.0 / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": H * 4, "d2h_bytes_per_step": H * 4,
+                "path": "pinned host residual -> sharded walk over all layers -> host"},
+        "gpu_launches": int(launches_per_step * args.steps),
+        "clocks": clk.summary(),
+    }
+    if rank == 0:
+        print(json.dumps(line))
+    be.close()
+    dist.destroy_process_group()
+
+
 def run_ours(args, wl):
     import torch
     import torch.distributed as dist
@@ -203,7 +339,7 @@ def run_ours(args, wl):
 
     H, N, K, L, B = wl["hidden"], wl["features"], wl["top_k"], wl["layers"], args.batch
     if world > 1:
-        raise SystemExit("multi-GPU sharded walk: not wired into the benchmark yet")
+        return run_sharded(args, wl, be, ext, dev, rank, world, local)
     row = H // 256 * 144
     # Small workloads rotate over enough distinct weight copies to exceed L2 between reuses.
     copies = 1

@@ -186,6 +186,23 @@ LQ_API int lq_last_walk_stats(lq_ctx* ctx, lq_walk_stats* out);
  * The reference's counterpart is PhaseTimingsHandle (crates/larql-inference/src/vindex/walk_ffn/timings.rs:12-33). */
 LQ_API int lq_fused_phase_us(lq_ctx* ctx, float* us, size_t n);
 
+/* ---- feature-sharded walk over the GPUs of one box (device pointers, one token) --------------
+ * The reference shards layers or experts over HTTP/gRPC (docs/ffn/distributed.md:14-40) and has no
+ * feature sharding; these three steps sit between the caller's collectives (NCCL over NVLink):
+ *   scan     -> all-reduce(sum) of hist_buf [LQ_HIST_BINS + 64] u32
+ *   classify -> all-gather of pack [2 + 2*cap] i32 per rank
+ *   gather   -> all-reduce(sum) of out_partial [hidden] f32 (the caller adds the residual).
+ * Each rank passes its contiguous row range [row_offset, row_offset + rows) of gate / up / down and
+ * the GLOBAL top_k; the union of the ranks' selections is the unsharded reference's top-K set. */
+#define LQ_HIST_WORDS (16384 + 64)
+LQ_API int lq_dev_shard_scan(lq_ctx* ctx, const lq_matrix* gate_shard, const float* x, uint32_t flags, int rank,
+                             int world, uint32_t* hist_buf);
+LQ_API int lq_dev_shard_classify(lq_ctx* ctx, const lq_matrix* gate_shard, uint32_t* hist_buf, int world,
+                                 size_t top_k, size_t row_offset, int32_t* pack, size_t cap);
+LQ_API int lq_dev_shard_gather(lq_ctx* ctx, const lq_matrix* up_shard, const lq_matrix* down_shard,
+                               const int32_t* packs, int world, int rank, size_t cap, size_t top_k,
+                               size_t row_offset, float* out_partial);
+
 /* ---- allocation-free entry point ---------------------------------------------------- */
 /* Has no counterpart in the reference.  A Q4_K matvec (same arithmetic and kernels as
  * lq_dev_q4k_matvec) for hosts that must not allocate device memory while running: processes

@@ -35,7 +35,8 @@ EXPORTS = [
     "lq_drop_weight_regions", "lq_device_ptr", "lq_q4k_matvec", "lq_q4k_matmul", "lq_q4k_matvec_exact",
     "lq_topk_abs", "lq_rms_norm", "lq_dequantize", "lq_walk_ffn", "lq_dev_q4k_matvec", "lq_dev_walk_ffn",
     "lq_stack_create", "lq_stack_run", "lq_stack_destroy", "lq_last_walk_stats", "lq_dev_quantize_q4k",
-    "lq_profile_walk", "lq_fused_phase_us", "lq_q4k_matvec_static",
+    "lq_profile_walk", "lq_fused_phase_us", "lq_q4k_matvec_static", "lq_dev_shard_scan", "lq_dev_shard_classify",
+    "lq_dev_shard_gather",
 ]
 
 
@@ -95,6 +96,9 @@ def load_library() -> C.CDLL:
         "lq_dev_quantize_q4k": (C.c_int, [vp, f32p, sz, vp]),
         "lq_profile_walk": (C.c_int, [vp, mp, mp, mp, f32p, sz, C.c_uint32, f32p, f32p]),
         "lq_fused_phase_us": (C.c_int, [vp, f32p, sz]),
+        "lq_dev_shard_scan": (C.c_int, [vp, mp, f32p, C.c_uint32, C.c_int, C.c_int, vp]),
+        "lq_dev_shard_classify": (C.c_int, [vp, mp, vp, C.c_int, sz, sz, vp, sz]),
+        "lq_dev_shard_gather": (C.c_int, [vp, mp, mp, vp, C.c_int, C.c_int, sz, sz, sz, f32p]),
         "lq_q4k_matvec_static": (C.c_int, [vp, sz, f32p, sz, sz, f32p, vp, C.c_char_p, sz]),
     }
     for name, (res, args) in sig.items():
@@ -325,6 +329,22 @@ class CudaBackend:
         ok = self._status(self._lib.lq_profile_walk(self._h, C.byref(g), C.byref(u), C.byref(d), x_ptr, int(top_k),
                                                     flags, out_ptr, ms))
         return list(ms) if ok else None
+
+    # -- feature-sharded walk: the steps between the collectives --------------------
+    def dev_shard_scan(self, gate, x_ptr: int, flags: int, rank: int, world: int, hist_ptr: int):
+        g = gate.c()
+        return self._status(self._lib.lq_dev_shard_scan(self._h, C.byref(g), x_ptr, flags, rank, world, hist_ptr))
+
+    def dev_shard_classify(self, gate, hist_ptr: int, world: int, top_k: int, row_offset: int, pack_ptr: int, cap: int):
+        g = gate.c()
+        return self._status(self._lib.lq_dev_shard_classify(self._h, C.byref(g), hist_ptr, world, int(top_k),
+                                                            int(row_offset), pack_ptr, int(cap)))
+
+    def dev_shard_gather(self, up, down, packs_ptr: int, world: int, rank: int, cap: int, top_k: int,
+                         row_offset: int, out_ptr: int):
+        u, d = up.c(), down.c()
+        return self._status(self._lib.lq_dev_shard_gather(self._h, C.byref(u), C.byref(d), packs_ptr, world, rank,
+                                                          int(cap), int(top_k), int(row_offset), out_ptr))
 
     def stack_create(self, gates, ups, downs, batch: int, top_k: int, flags: int = 0):
         n = len(gates)

@@ -23,6 +23,10 @@ cudaError_t launch_topk_abs_sorted(const float* scores, int n, int top_k, TokenW
                                    cudaStream_t st);
 cudaError_t launch_dequantize(const lq_matrix& m, float* out, cudaStream_t st);
 cudaError_t launch_quantize_q4k(const float* data, size_t n_elems, uint8_t* out, cudaStream_t st);
+cudaError_t launch_shard_bound_max(const uint32_t* slots, int world, uint32_t* bound_bits, cudaStream_t st);
+cudaError_t launch_shard_pack(TokenWs ws, uint32_t row_offset, int cap, int32_t* pack, int* err, cudaStream_t st);
+cudaError_t launch_shard_pick(const int32_t* packs, int world, int rank, int cap, int top_k, uint32_t row_offset,
+                              TokenWs ws, int* err, cudaStream_t st);
 cudaError_t launch_walk_fused_q4k(const void* layers_dev, const uint8_t* const* single, int n_layers, int n_rows,
                                   int hidden, int top_k, uint32_t flags, float c1, const float* h_in, float* h_out,
                                   uint8_t* ws, uint32_t* hit_out, uint32_t* count_out, lq_walk_stats* stats_dev,
@@ -764,6 +768,80 @@ int lq_profile_walk(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, con
     }
     for (auto& e : ev) cudaEventDestroy(e);
     return rc;
+}
+
+// ------------------------------------------------------- feature-sharded walk ----
+static int shard_check(lq_ctx* ctx, const lq_matrix* m, const char* name) {
+    int rc = check_matrix(ctx, m, name);
+    if (rc) return rc;
+    if ((m->fmt & 0xff) != LQ_FMT_Q4_K) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "sharded walk: Q4_K only");
+    if (m->cols > 16384 || m->cols == 0 || m->rows == 0) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "sharded walk: shape");
+    if (((uintptr_t)m->data & 15) != 0) return fail(ctx, LQ_ERR_ARGUMENT, "sharded walk: weights not 16-byte aligned");
+    return LQ_OK;
+}
+
+int lq_dev_shard_scan(lq_ctx* ctx, const lq_matrix* gate_shard, const float* x, uint32_t flags, int rank, int world,
+                      uint32_t* hist_buf) {
+    if (!ctx || !hist_buf || rank < 0 || world < 1 || rank >= world || world > 16) return LQ_ERR_ARGUMENT;
+    int rc = shard_check(ctx, gate_shard, "gate shard");
+    if (rc) return rc;
+    const int N = (int)gate_shard->rows, H = (int)gate_shard->cols;
+    rc = ensure_ws(ctx, 1, H, N);
+    if (rc) return rc;
+    TokenWs& w = ctx->tok[0];
+    cudaStream_t st = ctx->stream;
+    CK(cudaMemsetAsync(hist_buf + LQ_HIST_BINS, 0, 64 * 4, st));
+    launch_prep(x, 1, H, (flags & LQ_WALK_RMSNORM) ? 1 : 0, 1e-6, w.xn, w.xa, w.xb, w.bscale, w.bsum, w.babs, 0,
+                ctx->d_err, st);
+    CK(cudaGetLastError());
+    const Q4kMat g{(const uint8_t*)gate_shard->data, N, H};
+    CK(launch_scan_q4k(g, xprep_of(w), w.scores, hist_buf, &w.sel->bound_bits, bound_c1(H), ctx->d_err, ctx->sm_count,
+                       st));
+    CK(cudaMemcpyAsync(hist_buf + LQ_HIST_BINS + rank, &w.sel->bound_bits, 4, cudaMemcpyDeviceToDevice, st));
+    ctx->launches += 2;
+    return LQ_OK;
+}
+
+int lq_dev_shard_classify(lq_ctx* ctx, const lq_matrix* gate_shard, uint32_t* hist_buf, int world, size_t top_k,
+                          size_t row_offset, int32_t* pack, size_t cap) {
+    if (!ctx || !hist_buf || !pack || world < 1 || world > 16 || cap == 0) return LQ_ERR_ARGUMENT;
+    int rc = shard_check(ctx, gate_shard, "gate shard");
+    if (rc) return rc;
+    const int N = (int)gate_shard->rows, H = (int)gate_shard->cols;
+    if (top_k == 0) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "sharded walk: top_k == 0");
+    if ((size_t)N > ctx->ws_feat || (size_t)H > ctx->ws_hidden) return fail(ctx, LQ_ERR_ARGUMENT, "shard_scan first");
+    TokenWs w = ctx->tok[0];
+    cudaStream_t st = ctx->stream;
+    CK(launch_shard_bound_max(hist_buf + LQ_HIST_BINS, world, &w.sel->bound_bits, st));
+    TokenWs wh = w;
+    wh.hist = hist_buf;  // global histogram; the classify kernel clears it for the next layer
+    CK(launch_classify(w.scores, N, (int)top_k, wh, ctx->d_err, st));
+    const Q4kMat g{(const uint8_t*)gate_shard->data, N, H};
+    CK(launch_rescore_q4k(g, w.xn, w.band_idx, &w.sel->n_band, 0, w.band_exact, w, (int)top_k, 0, ctx->d_err,
+                          ctx->sm_count, st));
+    CK(launch_shard_pack(w, (uint32_t)row_offset, (int)cap, pack, ctx->d_err, st));
+    ctx->launches += 4;
+    return LQ_OK;
+}
+
+int lq_dev_shard_gather(lq_ctx* ctx, const lq_matrix* up_shard, const lq_matrix* down_shard, const int32_t* packs,
+                        int world, int rank, size_t cap, size_t top_k, size_t row_offset, float* out_partial) {
+    if (!ctx || !packs || !out_partial || world < 1 || world > 16 || rank < 0 || rank >= world) return LQ_ERR_ARGUMENT;
+    int rc;
+    if ((rc = shard_check(ctx, up_shard, "up shard")) || (rc = shard_check(ctx, down_shard, "down shard"))) return rc;
+    const int N = (int)up_shard->rows, H = (int)up_shard->cols;
+    if (down_shard->rows != up_shard->rows || down_shard->cols != up_shard->cols)
+        return fail(ctx, LQ_REFUSED_SHAPE, "sharded walk: up/down shapes differ");
+    if ((size_t)N > ctx->ws_feat || (size_t)H > ctx->ws_hidden) return fail(ctx, LQ_ERR_ARGUMENT, "shard_scan first");
+    TokenWs w = ctx->tok[0];
+    cudaStream_t st = ctx->stream;
+    CK(launch_shard_pick(packs, world, rank, (int)cap, (int)top_k, (uint32_t)row_offset, w, ctx->d_err, st));
+    const Q4kMat u{(const uint8_t*)up_shard->data, N, H}, d{(const uint8_t*)down_shard->data, N, H};
+    CK(launch_gather_q4k(u, d, xprep_of(w), w.hit_idx, w.hit_score, &w.sel->n_sel, N, ctx->partials, ctx->gather_grid,
+                         ctx->d_err, st));
+    CK(launch_finish(ctx->partials, ctx->gather_grid, H, nullptr, out_partial, st));
+    ctx->launches += 3;
+    return LQ_OK;
 }
 
 // ----------------------------------------------------------------- layer stack ----
