@@ -230,15 +230,9 @@ def run_sharded(args, wl, be, ext, dev, rank, world, local):
         out = sw.token(h_static, L)        # eager pass: sizes the workspace, warms NCCL
         be.synchronize()
         launches_per_step = be.launch_count() - launches0
-        try:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=ext):
-                out_static = sw.token(h_static, L)
-            graph = g
-        except Exception as e:  # capture of the collectives can be unavailable: run eagerly
-            if rank == 0:
-                print(f"# CUDA-graph capture unavailable ({type(e).__name__}); running eagerly", file=sys.stderr)
-            graph = None
+        # One token is NOT replayed from a CUDA graph here: capturing the NCCL collectives together
+        # with these kernels did not complete on this pool (the capture never returned), so the
+        # layer loop runs eagerly and its host overhead is part of the number.
     torch.cuda.synchronize()
 
     def step(i):
@@ -314,9 +308,14 @@ def run_sharded(args, wl, be, ext, dev, rank, world, local):
         "clocks": clk.summary(),
     }
     if rank == 0:
-        print(json.dumps(line))
-    be.close()
-    dist.destroy_process_group()
+        print(json.dumps(line), flush=True)
+    # Leave without running destructors: tensors that recorded events on the context's stream and
+    # NCCL's own teardown otherwise race the CUDA context at interpreter exit.
+    torch.cuda.synchronize()
+    dist.barrier()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 def run_ours(args, wl):
@@ -332,7 +331,10 @@ def run_ours(args, wl):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     torch.cuda.set_device(local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        import datetime
+        # a short timeout: a rank that dies must fail the others' next collective, not park them
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local),
+                                timeout=datetime.timedelta(seconds=120))
     dev = torch.device("cuda", local)
     be = larql_b200.CudaBackend(local)
     ext = torch.cuda.ExternalStream(be.stream(), device=dev)
