@@ -118,6 +118,32 @@ LQ_API int lq_q4k_matmul(lq_ctx* ctx, const uint8_t* w, size_t w_len, const floa
 LQ_API int lq_q4k_matvec_exact(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len,
                                size_t num_rows, size_t hidden, float* out, size_t out_len);
 
+/* Dense gemv of one block-format matrix (any of the four formats): out[n] = W[n,k] . x[k].
+ * exact = 0: fast path (integer / table dots, error within the bound the walk uses);
+ * exact = 1: the CPU backend's f32 order, bit-identical to q8_0_gemv
+ * (crates/larql-compute/src/cpu/kquant_gemv.rs:67-109), nvfp4_gemv (cpu/nvfp4_gemv.rs:29-65), the
+ * MXFP4 test loop (crates/larql-vindex/src/format/vindex3/opplan/exec/tests/device.rs:105-127) and
+ * q4k_matvec.  Refuses (LQ_REFUSED_SHAPE) where those return None. */
+LQ_API int lq_gemv(lq_ctx* ctx, const lq_matrix* m, const float* x, size_t x_len, float* out, size_t out_len,
+                   int exact);
+/* QuantMatVec::q8_0_gemv (backend/quant_matvec.rs:378-395): blocks [n, k/32, 34]. */
+LQ_API int lq_q8_0_gemv(lq_ctx* ctx, const uint8_t* blocks, size_t blocks_len, const float* x, size_t x_len, size_t n,
+                        size_t k, float* out);
+/* MatMul::mxfp4_gemv (backend/matmul.rs:226-235): packed [n, k/2], e8m0 scales [n, k/32]. */
+LQ_API int lq_mxfp4_gemv(lq_ctx* ctx, const uint8_t* packed, size_t packed_len, const uint8_t* scales,
+                         size_t scales_len, const float* x, size_t x_len, size_t n, size_t k, float* out);
+/* QuantMatVec::nvfp4_gemv (backend/quant_matvec.rs:397-427): packed [n, k/2], e4m3 scales [n, k/16]. */
+LQ_API int lq_nvfp4_gemv(lq_ctx* ctx, const uint8_t* packed, size_t packed_len, const uint8_t* scales,
+                         size_t scales_len, float tensor_scale, const float* x, size_t x_len, size_t n, size_t k,
+                         float* out);
+
+/* MoE routing (crates/larql-compute/src/cpu/ops/moe/math.rs:130-164, mod.rs:127-189): per token a
+ * max-subtracted softmax over n_experts logits, the top_k experts by probability (ties to the lower
+ * index, descending), weights renormalised over the selected when renormalise != 0.
+ * logits [n_tokens, n_experts]; idx_out, w_out [n_tokens, min(top_k, n_experts)].  n_experts <= 256. */
+LQ_API int lq_moe_route(lq_ctx* ctx, const float* logits, size_t n_tokens, size_t n_experts, size_t top_k,
+                        int renormalise, uint32_t* idx_out, float* w_out);
+
 /* top_k_by_abs (crates/larql-vindex/src/index/compute/gate_knn/mod.rs:50-108): the top_k largest
  * |score|, ties to the lower index, sorted by |score| descending then index.  *count = min(top_k, n).
  * LQ_ERR_NAN_SCORE if a score is NaN. */
@@ -202,6 +228,15 @@ LQ_API int lq_dev_shard_classify(lq_ctx* ctx, const lq_matrix* gate_shard, uint3
 LQ_API int lq_dev_shard_gather(lq_ctx* ctx, const lq_matrix* up_shard, const lq_matrix* down_shard,
                                const int32_t* packs, int world, int rank, size_t cap, size_t top_k,
                                size_t row_offset, float* out_partial);
+
+/* MoE expert walk (cpu_moe_forward's combine, crates/larql-compute/src/cpu/ops/moe/forward.rs:24-140,
+ * over walked experts): out[t] = sum_j w[t,j] * walk(expert idx[t,j], x[t]) with lq_moe_route's
+ * selection and lq_walk_ffn's per-expert top_k.  gates/ups/downs_fm: n_experts matrices each.
+ * flags: LQ_WALK_FORCE_SPARSE only.  expert_idx_out / expert_w_out may be NULL. */
+LQ_API int lq_moe_walk_ffn(lq_ctx* ctx, const lq_matrix* gates, const lq_matrix* ups, const lq_matrix* downs_fm,
+                           size_t n_experts, const float* logits, const float* x, size_t batch, size_t top_e,
+                           int renormalise, size_t top_k, uint32_t flags, float* out, uint32_t* expert_idx_out,
+                           float* expert_w_out);
 
 /* ---- allocation-free entry point ---------------------------------------------------- */
 /* Has no counterpart in the reference.  A Q4_K matvec (same arithmetic and kernels as

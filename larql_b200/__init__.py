@@ -36,7 +36,8 @@ EXPORTS = [
     "lq_topk_abs", "lq_rms_norm", "lq_dequantize", "lq_walk_ffn", "lq_dev_q4k_matvec", "lq_dev_walk_ffn",
     "lq_stack_create", "lq_stack_run", "lq_stack_destroy", "lq_last_walk_stats", "lq_dev_quantize_q4k",
     "lq_profile_walk", "lq_fused_phase_us", "lq_q4k_matvec_static", "lq_dev_shard_scan", "lq_dev_shard_classify",
-    "lq_dev_shard_gather",
+    "lq_dev_shard_gather", "lq_gemv", "lq_q8_0_gemv", "lq_mxfp4_gemv", "lq_nvfp4_gemv", "lq_moe_route",
+    "lq_moe_walk_ffn",
 ]
 
 
@@ -99,6 +100,13 @@ def load_library() -> C.CDLL:
         "lq_dev_shard_scan": (C.c_int, [vp, mp, f32p, C.c_uint32, C.c_int, C.c_int, vp]),
         "lq_dev_shard_classify": (C.c_int, [vp, mp, vp, C.c_int, sz, sz, vp, sz]),
         "lq_dev_shard_gather": (C.c_int, [vp, mp, mp, vp, C.c_int, C.c_int, sz, sz, sz, f32p]),
+        "lq_gemv": (C.c_int, [vp, mp, f32p, sz, f32p, sz, C.c_int]),
+        "lq_q8_0_gemv": (C.c_int, [vp, vp, sz, f32p, sz, sz, sz, f32p]),
+        "lq_mxfp4_gemv": (C.c_int, [vp, vp, sz, vp, sz, f32p, sz, sz, sz, f32p]),
+        "lq_nvfp4_gemv": (C.c_int, [vp, vp, sz, vp, sz, C.c_float, f32p, sz, sz, sz, f32p]),
+        "lq_moe_route": (C.c_int, [vp, f32p, sz, sz, sz, C.c_int, u32p, f32p]),
+        "lq_moe_walk_ffn": (C.c_int, [vp, mp, mp, mp, sz, f32p, f32p, sz, sz, C.c_int, sz, C.c_uint32, f32p, u32p,
+                                      f32p]),
         "lq_q4k_matvec_static": (C.c_int, [vp, sz, f32p, sz, sz, f32p, vp, C.c_char_p, sz]),
     }
     for name, (res, args) in sig.items():
@@ -249,10 +257,74 @@ class CudaBackend:
         return out.reshape(seq_len, num_rows) if ok else None
 
     def quant_matvec(self, fmt: int, weights, x, num_rows: int, hidden: int):
-        """Format-dispatched matvec (quant_matvec.rs:50-98): Q4_K only through this signature."""
+        """Format-dispatched matvec (quant_matvec.rs:50-98): formats that are one byte slice."""
         if fmt == FMT_Q4_K:
             return self.q4k_matvec(weights, x, num_rows, hidden)
+        if fmt == FMT_Q8_0:
+            return self.q8_0_gemv(weights, x, num_rows, hidden)
         return None
+
+    def gemv(self, m: "HostMatrix", x, exact: bool = False):
+        """out[rows] = m . x for any of the four formats; exact=True is the CPU backend's f32 order."""
+        x = _f32(x).reshape(-1)
+        out = np.empty(m.rows, np.float32)
+        mc = m.c()
+        ok = self._status(self._lib.lq_gemv(self._h, C.byref(mc), _ptr(x), x.size, _ptr(out), out.size, int(exact)))
+        return out if ok else None
+
+    def q8_0_gemv(self, blocks, x, n: int, k: int):
+        """QuantMatVec::q8_0_gemv: None on any geometry mismatch."""
+        w, x = _u8(blocks), _f32(x)
+        out = np.empty(n, np.float32)
+        ok = self._status(self._lib.lq_q8_0_gemv(self._h, _ptr(w), w.size, _ptr(x), x.size, n, k, _ptr(out)))
+        return out if ok else None
+
+    def mxfp4_gemv(self, packed, scales, x, n: int, k: int):
+        """MatMul::mxfp4_gemv."""
+        w, sc, x = _u8(packed), _u8(scales), _f32(x)
+        out = np.empty(n, np.float32)
+        ok = self._status(self._lib.lq_mxfp4_gemv(self._h, _ptr(w), w.size, _ptr(sc), sc.size, _ptr(x), x.size, n, k,
+                                                  _ptr(out)))
+        return out if ok else None
+
+    def nvfp4_gemv(self, packed, scales, tensor_scale: float, x, n: int, k: int):
+        """QuantMatVec::nvfp4_gemv: None on any geometry mismatch."""
+        w, sc, x = _u8(packed), _u8(scales), _f32(x)
+        out = np.empty(n, np.float32)
+        ok = self._status(self._lib.lq_nvfp4_gemv(self._h, _ptr(w), w.size, _ptr(sc), sc.size, float(tensor_scale),
+                                                  _ptr(x), x.size, n, k, _ptr(out)))
+        return out if ok else None
+
+    # -- MoE --------------------------------------------------------------------
+    def moe_route(self, logits, top_k: int, renormalise: bool = True):
+        """softmax -> top-k experts (value desc, index asc) -> weights; logits [tokens, experts]."""
+        lg = _f32(logits)
+        lg = lg.reshape(-1, lg.shape[-1])
+        t, e = lg.shape
+        k = min(int(top_k), e)
+        idx = np.zeros((t, max(k, 1)), np.uint32)
+        w = np.zeros((t, max(k, 1)), np.float32)
+        ok = self._status(self._lib.lq_moe_route(self._h, _ptr(lg), t, e, int(top_k), int(renormalise), idx.ctypes.data,
+                                                 w.ctypes.data))
+        return (idx[:, :k], w[:, :k]) if ok else None
+
+    def moe_walk_ffn(self, gates, ups, downs, logits, x, top_e: int, top_k: int, renormalise: bool = True,
+                     flags: int = 0):
+        """out[t] = sum over the token's top_e experts of w * walk(expert, x[t]); returns (out, idx, w)."""
+        x = _f32(x)
+        x2 = x.reshape(-1, x.shape[-1])
+        lg = _f32(logits).reshape(x2.shape[0], -1)
+        ne = len(gates)
+        arr = lambda ms: (LqMatrix * ne)(*[m.c() for m in ms])
+        ga, ua, da = arr(gates), arr(ups), arr(downs)
+        ke = min(int(top_e), ne)
+        out = np.empty_like(x2)
+        idx = np.zeros((x2.shape[0], max(ke, 1)), np.uint32)
+        w = np.zeros((x2.shape[0], max(ke, 1)), np.float32)
+        ok = self._status(self._lib.lq_moe_walk_ffn(self._h, ga, ua, da, ne, _ptr(lg), _ptr(x2), x2.shape[0], int(top_e),
+                                                    int(renormalise), int(top_k), int(flags), _ptr(out),
+                                                    idx.ctypes.data, w.ctypes.data))
+        return (out.reshape(x.shape), idx[:, :ke], w[:, :ke]) if ok else None
 
     # -- selection, norm, decode ----------------------------------------------
     def top_k_by_abs(self, scores, top_k: int):

@@ -303,13 +303,81 @@ float bound_c1(int hidden) {
     return (float)(n * u / (1.0 - n * u) * 1.01);
 }
 
+FmtMat fmtmat_of(const lq_matrix& m) {
+    return FmtMat{m.fmt & 0xff, (const uint8_t*)m.data, (const uint8_t*)m.scales, m.tensor_scale, (int)m.rows,
+                  (int)m.cols};
+}
+
+// The format kernels load whole blocks with vector loads: 2 / 16 / 8 byte alignment of the base.
+bool fmt_aligned(const lq_matrix& m) {
+    const uintptr_t a = (uintptr_t)m.data;
+    switch (m.fmt & 0xff) {
+        case LQ_FMT_Q8_0: return (a & 1) == 0;
+        case LQ_FMT_MXFP4: return (a & 15) == 0;
+        case LQ_FMT_NVFP4: return (a & 7) == 0;
+    }
+    return true;
+}
+
+// Reference rows of Q8_0 / MXFP4 / NVFP4 are one f32 chain over the whole row: hidden + 3 roundings
+// on a term's path; the fast path has at most 64.
+float bound_c1_fmt(int hidden) {
+    const double u = std::ldexp(1.0, -24);
+    const double n = (double)hidden + 3.0 + 64.0;
+    return (float)(n * u / (1.0 - n * u) * 1.01);
+}
+
+__global__ void scaled_add_kernel(float* __restrict__ out, const float* __restrict__ src, const float* __restrict__ w,
+                                  int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = fmaf(*w, src[i], out[i]);
+}
+
+// Walk of one prepared token for Q8_0 / MXFP4 / NVFP4 (separate kernels).
+int enqueue_walk_token_fmt(lq_ctx* ctx, const lq_matrix& gate, const lq_matrix& up, const lq_matrix& down, size_t t,
+                           int k, const float* residual, float* out) {
+    if (!fmt_aligned(gate) || !fmt_aligned(up) || !fmt_aligned(down))
+        return fail(ctx, LQ_REFUSED_UNSUPPORTED, "walk: weight base address not block aligned");
+    TokenWs& w = ctx->tok[t];
+    const int N = (int)gate.rows, H = (int)gate.cols;
+    const FmtMat g = fmtmat_of(gate), u = fmtmat_of(up), d = fmtmat_of(down);
+    const XPrep xp = xprep_of(w);
+    const bool sparse = k < N;
+    cudaStream_t st = ctx->stream;
+    CK(launch_scan_fmt(g, xp, w.scores, sparse ? w.hist : nullptr, &w.sel->bound_bits, bound_c1_fmt(H), ctx->d_err,
+                       ctx->sm_count, st));
+    if (sparse) {
+        CK(launch_classify(w.scores, N, k, w, ctx->d_err, st));
+        CK(launch_rescore_fmt(g, w.xn, w.band_idx, &w.sel->n_band, 0, w.band_exact, ctx->sm_count, st));
+        CK(launch_final_pick(w, ctx->d_err, st));
+        ctx->launches += 3;
+    } else {
+        CK(launch_select(w.scores, N, k, w, ctx->d_err, st));
+        ctx->launches += 1;
+    }
+    CK(launch_gather_fmt(u, d, xp, w.hit_idx, w.hit_score, &w.sel->n_sel, k, ctx->partials, ctx->gather_grid, st));
+    CK(launch_finish(ctx->partials, ctx->gather_grid, H, residual, out, st));
+    ctx->launches += 3;
+    return LQ_OK;
+}
+
 // Enqueue the walk of one prepared token.
 int enqueue_walk_token(lq_ctx* ctx, const lq_matrix& gate, const lq_matrix& up, const lq_matrix& down, size_t t,
                        size_t top_k, const float* residual, float* out) {
-    if (gate.fmt != LQ_FMT_Q4_K || up.fmt != LQ_FMT_Q4_K || down.fmt != LQ_FMT_Q4_K)
-        return fail(ctx, LQ_REFUSED_UNSUPPORTED, "walk: format not implemented");
+    if (gate.fmt != up.fmt || gate.fmt != down.fmt)
+        return fail(ctx, LQ_REFUSED_UNSUPPORTED, "walk: gate/up/down formats differ");
     TokenWs& w = ctx->tok[t];
     const int N = (int)gate.rows, H = (int)gate.cols;
+    if (gate.fmt != LQ_FMT_Q4_K) {
+        const int kk = (int)std::min<size_t>(top_k, (size_t)N);
+        if (kk == 0) {
+            CK(cudaMemsetAsync(w.sel, 0, sizeof(SelHeader), ctx->stream));
+            if (residual) CK(cudaMemcpyAsync(out, residual, (size_t)H * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+            else CK(cudaMemsetAsync(out, 0, (size_t)H * 4, ctx->stream));
+            return LQ_OK;
+        }
+        return enqueue_walk_token_fmt(ctx, gate, up, down, t, kk, residual, out);
+    }
     const Q4kMat g{(const uint8_t*)gate.data, N, H}, u{(const uint8_t*)up.data, N, H},
         d{(const uint8_t*)down.data, N, H};
     const XPrep xp = xprep_of(w);
@@ -352,6 +420,7 @@ int dev_walk(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const lq_m
         return fail(ctx, LQ_REFUSED_SHAPE, "walk: gate/up/down shapes differ");
     if (batch == 0 || H == 0) return LQ_OK;
     if (H > 16384) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "walk: hidden > 16384");
+    if (H % 32 != 0) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "walk: hidden not a multiple of 32");
     int rc = ensure_ws(ctx, batch, H, N);
     if (rc) return rc;
     const size_t k = effective_k(top_k, N, flags);
@@ -453,7 +522,7 @@ int lq_device_info(lq_ctx* ctx, char* buf, size_t cap) {
 
 int lq_supports_quant(lq_ctx* ctx, int fmt) {
     (void)ctx;
-    return fmt == LQ_FMT_Q4_K ? 1 : 0;
+    return (fmt == LQ_FMT_Q4_K || fmt == LQ_FMT_Q8_0 || fmt == LQ_FMT_MXFP4 || fmt == LQ_FMT_NVFP4) ? 1 : 0;
 }
 
 int lq_synchronize(lq_ctx* ctx) {
@@ -564,6 +633,79 @@ int lq_q4k_matvec_exact(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float
 int lq_q4k_matmul(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t num_rows,
                   size_t hidden, size_t seq_len, float* out, size_t out_len) {
     return q4k_host_common(ctx, w, w_len, x, x_len, num_rows, hidden, seq_len, out, out_len, 0);
+}
+
+// Dense gemv of one block-format matrix (host pointers): fast path, or the reference's exact order.
+int lq_gemv(lq_ctx* ctx, const lq_matrix* m, const float* x, size_t x_len, float* out, size_t out_len, int exact) {
+    if (!ctx) return LQ_ERR_ARGUMENT;
+    int rc = check_matrix(ctx, m, "gemv");
+    if (rc) return rc;
+    const int fmt = m->fmt & 0xff;
+    const size_t n = (size_t)m->rows, k = (size_t)m->cols;
+    if (fmt == LQ_FMT_Q4_K)
+        return q4k_host_common(ctx, (const uint8_t*)m->data, m->data_len, x, x_len, n, k, 1, out, out_len, exact);
+    if (x_len != k || out_len != n) return fail(ctx, LQ_REFUSED_SHAPE, "gemv: x_len != k or out_len != n");
+    if (n == 0) return LQ_OK;
+    if (k % 32 != 0 || k > 16384) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "gemv: k must be a multiple of 32, <= 16384");
+    lq_matrix dm;
+    rc = resolve_matrix(ctx, m, &dm);
+    if (rc) return rc;
+    if (!fmt_aligned(dm)) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "gemv: weight base address not block aligned");
+    rc = ensure_ws(ctx, 1, k, 32);
+    if (rc) return rc;
+    rc = ensure_stage(ctx, (k + n) * 4 + 512);
+    if (rc) return rc;
+    float* dx = (float*)ctx->stage;
+    float* dout = (float*)(ctx->stage + a256(k * 4));
+    TokenWs& t = ctx->tok[0];
+    CK(cudaMemcpyAsync(dx, x, k * 4, cudaMemcpyHostToDevice, ctx->stream));
+    const FmtMat fm = fmtmat_of(dm);
+    if (exact) {
+        CK(launch_rescore_fmt(fm, dx, nullptr, nullptr, (int)n, dout, ctx->sm_count, ctx->stream));
+        ctx->launches += 1;
+    } else {
+        launch_prep(dx, 1, (int)k, 0, 0.0, t.xn, t.xa, t.xb, t.bscale, t.bsum, t.babs, 0, nullptr, ctx->stream);
+        CK(cudaGetLastError());
+        CK(launch_scan_fmt(fm, xprep_of(t), dout, nullptr, nullptr, 0.0f, ctx->d_err, ctx->sm_count, ctx->stream));
+        ctx->launches += 2;
+    }
+    CK(cudaMemcpyAsync(out, dout, n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return lq_synchronize(ctx);
+}
+
+int lq_q8_0_gemv(lq_ctx* ctx, const uint8_t* blocks, size_t blocks_len, const float* x, size_t x_len, size_t n,
+                 size_t k, float* out) {
+    const lq_matrix m{LQ_FMT_Q8_0, blocks, blocks_len, nullptr, 0, 1.0f, (int64_t)n, (int64_t)k};
+    return lq_gemv(ctx, &m, x, x_len, out, n, 0);
+}
+int lq_mxfp4_gemv(lq_ctx* ctx, const uint8_t* packed, size_t packed_len, const uint8_t* scales, size_t scales_len,
+                  const float* x, size_t x_len, size_t n, size_t k, float* out) {
+    const lq_matrix m{LQ_FMT_MXFP4, packed, packed_len, scales, scales_len, 1.0f, (int64_t)n, (int64_t)k};
+    return lq_gemv(ctx, &m, x, x_len, out, n, 0);
+}
+int lq_nvfp4_gemv(lq_ctx* ctx, const uint8_t* packed, size_t packed_len, const uint8_t* scales, size_t scales_len,
+                  float tensor_scale, const float* x, size_t x_len, size_t n, size_t k, float* out) {
+    const lq_matrix m{LQ_FMT_NVFP4, packed, packed_len, scales, scales_len, tensor_scale, (int64_t)n, (int64_t)k};
+    return lq_gemv(ctx, &m, x, x_len, out, n, 0);
+}
+
+int lq_moe_route(lq_ctx* ctx, const float* logits, size_t n_tokens, size_t n_experts, size_t top_k, int renormalise,
+                 uint32_t* idx_out, float* w_out) {
+    if (!ctx || !logits || !idx_out || !w_out) return LQ_ERR_ARGUMENT;
+    if (n_experts == 0 || n_experts > 256) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "moe_route: 1..256 experts");
+    if (n_tokens == 0 || top_k == 0) return LQ_OK;
+    const size_t k = std::min(top_k, n_experts);
+    int rc = ensure_stage(ctx, a256(n_tokens * n_experts * 4) + 2 * a256(n_tokens * k * 4));
+    if (rc) return rc;
+    float* dl = (float*)ctx->stage;
+    uint32_t* di = (uint32_t*)(ctx->stage + a256(n_tokens * n_experts * 4));
+    float* dw = (float*)((uint8_t*)di + a256(n_tokens * k * 4));
+    CK(cudaMemcpyAsync(dl, logits, n_tokens * n_experts * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CK(launch_moe_route(dl, (int)n_tokens, (int)n_experts, (int)k, renormalise, di, dw, ctx->stream));
+    ctx->launches += 1;
+    CK(cudaMemcpyAsync(idx_out, di, n_tokens * k * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CK(cudaMemcpyAsync(w_out, dw, n_tokens * k * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return lq_synchronize(ctx);
 }
 
 int lq_topk_abs(lq_ctx* ctx, const float* scores, size_t n, size_t top_k, uint32_t* idx_out, float* val_out,
@@ -690,6 +832,65 @@ int lq_walk_ffn(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const l
         }
     }
     return LQ_OK;
+}
+
+// MoE expert walk: route each token to its top experts, walk each selected expert's
+// gate/up/down with the per-expert top-K, combine with the routing weights.
+int lq_moe_walk_ffn(lq_ctx* ctx, const lq_matrix* gates, const lq_matrix* ups, const lq_matrix* downs_fm,
+                    size_t n_experts, const float* logits, const float* x, size_t batch, size_t top_e, int renormalise,
+                    size_t top_k, uint32_t flags, float* out, uint32_t* expert_idx_out, float* expert_w_out) {
+    if (!ctx || !gates || !ups || !downs_fm || !logits || !x || !out) return LQ_ERR_ARGUMENT;
+    if (n_experts == 0 || n_experts > 256) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "moe_walk: 1..256 experts");
+    if (flags & (LQ_WALK_RMSNORM | LQ_WALK_RESIDUAL))
+        return fail(ctx, LQ_REFUSED_UNSUPPORTED, "moe_walk: norm/residual belong to the caller");
+    int rc;
+    std::vector<lq_matrix> g(n_experts), u(n_experts), d(n_experts);
+    for (size_t e = 0; e < n_experts; ++e) {
+        if ((rc = check_matrix(ctx, gates + e, "gate")) || (rc = check_matrix(ctx, ups + e, "up")) ||
+            (rc = check_matrix(ctx, downs_fm + e, "down")))
+            return rc;
+        if (gates[e].cols != gates[0].cols) return fail(ctx, LQ_REFUSED_SHAPE, "moe_walk: experts differ in hidden");
+        if ((rc = resolve_matrix(ctx, gates + e, &g[e])) || (rc = resolve_matrix(ctx, ups + e, &u[e])) ||
+            (rc = resolve_matrix(ctx, downs_fm + e, &d[e])))
+            return rc;
+    }
+    const size_t H = (size_t)gates[0].cols, ke = std::min(top_e, n_experts);
+    if (batch == 0 || H == 0) return LQ_OK;
+    const size_t lb = a256(batch * n_experts * 4), rb = a256(batch * std::max<size_t>(ke, 1) * 4), xb = a256(batch * H * 4);
+    rc = ensure_stage(ctx, lb + 2 * rb + 2 * xb + a256(H * 4));
+    if (rc) return rc;
+    float* dl = (float*)ctx->stage;
+    uint32_t* di = (uint32_t*)(ctx->stage + lb);
+    float* dw = (float*)(ctx->stage + lb + rb);
+    float* dx = (float*)(ctx->stage + lb + 2 * rb);
+    float* dout = (float*)(ctx->stage + lb + 2 * rb + xb);
+    float* dtmp = (float*)(ctx->stage + lb + 2 * rb + 2 * xb);
+    CK(cudaMemcpyAsync(dl, logits, batch * n_experts * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CK(cudaMemcpyAsync(dx, x, batch * H * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CK(cudaMemsetAsync(dout, 0, batch * H * 4, ctx->stream));
+    std::vector<uint32_t> hi(batch * ke);
+    if (ke) {
+        CK(launch_moe_route(dl, (int)batch, (int)n_experts, (int)ke, renormalise, di, dw, ctx->stream));
+        ctx->launches += 1;
+        CK(cudaMemcpyAsync(hi.data(), di, batch * ke * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        if (expert_w_out) CK(cudaMemcpyAsync(expert_w_out, dw, batch * ke * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        CK(cudaStreamSynchronize(ctx->stream));
+        if (expert_idx_out) memcpy(expert_idx_out, hi.data(), batch * ke * 4);
+    }
+    for (size_t t = 0; t < batch; ++t) {
+        for (size_t j = 0; j < ke; ++j) {
+            const uint32_t e = hi[t * ke + j];
+            if (e >= n_experts) return fail(ctx, LQ_ERR_CUDA, "moe_walk: router returned a bad expert");
+            rc = dev_walk(ctx, &g[e], &u[e], &d[e], dx + t * H, 1, top_k, flags, dtmp, nullptr, nullptr);
+            if (rc) return rc;
+            scaled_add_kernel<<<(unsigned)((H + 255) / 256), 256, 0, ctx->stream>>>(dout + t * H, dtmp, dw + t * ke + j,
+                                                                                  (int)H);
+            CK(cudaGetLastError());
+            ctx->launches += 1;
+        }
+    }
+    CK(cudaMemcpyAsync(out, dout, batch * H * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return lq_synchronize(ctx);
 }
 
 int lq_fused_phase_us(lq_ctx* ctx, float* us, size_t n) {

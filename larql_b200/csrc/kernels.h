@@ -47,6 +47,27 @@ struct Q4kMat {
     int cols;
 };
 
+// A block-format matrix other than Q4_K (device pointers).
+struct FmtMat {
+    int fmt;               // LQ_FMT_Q8_0 / LQ_FMT_MXFP4 / LQ_FMT_NVFP4
+    const uint8_t* data;   // blocks or packed codes
+    const uint8_t* scales; // MXFP4 e8m0 / NVFP4 e4m3 stream
+    float ts;              // NVFP4 tensor scale
+    int rows, cols;
+};
+
+// fmt_kernels.cu
+cudaError_t launch_scan_fmt(const FmtMat& m, const XPrep& xp, float* scores, uint32_t* hist, uint32_t* bound_bits,
+                            float c1, int* err, int sm_count, cudaStream_t st);
+cudaError_t launch_rescore_fmt(const FmtMat& m, const float* xn, const uint32_t* rows_idx, const int* n_rows_dev,
+                               int n_rows_host, float* out, int sm_count, cudaStream_t st);
+cudaError_t launch_gather_fmt(const FmtMat& up, const FmtMat& down, const XPrep& xp, const uint32_t* hit_idx,
+                              const float* hit_score, const int* n_hits_dev, int n_hits_host, float* partials,
+                              int grid, cudaStream_t st);
+// moe.cu: softmax over all experts, top-k by (value desc, index asc), optional renormalisation
+cudaError_t launch_moe_route(const float* logits, int n_tokens, int n_experts, int top_k, int renormalise,
+                             uint32_t* idx_out, float* w_out, cudaStream_t st);
+
 // prep.cu
 void launch_prep(const float* x_in, int batch, int hidden, int apply_norm, double eps, float* xn, uint32_t* xa,
                  uint32_t* xb, float* bscale, float* bsum, float* babs, size_t token_stride_f, int* err,

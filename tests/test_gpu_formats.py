@@ -1,0 +1,195 @@
+"""GPU parity tests for the Q8_0 / MXFP4 / NVFP4 paths and the MoE router, through the C ABI,
+against the CPU oracle.
+
+Bar: exact-order gemv bit-identical to the CPU backend's arithmetic, top-K index sets exact,
+walk outputs within 1e-3 relative L2 (f32), router selections exact and weights within 1e-6."""
+import numpy as np
+import pytest
+
+import oracle
+from conftest import bits, rel_l2, seeded_weights, seeded_x
+
+pytestmark = pytest.mark.gpu
+
+OUT_TOL = 1e-3
+FMTS = [oracle.FMT_Q8_0, oracle.FMT_MXFP4, oracle.FMT_NVFP4]
+NAMES = {oracle.FMT_Q8_0: "q8_0", oracle.FMT_MXFP4: "mxfp4", oracle.FMT_NVFP4: "nvfp4"}
+
+
+@pytest.fixture(scope="module")
+def be():
+    import larql_b200
+    b = larql_b200.CudaBackend(0)
+    yield b
+    b.close()
+
+
+@pytest.fixture(autouse=True)
+def _fresh_weight_cache(be):
+    yield
+    be.drop_weight_regions()
+
+
+def host(m: oracle.Matrix):
+    import larql_b200
+    return larql_b200.HostMatrix(m.fmt, m.rows, m.cols, m.data, m.scales, float(m.tensor_scale))
+
+
+def layer(seed, n, h, fmt):
+    return [oracle.quantize_matrix(fmt, seeded_weights(seed + i, n, h)) for i in range(3)]
+
+
+def test_supports_all_four_formats(be):
+    for f in (oracle.FMT_Q4_K, *FMTS):
+        assert be.supports_quant(f)
+
+
+@pytest.mark.parametrize("fmt", FMTS, ids=NAMES.get)
+@pytest.mark.parametrize("rows,cols", [(1, 32), (37, 512), (300, 2880), (1024, 1024), (96, 8192)])
+def test_exact_gemv_is_bit_identical_to_cpu_backend(be, fmt, rows, cols):
+    m = oracle.quantize_matrix(fmt, seeded_weights(rows * 7 + cols + fmt, rows, cols))
+    x = seeded_x(cols + rows, cols)
+    got = be.gemv(host(m), x, exact=True)
+    assert bits(got).tolist() == bits(m.gemv(x)).tolist()
+
+
+@pytest.mark.parametrize("fmt", FMTS, ids=NAMES.get)
+@pytest.mark.parametrize("rows,cols", [(37, 512), (3072, 1024), (300, 2880), (10240, 2560)])
+def test_fast_gemv_within_tolerance_and_deterministic(be, fmt, rows, cols):
+    m = oracle.quantize_matrix(fmt, seeded_weights(rows + cols + fmt, rows, cols))
+    x = seeded_x(cols, cols)
+    got = be.gemv(host(m), x)
+    want = m.gemv(x)
+    scale = np.abs(m.dequantize()).astype(np.float64) @ np.abs(x).astype(np.float64)
+    assert np.max(np.abs(got.astype(np.float64) - want) / scale) < 2e-4   # fixed-point planes: ~2^-15 of sum|w||x|
+    assert rel_l2(got, want) < OUT_TOL
+    assert np.array_equal(bits(got), bits(be.gemv(host(m), x)))
+
+
+def test_trait_shaped_gemv_entry_points_and_refusals(be):
+    x = seeded_x(5, 512)
+    q8 = oracle.quantize_matrix(oracle.FMT_Q8_0, seeded_weights(1, 40, 512))
+    mx = oracle.quantize_matrix(oracle.FMT_MXFP4, seeded_weights(2, 40, 512))
+    nv = oracle.quantize_matrix(oracle.FMT_NVFP4, seeded_weights(3, 40, 512))
+    assert rel_l2(be.q8_0_gemv(q8.data, x, 40, 512), q8.gemv(x)) < OUT_TOL
+    assert rel_l2(be.quant_matvec(oracle.FMT_Q8_0, q8.data, x, 40, 512), q8.gemv(x)) < OUT_TOL
+    assert rel_l2(be.mxfp4_gemv(mx.data, mx.scales, x, 40, 512), mx.gemv(x)) < OUT_TOL
+    assert rel_l2(be.nvfp4_gemv(nv.data, nv.scales, float(nv.tensor_scale), x, 40, 512), nv.gemv(x)) < OUT_TOL
+    # exact-length rules of q8_0_gemv / nvfp4_gemv: any mismatch is a refusal (None), as on the CPU backend
+    assert be.q8_0_gemv(q8.data[:-1], x, 40, 512) is None
+    assert be.q8_0_gemv(q8.data, x[:-1], 40, 512) is None
+    assert be.q8_0_gemv(q8.data, x, 39, 512) is None
+    assert be.nvfp4_gemv(nv.data, nv.scales[:-1], float(nv.tensor_scale), x, 40, 512) is None
+    assert be.nvfp4_gemv(nv.data, nv.scales, float(nv.tensor_scale), x, 40, 500) is None
+    # n == 0: empty result
+    assert be.q8_0_gemv(np.zeros(0, np.uint8), x, 0, 512).size == 0
+
+
+def _check_walk(be, gate, up, down, x, k, flags=4):
+    out, hits = be.walk_ffn(host(gate), host(up), host(down), x, k, flags)
+    x2, out2 = x.reshape(-1, gate.cols), out.reshape(-1, gate.cols)
+    for t in range(x2.shape[0]):
+        want, idx, _ = oracle.walk_token(gate, up, down, x2[t], k)
+        assert sorted(hits[t].tolist()) == sorted(idx.tolist()), f"token {t}: top-K index set differs"
+        assert rel_l2(out2[t], want) < OUT_TOL, f"token {t}"
+    return out, hits
+
+
+@pytest.mark.parametrize("fmt", FMTS, ids=NAMES.get)
+@pytest.mark.parametrize("h,n,k", [(256, 64, 8), (512, 300, 37), (1024, 3072, 512), (2880, 2880, 768),
+                                   (3840, 2048, 256), (8192, 1024, 128)])
+def test_walk_index_sets_exact_and_outputs_within_tolerance(be, fmt, h, n, k):
+    gate, up, down = layer(h + n + fmt, n, h, fmt)
+    for q in range(2):
+        x = oracle.rms_norm(seeded_x(0x5EED0000 + q, h))
+        _check_walk(be, gate, up, down, x, k)
+    st = be.last_walk_stats()
+    assert st.n_hits == min(k, n) and st.n_certain + st.need == k and st.n_band >= st.need
+
+
+@pytest.mark.parametrize("fmt", FMTS, ids=NAMES.get)
+def test_walk_edge_cases(be, fmt):
+    import larql_b200
+    gate, up, down = layer(77 + fmt, 96, 256, fmt)
+    x = oracle.rms_norm(seeded_x(78, 256))
+    F = larql_b200.WALK_FORCE_SPARSE
+    out, hits = be.walk_ffn(host(gate), host(up), host(down), x, 1000, F)
+    assert sorted(hits[0].tolist()) == list(range(96))
+    assert rel_l2(out, oracle.walk_token(gate, up, down, x, 1000)[0]) < OUT_TOL
+    out_d, hits_d = be.walk_ffn(host(gate), host(up), host(down), x, 80, 0)      # 80 % rule: dense
+    assert len(hits_d[0]) == 96 and rel_l2(out_d, oracle.walk_token_dense(gate, up, down, x)) < OUT_TOL
+    out0, hits0 = be.walk_ffn(host(gate), host(up), host(down), x, 0, F)
+    assert len(hits0[0]) == 0 and not out0.any()
+    outz, hitsz = be.walk_ffn(host(gate), host(up), host(down), np.zeros(256, np.float32), 10, F)
+    assert sorted(hitsz[0].tolist()) == list(range(10)) and not outz.any()
+    # duplicated gate rows: exact ties across the boundary resolve to the lower index
+    rb = gate.row_bytes()
+    sc = None if gate.scales is None else np.tile(gate.scales[:gate.scales.size // 96], 96)
+    g2 = oracle.Matrix(gate.fmt, 96, 256, np.tile(gate.data[:rb], 96), sc, gate.tensor_scale)
+    _, hits_t = be.walk_ffn(host(g2), host(up), host(down), x, 7, F)
+    assert sorted(hits_t[0].tolist()) == list(range(7))
+    xn = x.copy()
+    xn[5] = np.nan
+    with pytest.raises(larql_b200.BackendError):
+        be.walk_ffn(host(gate), host(up), host(down), xn, 8, F)
+    q4 = oracle.quantize_matrix(oracle.FMT_Q4_K, seeded_weights(1, 96, 256))
+    assert be.walk_ffn(host(gate), host(q4), host(down), x, 8) is None              # mixed formats refused
+
+
+@pytest.mark.parametrize("fmt", FMTS, ids=NAMES.get)
+def test_run_ffn_norm_residual_and_batch(be, fmt):
+    import larql_b200
+    gate, up, down = layer(91 + fmt, 512, 1024, fmt)
+    hin = seeded_x(92, 3, 1024)
+    flags = larql_b200.WALK_RMSNORM | larql_b200.WALK_RESIDUAL | larql_b200.WALK_FORCE_SPARSE
+    out, hits = be.walk_ffn(host(gate), host(up), host(down), hin, 64, flags)
+    for t in range(3):
+        want, idx = oracle.run_ffn_token(gate, up, down, hin[t], 64)
+        assert sorted(hits[t].tolist()) == sorted(idx.tolist())
+        assert rel_l2(out[t] - hin[t], want - hin[t]) < OUT_TOL
+
+
+# ------------------------------------------------------------------------- MoE
+def test_moe_route_matches_reference(be):
+    rng = np.random.Generator(np.random.PCG64(11))
+    logits = rng.standard_normal((64, 32)).astype(np.float32)
+    for renorm in (True, False):
+        idx, w = be.moe_route(logits, 4, renorm)
+        for t in range(64):
+            wi, ww = oracle.moe_route(logits[t], 4, renorm)
+            assert idx[t].tolist() == wi.tolist()
+            assert np.allclose(w[t], ww, rtol=0, atol=1e-6)
+    # ties: equal logits resolve to the lower expert index, in index order
+    tie = np.zeros((1, 8), np.float32)
+    tie[0, 5] = 1.0
+    idx, w = be.moe_route(tie, 3, True)
+    assert idx[0].tolist() == [5, 0, 1]
+    wi, ww = oracle.moe_route(tie[0], 3, True)
+    assert wi.tolist() == [5, 0, 1] and np.allclose(w[0], ww, atol=1e-6)
+    # top_k >= experts returns all, sorted by probability then index
+    idx, w = be.moe_route(logits[:2, :6], 10, True)
+    assert idx.shape == (2, 6) and np.allclose(w.sum(axis=1), 1.0, atol=1e-5)
+    for t in range(2):
+        assert idx[t].tolist() == oracle.moe_route(logits[t, :6], 10, True)[0].tolist()
+
+
+def test_moe_expert_walk_gpt_oss_shape(be):
+    # 8 experts of the gpt-oss expert shape (hidden 2880, intermediate 2880, MXFP4), top-4 routing,
+    # per-expert K = 768, a few tokens
+    import larql_b200
+    E, H, N, K, T = 8, 2880, 2880, 768, 3
+    experts = [layer(0x600 + 10 * e, N, H, oracle.FMT_MXFP4) for e in range(E)]
+    rng = np.random.Generator(np.random.PCG64(5))
+    logits = rng.standard_normal((T, E)).astype(np.float32)
+    xs = oracle.rms_norm(seeded_x(0x77, T, H))
+    got, idx, w = be.moe_walk_ffn([host(e[0]) for e in experts], [host(e[1]) for e in experts],
+                                  [host(e[2]) for e in experts], logits, xs, 4, K, True,
+                                  larql_b200.WALK_FORCE_SPARSE)
+    for t in range(T):
+        wi, ww = oracle.moe_route(logits[t], 4, True)
+        assert idx[t].tolist() == wi.tolist()
+        want = np.zeros(H, np.float32)
+        for e, we in zip(wi, ww):
+            o, _, _ = oracle.walk_token(*experts[int(e)], xs[t], K)
+            want += np.float32(we) * o
+        assert rel_l2(got[t], want) < OUT_TOL
