@@ -43,6 +43,7 @@ constexpr int FW_MAX_STAGES = 8;
 constexpr int FW_MAX_SLOTS = 32;
 constexpr float FW_NOISE_FLOOR = 1e-10f;  // ACTIVATION_NOISE_FLOOR, walk_config.rs:64
 constexpr int FW_PICK_CAP = 8192;    // band entries the final pick can stage in shared memory
+constexpr int FW_RANK_CAP = 2048;    // up to this many band entries the pick ranks by counting
 
 struct FusedGeom {
     int nsb, G, TS, P, Wt;      // super-blocks/row, cells/row, team size, teams, warps per team
@@ -82,7 +83,8 @@ struct FusedArgs {
     int* err;
 };
 
-enum { CTR_SYNC = 0, CTR_BOUND0 = 1, CTR_BOUND1 = 2, CTR_IN = 3, CTR_BAND = 4, CTR_HITS = 5, CTR_WORDS = 16 };
+enum { CTR_SYNC = 0, CTR_BOUND0 = 1, CTR_BOUND1 = 2, CTR_IN = 3, CTR_BAND = 4, CTR_HITS = 5, CTR_MAXBIN0 = 6,
+       CTR_MAXBIN1 = 7, CTR_WORDS = 16 };
 
 __host__ __device__ inline int fw_align(int v, int a) { return (v + a - 1) / a * a; }
 
@@ -122,6 +124,7 @@ __host__ inline bool fused_geom(int hidden, int n_rows, int grid_hint, FusedGeom
     g.ring_bytes = (budget - off) / 128 * 128;
     if (g.ring_bytes < 2 * g.tile_bytes || g.ring_bytes < 2 * g.slot_bytes) return false;
     if (g.ring_bytes < FW_PICK_CAP * 8 + 24 * 1024) return false;
+    if (g.ring_bytes < g.P * g.G * 65 * 4) return false;  // the merge stages one out[H] per team in the ring
     g.S = g.ring_bytes / g.tile_bytes;
     if (g.S > FW_MAX_STAGES) g.S = FW_MAX_STAGES;
     g.D = g.ring_bytes / g.slot_bytes;
@@ -438,71 +441,73 @@ __global__ void __launch_bounds__(FW_THREADS, 1) walk_fused_q4k_kernel(FusedGeom
         float* h_next = (l + 1 == a.n_layers) ? a.h_out : (par ? a.hbuf1 : a.hbuf0);
 
         FW_STAMP(0);
-        // ---- 0. prepare the activation (team 0) -------------------------------------
-        if (team == 0) {
-            float* xdst = xs + c * 68;
+        // ---- 0. prepare the activation: one thread per 32-element block ---------------------
+        {
+            const int n_blk32 = 2 * gm.G;
             double sq = 0.0;
-            if (active) {
-                const float4* src = reinterpret_cast<const float4*>(h_cur + (size_t)c * 64);
+            for (int blk = tid; blk < n_blk32; blk += FW_CONSUMERS) {
+                float* xdst = xs + (blk >> 1) * 68 + (blk & 1) * 32;
+                const float4* src = reinterpret_cast<const float4*>(h_cur + (size_t)blk * 32);
+                float4 t[8];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float4 t = __ldcg(src + j);
-                    *reinterpret_cast<float4*>(xdst + 4 * j) = t;
-                    sq += (double)t.x * (double)t.x + (double)t.y * (double)t.y;
-                    sq += (double)t.z * (double)t.z + (double)t.w * (double)t.w;
+                for (int j = 0; j < 8; ++j) t[j] = __ldcg(src + j);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    *reinterpret_cast<float4*>(xdst + 4 * j) = t[j];
+                    sq += (double)t[j].x * (double)t[j].x + (double)t[j].y * (double)t[j].y;
+                    sq += (double)t[j].z * (double)t[j].z + (double)t[j].w * (double)t[j].w;
                 }
             }
             float rms = 1.0f;
             if (a.flags & LQ_WALK_RMSNORM) {
                 double* dred = reinterpret_cast<double*>(red);
                 for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-                if (lane == 0) dred[wt] = sq;
-                bar_sync(1, gm.TS);
+                if (lane == 0) dred[warp] = sq;
+                bar_sync(FW_BAR_CONS, FW_CONSUMERS);
                 double t = 0.0;
-                for (int w = 0; w < gm.Wt; ++w) t += dred[w];
+                for (int w = 0; w < FW_NWARPS; ++w) t += dred[w];
                 rms = (float)sqrt(t / (double)hidden + 1e-6);
             }
-            if (active) {
-                bool bad = false;
-                for (int hb = 0; hb < 2; ++hb) {
-                    float v[32];
-                    float amax = 0.0f, sum = 0.0f, asum = 0.0f;
+            bool bad = false;
+            for (int blk = tid; blk < n_blk32; blk += FW_CONSUMERS) {
+                const int cc = blk >> 1, hb = blk & 1;
+                float* xdst = xs + cc * 68 + hb * 32;
+                float v[32];
+                float amax = 0.0f, sum = 0.0f, asum = 0.0f;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float4 t = *reinterpret_cast<const float4*>(xdst + hb * 32 + 4 * j);
-                        v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
-                    }
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        if (a.flags & LQ_WALK_RMSNORM) v[j] = __fdiv_rn(v[j], rms);
-                        bad |= !isfinite(v[j]);
-                        amax = fmaxf(amax, fabsf(v[j]));
-                        sum += v[j];
-                        asum += fabsf(v[j]);
-                    }
-                    const int blk = c * 2 + hb;
-                    const float inv = amax > 0.0f ? 32767.0f / amax : 0.0f;
-                    blk_s[blk] = amax / 32767.0f;
-                    blk_s[nblk + blk] = sum;
-                    blk_s[2 * nblk + blk] = asum;
-#pragma unroll
-                    for (int j4 = 0; j4 < 8; ++j4) {
-                        uint32_t wa = 0, wb = 0;
-#pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            int q = __float2int_rn(v[4 * j4 + b] * inv);
-                            q = max(-32767, min(32767, q));
-                            wa |= (uint32_t)((q >> 8) & 0xff) << (8 * b);
-                            wb |= (uint32_t)(q & 0xff) << (8 * b);
-                        }
-                        xa_s[(hb * 8 + j4) * gm.G + c] = wa;
-                        xb_s[(hb * 8 + j4) * gm.G + c] = wb;
-                        *reinterpret_cast<float4*>(xdst + hb * 32 + 4 * j4) =
-                            make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
-                    }
+                for (int j = 0; j < 8; ++j) {
+                    const float4 t = *reinterpret_cast<const float4*>(xdst + 4 * j);
+                    v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
                 }
-                if (bad) set_err(a.err, DEV_ERR_NAN_SCORE);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    if (a.flags & LQ_WALK_RMSNORM) v[j] = __fdiv_rn(v[j], rms);
+                    bad |= !isfinite(v[j]);
+                    amax = fmaxf(amax, fabsf(v[j]));
+                    sum += v[j];
+                    asum += fabsf(v[j]);
+                }
+                const float inv = amax > 0.0f ? 32767.0f / amax : 0.0f;
+                blk_s[blk] = amax / 32767.0f;
+                blk_s[nblk + blk] = sum;
+                blk_s[2 * nblk + blk] = asum;
+#pragma unroll
+                for (int j4 = 0; j4 < 8; ++j4) {
+                    uint32_t wa = 0, wb = 0;
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        int q = __float2int_rn(v[4 * j4 + b] * inv);
+                        q = max(-32767, min(32767, q));
+                        wa |= (uint32_t)((q >> 8) & 0xff) << (8 * b);
+                        wb |= (uint32_t)(q & 0xff) << (8 * b);
+                    }
+                    xa_s[(hb * 8 + j4) * gm.G + cc] = wa;
+                    xb_s[(hb * 8 + j4) * gm.G + cc] = wb;
+                    *reinterpret_cast<float4*>(xdst + 4 * j4) =
+                        make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
+                }
             }
+            if (bad) set_err(a.err, DEV_ERR_NAN_SCORE);
         }
         bar_sync(FW_BAR_CONS, FW_CONSUMERS);
 
@@ -511,6 +516,7 @@ __global__ void __launch_bounds__(FW_THREADS, 1) walk_fused_q4k_kernel(FusedGeom
         {
             CellX x;
             float ab_lo = 0.0f, ab_hi = 0.0f, bmax = 0.0f;
+            uint32_t kmax = 0;
             if (active) {
                 load_cellx(x, xa_s, xb_s, blk_s, nblk, s * 8 + 2 * g, gm.G, c);
                 ab_lo = blk_s[2 * nblk + s * 8 + 2 * g];
@@ -547,7 +553,9 @@ __global__ void __launch_bounds__(FW_THREADS, 1) walk_fused_q4k_kernel(FusedGeom
                         my_scores[k * R + r] = sc;
                         if (r < rows_here) {
                             if (sc != sc) set_err(a.err, DEV_ERR_NAN_SCORE);
-                            atomicAdd(&hist[__float_as_uint(fabsf(sc)) >> LQ_HIST_SHIFT], 1u);
+                            const uint32_t bin = __float_as_uint(fabsf(sc)) >> LQ_HIST_SHIFT;
+                            atomicAdd(&hist[bin], 1u);
+                            kmax = max(kmax, bin);
                         }
                     }
                 }
@@ -564,6 +572,11 @@ __global__ void __launch_bounds__(FW_THREADS, 1) walk_fused_q4k_kernel(FusedGeom
                     for (int w = 0; w < gm.Wt; ++w) t += wb[w];
                     if (t > 0.0f) atomicMax(&a.ctrs[CTR_BOUND0 + par], __float_as_uint(t));
                 }
+                if (c < gm.Rt && kmax > 0u) atomicMax(&a.ctrs[CTR_MAXBIN0 + par], kmax);
+            }
+            if (tid == 0) {
+                s_ctl[4] = 0;
+                s_ctl[7] = 0;
             }
         }
         FW_STAMP(2);
@@ -573,43 +586,48 @@ __global__ void __launch_bounds__(FW_THREADS, 1) walk_fused_q4k_kernel(FusedGeom
         // ---- 2. threshold bucket from the global histogram -----------------------------
         float hi, lo, B;
         {
-            constexpr int HT = 256, PER = LQ_HIST_BINS / HT;  // the first 256 threads take 64 bins each
-            uint32_t own = 0;
-            uint32_t* stash = reinterpret_cast<uint32_t*>(rg.ring) + tid * PER;  // the ring is idle here
-            if (tid < HT) {
-                const uint4* hp = reinterpret_cast<const uint4*>(hist + tid * PER);
-#pragma unroll
-                for (int b = 0; b < PER / 4; ++b) {
-                    const uint4 t = __ldcg(hp + b);
-                    reinterpret_cast<uint4*>(stash)[b] = t;
-                    own += t.x + t.y + t.z + t.w;
-                }
-            }
+            // Read the histogram from the highest occupied bin downwards, 1024 bins per round
+            // (256 threads x 4 bins, thread 0 the highest), until the cumulative count reaches K.
+            constexpr int HT = 256;
             const uint32_t bbits = __ldcg(&a.ctrs[CTR_BOUND0 + par]);
-            uint32_t suf = own;
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t v = __shfl_down_sync(0xffffffffu, suf, o);
-                if (lane + o < 32) suf += v;
-            }
+            const uint32_t maxbin = min(__ldcg(&a.ctrs[CTR_MAXBIN0 + par]), (uint32_t)LQ_HIST_BINS - 1u);
+            const uint32_t K = (uint32_t)a.top_k;
             uint32_t* wsum = reinterpret_cast<uint32_t*>(red);
-            if (lane == 0 && tid < HT) wsum[warp] = suf;
-            bar_sync(FW_BAR_CONS, FW_CONSUMERS);
-            if (tid < HT) {
-                uint32_t higher = 0;
-                for (int w = warp + 1; w < HT / 32; ++w) higher += wsum[w];
-                suf += higher;
-                const uint32_t above = suf - own, K = (uint32_t)a.top_k;
-                if (above < K && K <= suf) {
-                    uint32_t acc = above;
-                    int b = PER - 1;
-                    for (; b > 0; --b) {
-                        if (acc + stash[b] >= K) break;
-                        acc += stash[b];
-                    }
-                    s_ctl[4] = tid * PER + b;
+            uint32_t above_total = 0;
+            for (int base_end = (int)(maxbin / 4u + 1u) * 4; base_end > 0; base_end -= 4 * HT) {
+                const int b0 = base_end - 4 * (tid + 1);
+                uint4 t4 = make_uint4(0u, 0u, 0u, 0u);
+                if (tid < HT && b0 >= 0) t4 = __ldcg(reinterpret_cast<const uint4*>(hist + b0));
+                const uint32_t own = t4.x + t4.y + t4.z + t4.w;
+                uint32_t pre = own;  // inclusive prefix in thread order (higher bins first)
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t v = __shfl_up_sync(0xffffffffu, pre, o);
+                    if (lane >= o) pre += v;
                 }
+                if (lane == 31) wsum[warp] = pre;
+                bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+                uint32_t lower = 0, chunk_total = 0;
+                for (int w = 0; w < HT / 32; ++w) {
+                    const uint32_t v = wsum[w];
+                    if (w < warp) lower += v;
+                    chunk_total += v;
+                }
+                const uint32_t incl = above_total + lower + pre, excl = incl - own;
+                if (tid < HT && excl < K && K <= incl) {
+                    uint32_t acc = excl;
+                    int b = 3;
+                    const uint32_t bins4[4] = {t4.x, t4.y, t4.z, t4.w};
+                    for (; b > 0; --b) {
+                        if (acc + bins4[b] >= K) break;
+                        acc += bins4[b];
+                    }
+                    s_ctl[4] = b0 + b;
+                    s_ctl[7] = 1;
+                }
+                above_total += chunk_total;
+                bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+                if (s_ctl[7]) break;
             }
-            bar_sync(FW_BAR_CONS, FW_CONSUMERS);
             const uint32_t bstar = (uint32_t)s_ctl[4];
             B = __uint_as_float(bbits);
             const float t_lo = __uint_as_float(bstar << LQ_HIST_SHIFT);
@@ -722,6 +740,10 @@ __global__ void __launch_bounds__(FW_THREADS, 1) walk_fused_q4k_kernel(FusedGeom
             const int need = a.top_k - n_in_tot;
             uint32_t tau_key = 0, row_cut = 0xffffffffu;
             bool take_all = need >= n_band_tot;
+            // Small bands (the usual case): every CTA ranks its own band rows against all band
+            // entries by counting; large bands fall back to a radix select of the threshold.
+            const bool by_rank = !take_all && need > 0 && n_band_tot <= FW_RANK_CAP;
+            int* win_s = reinterpret_cast<int*>(rg.ring + FW_PICK_CAP * 8);
             if (!take_all && need > 0) {
                 // stage (|v| key, row) of every band entry in the idle ring
                 uint32_t* keys = reinterpret_cast<uint32_t*>(rg.ring);
@@ -734,20 +756,37 @@ __global__ void __launch_bounds__(FW_THREADS, 1) walk_fused_q4k_kernel(FusedGeom
                     }
                     bar_sync(FW_BAR_CONS, FW_CONSUMERS);
                 }
-                SelectSmem<FW_CONSUMERS>& sm = *reinterpret_cast<SelectSmem<FW_CONSUMERS>*>(rg.ring + FW_PICK_CAP * 8);
-                int cnt_gt, need_eq;
-                auto keyf = [&](int i) -> uint32_t { return staged ? keys[i] : abs_key(__ldcg(&a.band_exact[i])); };
-                block_kth_largest_keys<FW_CONSUMERS, FW_BAR_CONS>(keyf, n_band_tot, need, sm, tau_key, cnt_gt, need_eq);
-                // ties at the threshold: the need_eq lowest rows win
-                auto rowf = [&](int i) -> uint32_t {
-                    if (keyf(i) != tau_key) return 0u;
-                    return ~(staged ? rows[i] : __ldcg(&a.band_row[i]));
-                };
-                uint32_t cut_key;
-                int c2, n2;
-                block_kth_largest_keys<FW_CONSUMERS, FW_BAR_CONS>(rowf, n_band_tot, need_eq, sm, cut_key, c2, n2);
-                row_cut = ~cut_key;
-                bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+                if (by_rank) {
+                    for (int i = warp; i < n_band_mine; i += FW_NWARPS) {
+                        const int m = band_list[i];
+                        const uint32_t key = abs_key(band_ex[i]);
+                        const uint32_t row = (uint32_t)((first_tile + (m / R) * (int)gridDim.x) * R + (m % R));
+                        int ahead = 0;  // entries that order before this one under (|v| desc, row asc)
+                        for (int j = lane; j < n_band_tot; j += 32) {
+                            const uint32_t kj = keys[j];
+                            ahead += (kj > key || (kj == key && rows[j] < row)) ? 1 : 0;
+                        }
+                        for (int o = 16; o > 0; o >>= 1) ahead += __shfl_xor_sync(0xffffffffu, ahead, o);
+                        if (lane == 0) win_s[i] = ahead < need ? 1 : 0;
+                    }
+                    bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+                } else {
+                    SelectSmem<FW_CONSUMERS>& sm =
+                        *reinterpret_cast<SelectSmem<FW_CONSUMERS>*>(rg.ring + FW_PICK_CAP * 8);
+                    int cnt_gt, need_eq;
+                    auto keyf = [&](int i) -> uint32_t { return staged ? keys[i] : abs_key(__ldcg(&a.band_exact[i])); };
+                    block_kth_largest_keys<FW_CONSUMERS, FW_BAR_CONS>(keyf, n_band_tot, need, sm, tau_key, cnt_gt, need_eq);
+                    // ties at the threshold: the need_eq lowest rows win
+                    auto rowf = [&](int i) -> uint32_t {
+                        if (keyf(i) != tau_key) return 0u;
+                        return ~(staged ? rows[i] : __ldcg(&a.band_row[i]));
+                    };
+                    uint32_t cut_key;
+                    int c2, n2;
+                    block_kth_largest_keys<FW_CONSUMERS, FW_BAR_CONS>(rowf, n_band_tot, need_eq, sm, cut_key, c2, n2);
+                    row_cut = ~cut_key;
+                    bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+                }
             }
             // winners among this CTA's band rows, in slot order
             if (warp == 0) {
@@ -760,7 +799,8 @@ __global__ void __launch_bounds__(FW_THREADS, 1) walk_fused_q4k_kernel(FusedGeom
                         m = band_list[i];
                         const uint32_t key = abs_key(band_ex[i]);
                         const uint32_t row = (uint32_t)((first_tile + (m / R) * (int)gridDim.x) * R + (m % R));
-                        win = take_all || key > tau_key || (key == tau_key && row <= row_cut);
+                        win = by_rank ? (win_s[i] != 0)
+                                      : (take_all || key > tau_key || (key == tau_key && row <= row_cut));
                         if (win) my_scores[m] = band_ex[i];  // the gather uses the exact gate score
                     }
                     const uint32_t bal = __ballot_sync(0xffffffffu, win);
@@ -788,7 +828,7 @@ __global__ void __launch_bounds__(FW_THREADS, 1) walk_fused_q4k_kernel(FusedGeom
                             acc_hi, corr_lo, corr_hi, failed);
         else
             g_it += n_g2;
-        bar_sync(FW_BAR_ALL, FW_THREADS);  // C: the ring is free for the next layer's tiles
+        bar_sync(FW_BAR_CONS, FW_CONSUMERS);  // every team has finished reading its gather slots
         FW_STAMP(9);
 
         // optional: selected rows of the last layer (unordered)
@@ -803,33 +843,39 @@ __global__ void __launch_bounds__(FW_THREADS, 1) walk_fused_q4k_kernel(FusedGeom
             }
         }
 
-        // ---- partial out[H] of this CTA: merge the teams in team order ------------------
+        // ---- partial out[H] of this CTA: the teams' accumulators, summed in team order ---------
         {
-            float* out_s = xs;  // 64-float chunks at a stride of 65 (xs is idle after the re-score)
-            for (int p = 0; p < P; ++p) {
-                if (active && team == p) {
-                    float* o_lo = out_s + c * 65;
-                    float* o_hi = o_lo + 32;
+            // one region per team in the idle ring, 64-float chunks at a stride of 65
+            float* out_r = reinterpret_cast<float*>(rg.ring);
+            const int region = gm.G * 65;
+            if (active) {
+                float* o_lo = out_r + team * region + c * 65;
+                float* o_hi = o_lo + 32;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float vl = acc_lo[j] - corr_lo, vh = acc_hi[j] - corr_hi;
-                        if (p == 0) {
-                            o_lo[j] = vl;
-                            o_hi[j] = vh;
-                        } else {
-                            o_lo[j] += vl;
-                            o_hi[j] += vh;
-                        }
-                    }
+                for (int j = 0; j < 32; ++j) {
+                    o_lo[j] = acc_lo[j] - corr_lo;
+                    o_hi[j] = acc_hi[j] - corr_hi;
                 }
-                bar_sync(FW_BAR_CONS, FW_CONSUMERS);
             }
+            bar_sync(FW_BAR_CONS, FW_CONSUMERS);
             float* dst = a.partials + (size_t)blockIdx.x * hidden;
-            for (int i = tid; i < hidden; i += FW_CONSUMERS) dst[i] = out_s[(i >> 6) * 65 + (i & 63)];
+            for (int i = tid; i < hidden; i += FW_CONSUMERS) {
+                const int o = (i >> 6) * 65 + (i & 63);
+                float v = out_r[o];
+                for (int p = 1; p < P; ++p) v += out_r[p * region + o];
+                dst[i] = v;
+            }
         }
+        // the merge used the ring with plain loads and stores; order them before the TMA writes of
+        // the next layer's tiles
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        bar_sync(FW_BAR_ALL, FW_THREADS);  // C: the ring is free for the next layer's tiles
         // housekeeping for the layer after next (nobody reads these before two more grid barriers)
         for (int i = blockIdx.x * FW_CONSUMERS + tid; i < LQ_HIST_BINS; i += gridDim.x * FW_CONSUMERS) hist[i] = 0;
-        if (blockIdx.x == 0 && tid == 0) a.ctrs[CTR_BOUND0 + par] = 0;
+        if (blockIdx.x == 0 && tid == 0) {
+            a.ctrs[CTR_BOUND0 + par] = 0;
+            a.ctrs[CTR_MAXBIN0 + par] = 0;
+        }
         FW_STAMP(10);
         grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[6]);
         FW_STAMP(11);
