@@ -68,6 +68,7 @@ struct lq_ctx {
     std::vector<TokenWs> tok;
     float* partials = nullptr;
     int gather_grid = 0;
+    size_t batch_min = 2;  // smallest batch that takes the batched (tensor-core scan) path
     unsigned long long* sort_buf = nullptr;
     size_t sort_cap = 0;
     // staging for the host-pointer API
@@ -139,6 +140,17 @@ int check_matrix(lq_ctx* ctx, const lq_matrix* m, const char* name) {
     return LQ_OK;
 }
 
+// CTAs per token of the batched gather, and the partial-output blocks a batch needs.
+int batch_gather_grid(const lq_ctx* ctx, size_t nb) {
+    if (nb <= 1) return ctx->gather_grid;
+    int g = (int)((2 * (size_t)ctx->sm_count + nb - 1) / nb);
+    return std::max(8, std::min(g, ctx->gather_grid));
+}
+size_t partial_blocks(const lq_ctx* ctx, size_t batch) {
+    const size_t chunk = std::min<size_t>(batch, 64);
+    return std::max<size_t>((size_t)ctx->gather_grid, chunk * (size_t)batch_gather_grid(ctx, chunk));
+}
+
 int ensure_ws(lq_ctx* ctx, size_t batch, size_t hidden, size_t feat) {
     if (batch <= ctx->ws_batch && hidden <= ctx->ws_hidden && feat <= ctx->ws_feat) return LQ_OK;
     cudaStreamCaptureStatus cs;
@@ -154,7 +166,7 @@ int ensure_ws(lq_ctx* ctx, size_t batch, size_t hidden, size_t feat) {
     const size_t per_tok = a256(H * 4) + 2 * a256(H) + 3 * a256(H / 32 * 4) + a256(N * 4) + a256(LQ_HIST_BINS * 4) + 256 +
                            4 * a256(N * 4);
     ctx->gather_grid = ctx->sm_count;
-    const size_t part_bytes = a256((size_t)ctx->gather_grid * H * 4);
+    const size_t part_bytes = a256(partial_blocks(ctx, batch) * H * 4);
     const size_t total = batch * per_tok + part_bytes;
     CK(cudaMalloc(&ctx->ws_raw, total));
     CK(cudaMemsetAsync(ctx->ws_raw, 0, total, ctx->stream));
@@ -181,7 +193,7 @@ int ensure_ws(lq_ctx* ctx, size_t batch, size_t hidden, size_t feat) {
         w.band_idx = (uint32_t*)take(N * 4);
         w.band_exact = (float*)take(N * 4);
     }
-    ctx->partials = (float*)take((size_t)ctx->gather_grid * H * 4);
+    ctx->partials = (float*)take(partial_blocks(ctx, batch) * H * 4);
     ctx->ws_batch = batch;
     ctx->ws_hidden = hidden;
     ctx->ws_feat = feat;
@@ -424,7 +436,7 @@ int dev_walk(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const lq_m
     int rc = ensure_ws(ctx, batch, H, N);
     if (rc) return rc;
     const size_t k = effective_k(top_k, N, flags);
-    if (N > 0 && fused_ok(ctx, *gate, *up, *down, k)) {
+    if (N > 0 && batch < ctx->batch_min && fused_ok(ctx, *gate, *up, *down, k)) {
         rc = ensure_fused(ctx, H, N);
         if (rc) return rc;
         const uint8_t* single[3] = {(const uint8_t*)gate->data, (const uint8_t*)up->data, (const uint8_t*)down->data};
@@ -447,6 +459,36 @@ int dev_walk(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const lq_m
                 w0.bsum, w0.babs, tok_stride_f, ctx->d_err, ctx->stream);
     CK(cudaGetLastError());
     ctx->launches += 1;
+    // Batches of Q4_K tokens: one tensor-core scan and one launch of each selection / gather kernel
+    // for up to 64 tokens at a time (the gate matrix is read once per chunk instead of once per token).
+    if (batch >= ctx->batch_min && N > 0 && k < N && k > 0 && gate->fmt == LQ_FMT_Q4_K && up->fmt == LQ_FMT_Q4_K &&
+        down->fmt == LQ_FMT_Q4_K) {
+        const Q4kMat g{(const uint8_t*)gate->data, (int)N, (int)H}, u{(const uint8_t*)up->data, (int)N, (int)H},
+            d{(const uint8_t*)down->data, (int)N, (int)H};
+        const size_t ws_stride = (size_t)((uint8_t*)ctx->tok[1].xn - (uint8_t*)ctx->tok[0].xn);
+        for (size_t c0 = 0; c0 < batch; c0 += 64) {
+            const int nb = (int)std::min<size_t>(64, batch - c0);
+            const TokenWs& w = ctx->tok[c0];
+            const int gb = batch_gather_grid(ctx, (size_t)nb);
+            const TokStride ts{ws_stride, H, (size_t)gb * H};
+            CK(launch_scan_q4k_mma(g, w, ws_stride, nb, 1, bound_c1((int)H), ctx->d_err, ctx->sm_count, ctx->stream));
+            CK(launch_classify(w.scores, (int)N, (int)k, w, ctx->d_err, ctx->stream, nb, ws_stride));
+            CK(launch_rescore_q4k(g, w.xn, w.band_idx, &w.sel->n_band, 0, w.band_exact, w, (int)k, 1, ctx->d_err,
+                                  ctx->sm_count, ctx->stream, nb, ws_stride));
+            CK(launch_gather_q4k(u, d, xprep_of(w), w.hit_idx, w.hit_score, &w.sel->n_sel, (int)k, ctx->partials, gb,
+                                 ctx->d_err, ctx->stream, nb, ts));
+            CK(launch_finish(ctx->partials, gb, (int)H, (flags & LQ_WALK_RESIDUAL) ? x + c0 * H : nullptr, out + c0 * H,
+                             ctx->stream, nb, ts));
+            ctx->launches += 5;
+            if (idx_out)
+                CK(cudaMemcpy2DAsync(idx_out + c0 * k, k * 4, w.hit_idx, ws_stride, k * 4, (size_t)nb,
+                                     cudaMemcpyDeviceToDevice, ctx->stream));
+            if (count_out)
+                CK(cudaMemcpy2DAsync(count_out + c0, 4, &w.sel->n_sel, ws_stride, 4, (size_t)nb, cudaMemcpyDeviceToDevice,
+                                     ctx->stream));
+        }
+        return LQ_OK;
+    }
     for (size_t t = 0; t < batch; ++t) {
         if (N == 0) {
             if (flags & LQ_WALK_RESIDUAL)
@@ -493,6 +535,7 @@ int lq_create(int device, lq_ctx** out) {
         return LQ_ERR_CUDA;
     }
     if (const char* e = getenv("LARQL_B200_NO_FUSED")) ctx->use_fused = !(e[0] && e[0] != '0');
+    if (const char* e = getenv("LARQL_B200_BATCH_MIN")) ctx->batch_min = (size_t)std::max(2, atoi(e));
     *out = ctx;
     return LQ_OK;
 }

@@ -56,8 +56,17 @@ __host__ inline bool gather_geom(int hidden, GatherGeom& g) {
 __global__ void __launch_bounds__(GATHER_THREADS, 1)
 gather_q4k_kernel(const uint8_t* __restrict__ Wup, const uint8_t* __restrict__ Wdown, GatherGeom gm, XPrep xp,
                   const uint32_t* __restrict__ hit_idx, const float* __restrict__ hit_score,
-                  const int* __restrict__ n_hits_dev, int n_hits_host, float* __restrict__ partials, int* err) {
+                  const int* __restrict__ n_hits_dev, int n_hits_host, float* __restrict__ partials, int* err,
+                  TokStride ts) {
     extern __shared__ __align__(128) uint8_t smem[];
+    {
+        const size_t off = ts.ws * blockIdx.y;
+        xp = xp_at(xp, off);
+        hit_idx = tok_off(hit_idx, off);
+        hit_score = tok_off(hit_score, off);
+        n_hits_dev = tok_off(n_hits_dev, off);
+        partials += ts.part * blockIdx.y;
+    }
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);  // [2]
     float* part = reinterpret_cast<float*>(smem + 128);  // [F][G]
     float* act_s = part + gm.F * gm.G;                   // [F] (<= 64)
@@ -236,8 +245,12 @@ gather_q4k_kernel(const uint8_t* __restrict__ Wup, const uint8_t* __restrict__ W
 // out[h] = residual[h] + sum_p partials[p][h], p ascending inside each of 8 interleaved
 // groups and the 8 group sums added in group order: fixed, so run-to-run identical.
 __global__ void __launch_bounds__(256) finish_kernel(const float* __restrict__ partials, int n_partials, int hidden,
-                                                    const float* __restrict__ residual, float* __restrict__ out) {
+                                                    const float* __restrict__ residual, float* __restrict__ out,
+                                                    TokStride ts) {
     __shared__ float red[8][32];
+    partials += ts.part * blockIdx.y;
+    if (residual) residual += ts.io * blockIdx.y;
+    out += ts.io * blockIdx.y;
     const int col = blockIdx.x * 32 + threadIdx.x, y = threadIdx.y;
     float a = 0.0f;
     if (col < hidden) {
@@ -260,7 +273,7 @@ int gather_q4k_grid(int sm_count) { return sm_count; }
 
 cudaError_t launch_gather_q4k(const Q4kMat& up, const Q4kMat& down, const XPrep& xp, const uint32_t* hit_idx,
                               const float* hit_score, const int* n_hits_dev, int n_hits_host, float* partials,
-                              int grid, int* err, cudaStream_t st) {
+                              int grid, int* err, cudaStream_t st, int batch, TokStride ts) {
     GatherGeom g;
     if (up.cols != down.cols || !gather_geom(up.cols, g)) return cudaErrorInvalidValue;
     static bool attr_set = false;
@@ -270,14 +283,14 @@ cudaError_t launch_gather_q4k(const Q4kMat& up, const Q4kMat& down, const XPrep&
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    gather_q4k_kernel<<<grid, GATHER_THREADS, g.smem_bytes, st>>>(up.w, down.w, g, xp, hit_idx, hit_score, n_hits_dev,
-                                                                 n_hits_host, partials, err);
+    gather_q4k_kernel<<<dim3(grid, batch), GATHER_THREADS, g.smem_bytes, st>>>(up.w, down.w, g, xp, hit_idx, hit_score,
+                                                                              n_hits_dev, n_hits_host, partials, err, ts);
     return cudaGetLastError();
 }
 
 cudaError_t launch_finish(const float* partials, int n_partials, int hidden, const float* residual, float* out,
-                          cudaStream_t st) {
-    finish_kernel<<<(hidden + 31) / 32, dim3(32, 8), 0, st>>>(partials, n_partials, hidden, residual, out);
+                          cudaStream_t st, int batch, TokStride ts) {
+    finish_kernel<<<dim3((hidden + 31) / 32, batch), dim3(32, 8), 0, st>>>(partials, n_partials, hidden, residual, out, ts);
     return cudaGetLastError();
 }
 

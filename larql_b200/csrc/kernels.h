@@ -37,6 +37,33 @@ struct TokenWs {
     float* band_exact;  // [N] exact reference-order score per band row
 };
 
+// Batched launches: the kernels below take the views of token 0 and advance every per-token
+// pointer by a constant byte stride per token (blockIdx.y).
+struct TokStride {
+    size_t ws;    // bytes between two tokens' workspaces (TokenWs / XPrep members)
+    size_t io;    // floats between two tokens' residual / output rows
+    size_t part;  // floats between two tokens' partial-output blocks
+};
+#ifdef __CUDACC__
+template <class T>
+__device__ __forceinline__ T* tok_off(T* p, size_t bytes) {
+    return p ? reinterpret_cast<T*>(reinterpret_cast<uintptr_t>(p) + bytes) : p;
+}
+__device__ __forceinline__ TokenWs ws_at(TokenWs w, size_t b) {
+    w.xn = tok_off(w.xn, b); w.xa = tok_off(w.xa, b); w.xb = tok_off(w.xb, b);
+    w.bscale = tok_off(w.bscale, b); w.bsum = tok_off(w.bsum, b); w.babs = tok_off(w.babs, b);
+    w.scores = tok_off(w.scores, b); w.hist = tok_off(w.hist, b); w.sel = tok_off(w.sel, b);
+    w.hit_idx = tok_off(w.hit_idx, b); w.hit_score = tok_off(w.hit_score, b);
+    w.band_idx = tok_off(w.band_idx, b); w.band_exact = tok_off(w.band_exact, b);
+    return w;
+}
+__device__ __forceinline__ XPrep xp_at(XPrep x, size_t b) {
+    x.xn = tok_off(x.xn, b); x.xa = tok_off(x.xa, b); x.xb = tok_off(x.xb, b);
+    x.scale = tok_off(x.scale, b); x.sum = tok_off(x.sum, b); x.abs = tok_off(x.abs, b);
+    return x;
+}
+#endif
+
 // Coarse histogram of |score| bit patterns: 8 exponent + 6 mantissa bits.
 #define LQ_HIST_SHIFT 17
 #define LQ_HIST_BINS 16384
@@ -84,12 +111,18 @@ cudaError_t launch_scan_q4k(const Q4kMat& m, const XPrep& xp, float* scores, uin
 // all rows when rows_idx == nullptr.  When sel != nullptr the last CTA to finish runs the final pick.
 cudaError_t launch_rescore_q4k(const Q4kMat& m, const float* xn, const uint32_t* rows_idx, const int* n_rows_dev,
                                int n_rows_host, float* out, TokenWs ws, int top_k, int run_final, int* err,
-                               int sm_count, cudaStream_t st);
+                               int sm_count, cudaStream_t st, int batch = 1, size_t ws_stride = 0);
+// scan_q4k_mma.cu: fast scores of every row for `batch` tokens at once on the tensor cores
+// (integer dots of the 4-bit weights against the tokens' fixed-point planes), with the histogram
+// and the bound of every token as launch_scan_q4k leaves them.
+cudaError_t launch_scan_q4k_mma(const Q4kMat& m, TokenWs ws0, size_t ws_stride, int batch, int want_hist, float c1,
+                                int* err, int sm_count, cudaStream_t st);
 
 // select.cu
 cudaError_t launch_select(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st);
 // Band classification from the scan's coarse histogram (walk path).
-cudaError_t launch_classify(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st);
+cudaError_t launch_classify(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st,
+                            int batch = 1, size_t ws_stride = 0);
 // Stand-alone exact top-K by |score| (ties -> lower index), sorted (|v| desc, idx asc).
 cudaError_t launch_topk_abs_sorted(const float* scores, int n, int top_k, uint32_t* idx_out, float* val_out,
                                    int* count_out, void* scratch, int* err, cudaStream_t st);
@@ -98,10 +131,10 @@ cudaError_t launch_topk_abs_sorted(const float* scores, int n, int top_k, uint32
 int gather_q4k_grid(int sm_count);
 cudaError_t launch_gather_q4k(const Q4kMat& up, const Q4kMat& down, const XPrep& xp, const uint32_t* hit_idx,
                               const float* hit_score, const int* n_hits_dev, int max_hits, float* partials,
-                              int grid, int* err, cudaStream_t st);
+                              int grid, int* err, cudaStream_t st, int batch = 1, TokStride ts = TokStride{0, 0, 0});
 // out[h] = (residual ? residual[h] : 0) + sum_c partials[c][h]   (fixed order)
 cudaError_t launch_finish(const float* partials, int n_partials, int hidden, const float* residual, float* out,
-                          cudaStream_t st);
+                          cudaStream_t st, int batch = 1, TokStride ts = TokStride{0, 0, 0});
 
 // walk_fused_q4k.cu — the fused persistent walk (one token, all layers, one cooperative launch)
 bool fused_q4k_supported(int hidden, int n_rows, int top_k, int sm_count);

@@ -206,8 +206,16 @@ constexpr int RESCORE_THREADS = 256;  // 8 warps, one row per warp at a time
 __global__ void __launch_bounds__(RESCORE_THREADS)
 rescore_q4k_kernel(const uint8_t* __restrict__ W, int n_rows_total, int nsb, const float* __restrict__ xn,
                    const uint32_t* __restrict__ rows_idx, const int* __restrict__ n_rows_dev, int n_rows_host,
-                   float* __restrict__ out, TokenWs ws, int top_k, int run_final, int* err) {
+                   float* __restrict__ out, TokenWs ws, int top_k, int run_final, int* err, size_t ws_stride) {
     extern __shared__ __align__(128) uint8_t smem[];
+    {
+        const size_t off = ws_stride * blockIdx.y;
+        ws = ws_at(ws, off);
+        xn = tok_off(xn, off);
+        rows_idx = tok_off(rows_idx, off);
+        n_rows_dev = tok_off(n_rows_dev, off);
+        out = tok_off(out, off);
+    }
     float* sb_part_all = reinterpret_cast<float*>(smem);  // [8 warps][nsb]
     float* xs = sb_part_all + (RESCORE_THREADS / 32) * nsb; // [4*nsb chunks][68]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -264,11 +272,11 @@ cudaError_t launch_scan_q4k(const Q4kMat& m, const XPrep& xp, float* scores, uin
 
 cudaError_t launch_rescore_q4k(const Q4kMat& m, const float* xn, const uint32_t* rows_idx, const int* n_rows_dev,
                                int n_rows_host, float* out, TokenWs ws, int top_k, int run_final, int* err,
-                               int sm_count, cudaStream_t st) {
+                               int sm_count, cudaStream_t st, int batch, size_t ws_stride) {
     if (m.cols <= 0 || m.cols % 256 != 0) return cudaErrorInvalidValue;
     const int nsb = m.cols / 256;
     int grid;
-    if (n_rows_dev) grid = sm_count * 2;  // count unknown on the host: a fixed grid strides over the list
+    if (n_rows_dev) grid = batch > 1 ? 16 : sm_count * 2;  // count unknown on the host: a fixed grid strides over the list
     else {
         grid = (n_rows_host + 7) / 8;
         if (grid > sm_count * 8) grid = sm_count * 8;
@@ -281,8 +289,9 @@ cudaError_t launch_rescore_q4k(const Q4kMat& m, const float* xn, const uint32_t*
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    rescore_q4k_kernel<<<grid, RESCORE_THREADS, smem, st>>>(m.w, m.rows, nsb, xn, rows_idx, n_rows_dev, n_rows_host,
-                                                           out, ws, top_k, run_final, err);
+    rescore_q4k_kernel<<<dim3(grid, batch), RESCORE_THREADS, smem, st>>>(m.w, m.rows, nsb, xn, rows_idx, n_rows_dev,
+                                                                        n_rows_host, out, ws, top_k, run_final, err,
+                                                                        ws_stride);
     return cudaGetLastError();
 }
 

@@ -95,7 +95,10 @@ select_kernel(const float* __restrict__ scores, int n, int top_k, TokenWs ws, in
 //   else              -> certainly out                        (at least K rows reach t_lo).
 // The histogram and the bound word are cleared for the next scan.
 __global__ void __launch_bounds__(SEL_T, 1)
-classify_kernel(const float* __restrict__ scores_g, int n, int top_k, TokenWs ws, int* err, int use_smem) {
+classify_kernel(const float* __restrict__ scores_g, int n, int top_k, TokenWs ws, int* err, int use_smem,
+                size_t ws_stride) {
+    ws = ws_at(ws, ws_stride * blockIdx.y);
+    scores_g = tok_off(scores_g, ws_stride * blockIdx.y);
     extern __shared__ __align__(16) float s_vals[];
     __shared__ SelectSmem<SEL_T> sm;
     __shared__ uint32_t s_wsum[SEL_T / 32];
@@ -221,7 +224,8 @@ cudaError_t launch_select(const float* scores, int n, int top_k, TokenWs ws, int
     return cudaGetLastError();
 }
 
-cudaError_t launch_classify(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st) {
+cudaError_t launch_classify(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st, int batch,
+                            size_t ws_stride) {
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(classify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -231,7 +235,7 @@ cudaError_t launch_classify(const float* scores, int n, int top_k, TokenWs ws, i
     }
     const int use_smem = n <= SEL_SMEM_VALS_MAX;
     const size_t smem = use_smem ? (size_t)((n + 3) / 4 * 4) * sizeof(float) : 0;
-    classify_kernel<<<1, SEL_T, smem, st>>>(scores, n, top_k, ws, err, use_smem);
+    classify_kernel<<<dim3(1, batch), SEL_T, smem, st>>>(scores, n, top_k, ws, err, use_smem, ws_stride);
     return cudaGetLastError();
 }
 
