@@ -142,9 +142,9 @@ int check_matrix(lq_ctx* ctx, const lq_matrix* m, const char* name) {
 
 // CTAs per token of the batched gather, and the partial-output blocks a batch needs.
 int batch_gather_grid(const lq_ctx* ctx, size_t nb) {
+    // one CTA per SM in total (the gather kernel fills an SM): a single wave, no tail
     if (nb <= 1) return ctx->gather_grid;
-    int g = (int)((2 * (size_t)ctx->sm_count + nb - 1) / nb);
-    return std::max(8, std::min(g, ctx->gather_grid));
+    return std::max(1, ctx->sm_count / (int)nb);
 }
 size_t partial_blocks(const lq_ctx* ctx, size_t batch) {
     const size_t chunk = std::min<size_t>(batch, 64);
@@ -1155,7 +1155,7 @@ int lq_stack_create(lq_ctx* ctx, const lq_matrix* gates, const lq_matrix* ups, c
         for (size_t l = 0; l < n_layers; ++l)
             same = same && gates[l].rows == gates[0].rows && gates[l].cols == gates[0].cols;
         const size_t k = effective_k(top_k, (size_t)gates[0].rows, s->flags);
-        bool ok = same;
+        bool ok = same && batch < ctx->batch_min;  // batches take the tensor-core scan, layer by layer
         for (size_t l = 0; ok && l < n_layers; ++l) ok = fused_ok(ctx, s->gates[l], s->ups[l], s->downs[l], k);
         if (ok) {
             rc = ensure_fused(ctx, (size_t)s->hidden, (size_t)gates[0].rows);

@@ -276,7 +276,8 @@ cudaError_t launch_rescore_q4k(const Q4kMat& m, const float* xn, const uint32_t*
     if (m.cols <= 0 || m.cols % 256 != 0) return cudaErrorInvalidValue;
     const int nsb = m.cols / 256;
     int grid;
-    if (n_rows_dev) grid = batch > 1 ? 16 : sm_count * 2;  // count unknown on the host: a fixed grid strides over the list
+    // count unknown on the host: a fixed grid strides over the list (about 4 CTAs per SM in total)
+    if (n_rows_dev) grid = batch > 1 ? (4 * sm_count / batch > 8 ? 4 * sm_count / batch : 8) : sm_count * 2;
     else {
         grid = (n_rows_host + 7) / 8;
         if (grid > sm_count * 8) grid = sm_count * 8;
