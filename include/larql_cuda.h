@@ -185,6 +185,9 @@ typedef struct lq_stack lq_stack;
 LQ_API int lq_stack_create(lq_ctx* ctx, const lq_matrix* gates, const lq_matrix* ups, const lq_matrix* downs_fm,
                            size_t n_layers, size_t batch, size_t top_k, uint32_t flags, lq_stack** out);
 LQ_API int lq_stack_run(lq_ctx* ctx, lq_stack* stack, const float* h_in, float* h_out);
+/* The same with HOST residuals: one upload, every layer on the device, one download; returns when
+ * h_out_host is written (device or NaN-score errors come back as the status). */
+LQ_API int lq_stack_run_host(lq_ctx* ctx, lq_stack* stack, const float* h_in_host, float* h_out_host);
 LQ_API void lq_stack_destroy(lq_ctx* ctx, lq_stack* stack);
 
 /* quantize_q4_k (crates/larql-compute/src/cpu/ops/q4_common/quantize.rs:89-189) on the device:

@@ -37,7 +37,7 @@ EXPORTS = [
     "lq_stack_create", "lq_stack_run", "lq_stack_destroy", "lq_last_walk_stats", "lq_dev_quantize_q4k",
     "lq_profile_walk", "lq_fused_phase_us", "lq_q4k_matvec_static", "lq_dev_shard_scan", "lq_dev_shard_classify",
     "lq_dev_shard_gather", "lq_gemv", "lq_q8_0_gemv", "lq_mxfp4_gemv", "lq_nvfp4_gemv", "lq_moe_route",
-    "lq_moe_walk_ffn",
+    "lq_moe_walk_ffn", "lq_stack_run_host",
 ]
 
 
@@ -92,6 +92,7 @@ def load_library() -> C.CDLL:
         "lq_dev_walk_ffn": (C.c_int, [vp, mp, mp, mp, f32p, sz, sz, C.c_uint32, f32p, u32p, u32p]),
         "lq_stack_create": (C.c_int, [vp, mp, mp, mp, sz, sz, sz, C.c_uint32, C.POINTER(vp)]),
         "lq_stack_run": (C.c_int, [vp, vp, f32p, f32p]),
+        "lq_stack_run_host": (C.c_int, [vp, vp, f32p, f32p]),
         "lq_stack_destroy": (None, [vp, vp]),
         "lq_last_walk_stats": (C.c_int, [vp, C.POINTER(WalkStats)]),
         "lq_dev_quantize_q4k": (C.c_int, [vp, f32p, sz, vp]),
@@ -428,6 +429,10 @@ class CudaBackend:
 
     def stack_run(self, stack, h_in_ptr: int, h_out_ptr: int):
         return self._status(self._lib.lq_stack_run(self._h, stack, h_in_ptr, h_out_ptr))
+
+    def stack_run_host(self, stack, h_in_ptr: int, h_out_ptr: int):
+        """All layers of a stack on HOST residuals (pointers to batch*hidden floats): upload, walk, download."""
+        return self._status(self._lib.lq_stack_run_host(self._h, stack, h_in_ptr, h_out_ptr))
 
     def stack_destroy(self, stack):
         self._lib.lq_stack_destroy(self._h, stack)

@@ -648,6 +648,26 @@ static int q4k_host_common(lq_ctx* ctx, const uint8_t* w, size_t w_len, const fl
     float* dx = (float*)ctx->stage;
     float* dout = (float*)(ctx->stage + a256(x_len * 4));
     CK(cudaMemcpyAsync(dx, x, x_len * 4, cudaMemcpyHostToDevice, ctx->stream));
+    if (!exact && seq >= 2 && ((uintptr_t)dw & 15) == 0) {
+        // q4k_matmul: the integer-MMA scan, up to 64 positions per launch
+        rc = ensure_ws(ctx, std::min<size_t>(seq, 64), hidden, num_rows);
+        if (rc) return rc;
+        const Q4kMat m{dw, (int)num_rows, (int)hidden};
+        const size_t tstride = ctx->tok.size() > 1 ? (size_t)((uint8_t*)ctx->tok[1].xn - (uint8_t*)ctx->tok[0].xn) : 0;
+        for (size_t c0 = 0; c0 < seq; c0 += 64) {
+            const size_t nb = std::min<size_t>(64, seq - c0);
+            TokenWs& t0 = ctx->tok[0];
+            launch_prep(dx + c0 * hidden, (int)nb, (int)hidden, 0, 0.0, t0.xn, t0.xa, t0.xb, t0.bscale, t0.bsum, t0.babs,
+                        tstride / sizeof(float), nullptr, ctx->stream);
+            CK(cudaGetLastError());
+            CK(launch_scan_q4k_mma(m, t0, tstride, (int)nb, 0, 0.0f, ctx->d_err, ctx->sm_count, ctx->stream));
+            CK(cudaMemcpy2DAsync(dout + c0 * num_rows, num_rows * 4, t0.scores, tstride ? tstride : num_rows * 4,
+                                 num_rows * 4, nb, cudaMemcpyDeviceToDevice, ctx->stream));
+            ctx->launches += 2;
+        }
+        CK(cudaMemcpyAsync(out, dout, out_len * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        return lq_synchronize(ctx);
+    }
     for (size_t s = 0; s < seq; ++s) {
         if (exact) {
             rc = ensure_ws(ctx, 1, hidden, 32);
@@ -1126,13 +1146,16 @@ int lq_stack_create(lq_ctx* ctx, const lq_matrix* gates, const lq_matrix* ups, c
         if (gates[l].cols != gates[0].cols) return fail(ctx, LQ_REFUSED_SHAPE, "stack: hidden differs per layer");
     }
     lq_stack* s = new lq_stack();
-    s->gates.assign(gates, gates + n_layers);
-    s->ups.assign(ups, ups + n_layers);
-    s->downs.assign(downs_fm, downs_fm + n_layers);
+    s->gates.resize(n_layers);
+    s->ups.resize(n_layers);
+    s->downs.resize(n_layers);
     for (size_t l = 0; l < n_layers; ++l) {
-        s->gates[l].fmt &= 0xff;
-        s->ups[l].fmt &= 0xff;
-        s->downs[l].fmt &= 0xff;
+        // host matrices are uploaded once through the weight cache, device matrices are taken as they are
+        if ((rc = resolve_matrix(ctx, &gates[l], &s->gates[l])) || (rc = resolve_matrix(ctx, &ups[l], &s->ups[l])) ||
+            (rc = resolve_matrix(ctx, &downs_fm[l], &s->downs[l]))) {
+            delete s;
+            return rc;
+        }
     }
     s->batch = batch;
     s->top_k = top_k;
@@ -1216,6 +1239,19 @@ int lq_stack_run(lq_ctx* ctx, lq_stack* s, const float* h_in, float* h_out) {
         CK(cudaGraphLaunch(s->exec, ctx->stream));
     CK(cudaMemcpyAsync(h_out, s->h_out, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
     return LQ_OK;
+}
+
+int lq_stack_run_host(lq_ctx* ctx, lq_stack* s, const float* h_in_host, float* h_out_host) {
+    if (!ctx || !s || (!s->exec && !s->fused) || !h_in_host || !h_out_host) return LQ_ERR_ARGUMENT;
+    const size_t bytes = s->batch * s->hidden * 4;
+    CK(cudaMemcpyAsync(s->h_in, h_in_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    if (s->fused) {
+        int rc = stack_enqueue(ctx, s);
+        if (rc) return rc;
+    } else
+        CK(cudaGraphLaunch(s->exec, ctx->stream));
+    CK(cudaMemcpyAsync(h_out_host, s->h_out, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    return lq_synchronize(ctx);
 }
 
 void lq_stack_destroy(lq_ctx* ctx, lq_stack* s) {

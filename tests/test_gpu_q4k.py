@@ -267,3 +267,32 @@ def test_batched_walk_tensor_core_scan(be, h, n, k, batch):
         want, idx = oracle.run_ffn_token(gate, up, down, hin[t], k)
         assert sorted(h3[t].tolist()) == sorted(idx.tolist())
         assert rel_l2(o3[t] - hin[t], want - hin[t]) < OUT_TOL
+
+
+@pytest.mark.parametrize("rows,cols,seq", [(300, 1024, 8), (3072, 1024, 32), (1000, 2560, 70)])
+def test_matmul_on_tensor_cores_matches_reference(be, rows, cols, seq):
+    # seq >= 2 runs the integer-MMA scan; the reference is q4k_matmul_into (decode, then 8 strided accumulators)
+    m = oracle.quantize_matrix(oracle.FMT_Q4_K, seeded_weights(rows + seq, rows, cols))
+    x = seeded_x(cols + seq, seq, cols)
+    got = be.q4k_matmul(m.data, x, rows, cols, seq)
+    want = oracle.q4k_matmul(m.data, x, rows, cols, seq)
+    assert got.shape == (seq, rows) and rel_l2(got, want) < 1e-4
+    scale = np.abs(x).astype(np.float64) @ np.abs(m.dequantize()).astype(np.float64).T
+    assert np.max(np.abs(got.astype(np.float64) - want) / scale) < 2e-4
+    assert np.array_equal(bits(got), bits(be.q4k_matmul(m.data, x, rows, cols, seq)))
+
+
+def test_stack_run_host_matches_layer_by_layer_oracle(be):
+    import larql_b200
+    h, n, k, L = 1024, 3072, 512, 3
+    ls = [layer(0x57AC + 10 * l, n, h) for l in range(L)]
+    st = be.stack_create([host(m[0]) for m in ls], [host(m[1]) for m in ls], [host(m[2]) for m in ls], 1, k,
+                         larql_b200.WALK_FORCE_SPARSE)
+    hin = seeded_x(0x57AD, 1, h)
+    out = np.empty_like(hin)
+    assert be.stack_run_host(st, hin.ctypes.data, out.ctypes.data)
+    want = hin[0].copy()
+    for l in range(L):
+        want, _ = oracle.run_ffn_token(*ls[l], want, k)
+    assert rel_l2(out[0] - hin[0], want - hin[0]) < OUT_TOL
+    be.stack_destroy(st)
