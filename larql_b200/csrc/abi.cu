@@ -331,14 +331,6 @@ bool fmt_aligned(const lq_matrix& m) {
     return true;
 }
 
-// Reference rows of Q8_0 / MXFP4 / NVFP4 are one f32 chain over the whole row: hidden + 3 roundings
-// on a term's path; the fast path has at most 64.
-float bound_c1_fmt(int hidden) {
-    const double u = std::ldexp(1.0, -24);
-    const double n = (double)hidden + 3.0 + 64.0;
-    return (float)(n * u / (1.0 - n * u) * 1.01);
-}
-
 __global__ void scaled_add_kernel(float* __restrict__ out, const float* __restrict__ src, const float* __restrict__ w,
                                   int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -356,15 +348,14 @@ int enqueue_walk_token_fmt(lq_ctx* ctx, const lq_matrix& gate, const lq_matrix& 
     const XPrep xp = xprep_of(w);
     const bool sparse = k < N;
     cudaStream_t st = ctx->stream;
-    CK(launch_scan_fmt(g, xp, w.scores, sparse ? w.hist : nullptr, &w.sel->bound_bits, bound_c1_fmt(H), ctx->d_err,
-                       ctx->sm_count, st));
+    // The reference rows of these formats are one running f32 sum over the whole row: a rigorous
+    // bound on a re-associated fast score is wide (thousands of band rows at 28672 x 8192), so the
+    // scan itself runs in the reference's order and the selection works on exact scores.
+    CK(launch_scan_exact_fmt(g, w.xn, w.scores, ctx->d_err, st));
+    CK(launch_select(w.scores, N, k, w, ctx->d_err, st));
+    ctx->launches += 2;
     if (sparse) {
-        CK(launch_classify(w.scores, N, k, w, ctx->d_err, st));
-        CK(launch_rescore_fmt(g, w.xn, w.band_idx, &w.sel->n_band, 0, w.band_exact, ctx->sm_count, st));
-        CK(launch_final_pick(w, ctx->d_err, st));
-        ctx->launches += 3;
-    } else {
-        CK(launch_select(w.scores, N, k, w, ctx->d_err, st));
+        CK(launch_final_pick(w, ctx->d_err, st));  // ties at the K-th |score|: the lower rows win
         ctx->launches += 1;
     }
     CK(launch_gather_fmt(u, d, xp, w.hit_idx, w.hit_score, &w.sel->n_sel, k, ctx->partials, ctx->gather_grid, st));

@@ -194,67 +194,272 @@ __global__ void rescore_fmt_kernel(FmtMat m, const float* __restrict__ xn, const
     }
 }
 
-// Element h of row `row`, decoded exactly as the reference's dequantiser does.
+// Exact-order scan: one thread per row walks the row in the reference's element order (one running
+// f32 sum, separate multiplies and add), so the scores ARE the reference's scores and the top-K
+// needs no bound, band or re-score.  The sum over a row cannot be split without changing its bits;
+// rows are the parallelism (one row per thread, the activation broadcast from shared memory, each
+// thread streaming its own row with 16-byte loads that the L1 turns into whole lines).
 template <int FMT>
-__device__ __forceinline__ float decode_elem(const FmtMat& m, size_t row, int h) {
+__global__ void __launch_bounds__(64) scan_exact_fmt_kernel(FmtMat m, const float* __restrict__ xn,
+                                                           float* __restrict__ scores, int* err) {
+    extern __shared__ __align__(16) float xs[];  // [cols]
+    for (int i = threadIdx.x; i < m.cols; i += blockDim.x) xs[i] = xn[i];
+    __syncthreads();
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= m.rows) return;
+    float acc = 0.0f;
     if (FMT == LQ_FMT_Q8_0) {
-        const uint8_t* p = m.data + (row * (m.cols / 32) + h / 32) * 34;
-        return __fmul_rn((float)(int8_t)p[2 + (h & 31)], f16_bits_to_f32((uint32_t)p[0] | ((uint32_t)p[1] << 8)));
+        const int nb = m.cols / 32;
+        const uint16_t* p = reinterpret_cast<const uint16_t*>(m.data + (size_t)row * nb * 34);
+        for (int b = 0; b < nb; ++b, p += 17) {
+            const float d = f16_bits_to_f32(p[0]);
+            uint32_t q[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) q[j] = (uint32_t)p[1 + 2 * j] | ((uint32_t)p[2 + 2 * j] << 16);
+            const float4* xv = reinterpret_cast<const float4*>(xs + b * 32);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float4 x4 = xv[j];
+                const float xe[4] = {x4.x, x4.y, x4.z, x4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float qf = (float)(int)(int8_t)(q[j] >> (8 * e));
+                    acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(qf, d), xe[e]));
+                }
+            }
+        }
     } else if (FMT == LQ_FMT_MXFP4) {
-        const size_t g = row * (m.cols / 32) + h / 32;
-        const uint32_t byte = m.data[g * 16 + (h & 31) / 2];
-        return __fmul_rn(e2m1_to_f32((h & 1) ? (byte >> 4) : (byte & 15u)), e8m0_to_f32(m.scales[g]));
+        const int nb = m.cols / 32;
+        const uint4* p = reinterpret_cast<const uint4*>(m.data + (size_t)row * nb * 16);
+        const uint8_t* sc = m.scales + (size_t)row * nb;
+        for (int b = 0; b < nb; ++b) {
+            const uint4 w = p[b];
+            const float scale = e8m0_to_f32(sc[b]);
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+            const float4* xv = reinterpret_cast<const float4*>(xs + b * 32);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 xa4 = xv[2 * j], xb4 = xv[2 * j + 1];
+                const float xe[8] = {xa4.x, xa4.y, xa4.z, xa4.w, xb4.x, xb4.y, xb4.z, xb4.w};
+#pragma unroll
+                for (int e = 0; e < 8; ++e)  // nibble e of the word: low nibble of a byte first
+                    acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(e2m1_to_f32((ww[j] >> (4 * e)) & 15u), scale), xe[e]));
+            }
+        }
     } else {
-        const size_t g = row * (m.cols / 16) + h / 16;
-        const uint32_t byte = m.data[g * 8 + (h & 15) / 2];
-        return __fmul_rn(__fmul_rn(m.ts, e4m3_to_f32(m.scales[g])), e2m1_to_f32((h & 1) ? (byte >> 4) : (byte & 15u)));
+        const int ng = m.cols / 16;
+        const uint2* p = reinterpret_cast<const uint2*>(m.data + (size_t)row * ng * 8);
+        const uint8_t* sc = m.scales + (size_t)row * ng;
+        for (int g = 0; g < ng; ++g) {
+            const uint2 w = p[g];
+            const float step = __fmul_rn(m.ts, e4m3_to_f32(sc[g]));
+            const uint32_t ww[2] = {w.x, w.y};
+            const float4* xv = reinterpret_cast<const float4*>(xs + g * 16);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float4 xa4 = xv[2 * j], xb4 = xv[2 * j + 1];
+                const float xe[8] = {xa4.x, xa4.y, xa4.z, xa4.w, xb4.x, xb4.y, xb4.z, xb4.w};
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(step, e2m1_to_f32((ww[j] >> (4 * e)) & 15u)), xe[e]));
+            }
+        }
+    }
+    scores[row] = acc;
+    if (acc != acc) set_err(err, DEV_ERR_NAN_SCORE);
+}
+
+// Exact-order scan, staged: the same arithmetic as scan_exact_fmt_kernel, but a warp brings the next
+// 256 elements of its 32 rows into shared memory with coalesced 16-byte loads (rows are a power-of-two
+// stride apart, which makes per-thread streaming thrash the L1 sets) and every lane then walks its own
+// row's chunk from shared memory.  Needs cols % 256 == 0 and 16-byte aligned streams.
+template <int FMT>
+struct StagedGeom {
+    static constexpr int CHB = FMT == LQ_FMT_Q8_0 ? 272 : 128;                           // data bytes per row and chunk
+    static constexpr int SCB = FMT == LQ_FMT_NVFP4 ? 16 : (FMT == LQ_FMT_MXFP4 ? 8 : 0);  // scale bytes
+    static constexpr int ROWB = CHB + (FMT == LQ_FMT_Q8_0 ? 32 : 16);                    // padded: shifts the banks per row
+    static constexpr int WARP_BYTES = 32 * ROWB + 32 * 32;
+};
+
+template <int FMT>
+__global__ void __launch_bounds__(128) scan_exact_staged_kernel(FmtMat m, const float* __restrict__ xn,
+                                                               float* __restrict__ scores, int* err) {
+    using SG = StagedGeom<FMT>;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    float* xs = reinterpret_cast<float*>(smem_raw);  // [cols]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint8_t* wbuf = smem_raw + (size_t)m.cols * 4 + (size_t)warp * SG::WARP_BYTES;
+    uint8_t* sbuf = wbuf + 32 * SG::ROWB;  // [32][32] scale bytes
+    for (int i = threadIdx.x; i < m.cols; i += blockDim.x) xs[i] = xn[i];
+    __syncthreads();
+    const int row0 = (blockIdx.x * 4 + warp) * 32;
+    if (row0 >= m.rows) return;
+    const int row = row0 + lane;
+    const int n_chunks = m.cols / 256;
+    const size_t data_stride = (size_t)n_chunks * SG::CHB;
+    const size_t sc_stride = (size_t)n_chunks * SG::SCB;
+    constexpr int PIECES = SG::CHB / 16;  // 16-byte pieces per row and chunk
+    float acc = 0.0f;
+    for (int c = 0; c < n_chunks; ++c) {
+        // coalesced: consecutive lanes take consecutive 16-byte pieces of a row
+        for (int p = lane; p < 32 * PIECES; p += 32) {
+            const int r = p / PIECES, piece = p % PIECES;
+            const int rr = min(row0 + r, m.rows - 1);
+            const uint4 v = *reinterpret_cast<const uint4*>(m.data + (size_t)rr * data_stride + (size_t)c * SG::CHB + piece * 16);
+            *reinterpret_cast<uint4*>(wbuf + r * SG::ROWB + piece * 16) = v;
+        }
+        if (SG::SCB == 16) {
+            const int rr = min(row0 + lane, m.rows - 1);
+            *reinterpret_cast<uint4*>(sbuf + lane * 32) =
+                *reinterpret_cast<const uint4*>(m.scales + (size_t)rr * sc_stride + (size_t)c * 16);
+        } else if (SG::SCB == 8) {
+            const int rr = min(row0 + lane, m.rows - 1);
+            *reinterpret_cast<uint2*>(sbuf + lane * 32) =
+                *reinterpret_cast<const uint2*>(m.scales + (size_t)rr * sc_stride + (size_t)c * 8);
+        }
+        __syncwarp();
+        const uint8_t* mine = wbuf + lane * SG::ROWB;
+        const float* xc = xs + c * 256;
+        if (FMT == LQ_FMT_Q8_0) {
+#pragma unroll 2
+            for (int b = 0; b < 8; ++b) {
+                const uint16_t* p = reinterpret_cast<const uint16_t*>(mine + b * 34);
+                const float d = f16_bits_to_f32(p[0]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint32_t q = (uint32_t)p[1 + 2 * j] | ((uint32_t)p[2 + 2 * j] << 16);
+                    const float4 x4 = *reinterpret_cast<const float4*>(xc + b * 32 + 4 * j);
+                    const float xe[4] = {x4.x, x4.y, x4.z, x4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        acc = __fadd_rn(acc, __fmul_rn(__fmul_rn((float)(int)(int8_t)(q >> (8 * e)), d), xe[e]));
+                }
+            }
+        } else {
+            constexpr int GE = FMT == LQ_FMT_MXFP4 ? 32 : 16;  // elements per scale
+#pragma unroll 2
+            for (int w8 = 0; w8 < 8; ++w8) {  // 16 bytes = 32 elements
+                const uint4 w = *reinterpret_cast<const uint4*>(mine + w8 * 16);
+                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int e0 = w8 * 32 + j * 8;
+                    const uint32_t sb = sbuf[lane * 32 + e0 / GE];
+                    const float scale = FMT == LQ_FMT_MXFP4 ? e8m0_to_f32(sb) : __fmul_rn(m.ts, e4m3_to_f32(sb));
+                    const float4 xa4 = *reinterpret_cast<const float4*>(xc + e0), xb4 = *reinterpret_cast<const float4*>(xc + e0 + 4);
+                    const float xe[8] = {xa4.x, xa4.y, xa4.z, xa4.w, xb4.x, xb4.y, xb4.z, xb4.w};
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float v = e2m1_to_f32((ww[j] >> (4 * e)) & 15u);
+                        const float t = FMT == LQ_FMT_MXFP4 ? __fmul_rn(v, scale) : __fmul_rn(scale, v);
+                        acc = __fadd_rn(acc, __fmul_rn(t, xe[e]));
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+    if (row < m.rows) {
+        scores[row] = acc;
+        if (acc != acc) set_err(err, DEV_ERR_NAN_SCORE);
     }
 }
 
-// Gather: each CTA takes a contiguous slice of the hit list; per hit the CTA's warps share the
-// up dot (fast form), then every thread adds act * down[row][h] into its columns of out[H]
-// kept in shared memory.  Partials per CTA; `finish` adds them in fixed order.
+// Gather: each CTA takes a contiguous slice of the hit list, 64 hits at a time.  First the up dots
+// of the chunk, one warp per hit (fast form), and the activations; then, hit by hit, every thread
+// adds act * down[row] for its own 32-column block(s) - one vector load of the block, the 32 values
+// decoded exactly as the reference's dequantiser does - into register accumulators.  Per-CTA
+// partials; `finish` adds them in fixed order.
 template <int FMT>
+__device__ __forceinline__ void decode_block32(const FmtMat& m, size_t row, int blk, float (&v)[32]) {
+    const int nblk = m.cols / 32;
+    if (FMT == LQ_FMT_Q8_0) {
+        const uint16_t* p = reinterpret_cast<const uint16_t*>(m.data + (row * nblk + blk) * 34);
+        const float d = f16_bits_to_f32(p[0]);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const uint32_t q = p[1 + j];
+            v[2 * j] = __fmul_rn((float)(int)(int8_t)(q & 0xff), d);
+            v[2 * j + 1] = __fmul_rn((float)(int)(int8_t)(q >> 8), d);
+        }
+    } else if (FMT == LQ_FMT_MXFP4) {
+        const uint4 w = *reinterpret_cast<const uint4*>(m.data + (row * nblk + blk) * 16);
+        const float scale = e8m0_to_f32(m.scales[row * nblk + blk]);
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int e = 0; e < 32; ++e) v[e] = __fmul_rn(e2m1_to_f32((ww[e >> 3] >> (4 * (e & 7))) & 15u), scale);
+    } else {
+        const uint4 w = *reinterpret_cast<const uint4*>(m.data + (row * nblk + blk) * 16);
+        const uint32_t sc2 = *reinterpret_cast<const uint16_t*>(m.scales + (row * nblk + blk) * 2);
+        const float s0 = __fmul_rn(m.ts, e4m3_to_f32(sc2 & 0xff)), s1 = __fmul_rn(m.ts, e4m3_to_f32(sc2 >> 8));
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int e = 0; e < 32; ++e)
+            v[e] = __fmul_rn(e < 16 ? s0 : s1, e2m1_to_f32((ww[e >> 3] >> (4 * (e & 7))) & 15u));
+    }
+}
+
+template <int FMT, int BPT>
 __global__ void __launch_bounds__(FK_THREADS) gather_fmt_kernel(FmtMat up, FmtMat down, XPrep xp,
                                                                const uint32_t* __restrict__ hit_idx,
                                                                const float* __restrict__ hit_score,
                                                                const int* __restrict__ n_hits_dev, int n_hits_host,
                                                                float* __restrict__ partials) {
-    extern __shared__ __align__(16) float out_s[];  // [H]
-    __shared__ float s_part[FK_THREADS / 32];
-    __shared__ float s_act;
+    __shared__ float act_s[64];
+    __shared__ uint32_t row_s[64];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int H = up.cols;
+    const int H = up.cols, nblk = H / 32;
     const float lut = fp4_lut_lane(lane);
-    for (int h = tid; h < H; h += FK_THREADS) out_s[h] = 0.0f;
+    float acc[BPT][32];
+#pragma unroll
+    for (int b = 0; b < BPT; ++b)
+#pragma unroll
+        for (int e = 0; e < 32; ++e) acc[b][e] = 0.0f;
     const int n_hits = n_hits_dev ? *n_hits_dev : n_hits_host;
     const int per = (n_hits + gridDim.x - 1) / gridDim.x;
     const int h0 = min(n_hits, (int)blockIdx.x * per), h1 = min(n_hits, h0 + per);
-    __syncthreads();
-    for (int i = h0; i < h1; ++i) {
-        const size_t row = hit_idx[i];
-        // up dot: warp w takes the row's blocks w*32+lane, +256, ... by viewing the row as 8 sub-rows
-        // is format specific; simpler and still parallel: warp 0..7 each compute the whole dot of a
-        // different hit would need 8 hits in flight.  Here one warp does the dot, the rest wait.
-        if (warp == 0) {
+    for (int c0 = h0; c0 < h1; c0 += 64) {
+        const int nh = min(64, h1 - c0);
+        for (int i = warp; i < nh; i += FK_THREADS / 32) {
+            const uint32_t row = hit_idx[c0 + i];
             float b;
             const float u = fast_row<FMT>(up, row, xp, 0.0f, b, lane, lut);
             if (lane == 0) {
-                const float gs = hit_score[i];
+                const float gs = hit_score[c0 + i];
                 const float sig = __fdiv_rn(1.0f, 1.0f + expf(-gs));
                 const float act = (gs * sig) * u;
-                s_act = fabsf(act) > FK_NOISE_FLOOR ? act : 0.0f;
+                act_s[i] = fabsf(act) > FK_NOISE_FLOOR ? act : 0.0f;
+                row_s[i] = row;
             }
         }
         __syncthreads();
-        const float act = s_act;
-        if (act != 0.0f)
-            for (int h = tid; h < H; h += FK_THREADS) out_s[h] = fmaf(act, decode_elem<FMT>(down, row, h), out_s[h]);
+        for (int i = 0; i < nh; ++i) {
+            const float act = act_s[i];
+            if (act == 0.0f) continue;
+            const size_t row = row_s[i];
+#pragma unroll
+            for (int b = 0; b < BPT; ++b) {
+                const int blk = tid + b * FK_THREADS;
+                if (blk < nblk) {
+                    float v[32];
+                    decode_block32<FMT>(down, row, blk, v);
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) acc[b][e] = fmaf(act, v[e], acc[b][e]);
+                }
+            }
+        }
         __syncthreads();
     }
-    (void)s_part;
     float* dst = partials + (size_t)blockIdx.x * H;
-    for (int h = tid; h < H; h += FK_THREADS) dst[h] = out_s[h];
+#pragma unroll
+    for (int b = 0; b < BPT; ++b) {
+        const int blk = tid + b * FK_THREADS;
+        if (blk < nblk) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4)
+                *reinterpret_cast<float4*>(dst + blk * 32 + e) = make_float4(acc[b][e], acc[b][e + 1], acc[b][e + 2], acc[b][e + 3]);
+        }
+    }
 }
 
 }  // namespace
@@ -278,6 +483,45 @@ cudaError_t launch_scan_fmt(const FmtMat& m, const XPrep& xp, float* scores, uin
     return cudaGetLastError();
 }
 
+cudaError_t launch_scan_exact_fmt(const FmtMat& m, const float* xn, float* scores, int* err, cudaStream_t st) {
+    if (m.rows == 0) return cudaSuccess;
+    const bool aligned = (((uintptr_t)m.data | (uintptr_t)(m.scales ? m.scales : m.data)) & 15) == 0;
+    if (m.cols % 256 == 0 && aligned) {
+        const int sgrid = (m.rows + 127) / 128;
+#define SCALL(F)                                                                                                   \
+    {                                                                                                              \
+        const size_t sm = (size_t)m.cols * 4 + 4 * (size_t)StagedGeom<F>::WARP_BYTES;                              \
+        static bool attr = false;                                                                                  \
+        if (!attr) {                                                                                               \
+            cudaError_t e = cudaFuncSetAttribute(scan_exact_staged_kernel<F>,                                      \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);         \
+            if (e != cudaSuccess) return e;                                                                        \
+            attr = true;                                                                                           \
+        }                                                                                                          \
+        scan_exact_staged_kernel<F><<<sgrid, 128, sm, st>>>(m, xn, scores, err);                                   \
+    }
+        FMT_DISPATCH(m.fmt, SCALL)
+#undef SCALL
+        return cudaGetLastError();
+    }
+    const int grid = (m.rows + 63) / 64;
+    const size_t smem = (size_t)m.cols * sizeof(float);
+#define CALL(F)                                                                                                     \
+    {                                                                                                               \
+        static bool attr = false;                                                                                   \
+        if (!attr) {                                                                                                \
+            cudaError_t e = cudaFuncSetAttribute(scan_exact_fmt_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                                 64 * 1024);                                                        \
+            if (e != cudaSuccess) return e;                                                                         \
+            attr = true;                                                                                            \
+        }                                                                                                           \
+        scan_exact_fmt_kernel<F><<<grid, 64, smem, st>>>(m, xn, scores, err);                                        \
+    }
+    FMT_DISPATCH(m.fmt, CALL)
+#undef CALL
+    return cudaGetLastError();
+}
+
 cudaError_t launch_rescore_fmt(const FmtMat& m, const float* xn, const uint32_t* rows_idx, const int* n_rows_dev,
                                int n_rows_host, float* out, int sm_count, cudaStream_t st) {
     int grid = n_rows_dev ? sm_count * 4 : (n_rows_host + 63) / 64;
@@ -292,19 +536,16 @@ cudaError_t launch_rescore_fmt(const FmtMat& m, const float* xn, const uint32_t*
 cudaError_t launch_gather_fmt(const FmtMat& up, const FmtMat& down, const XPrep& xp, const uint32_t* hit_idx,
                               const float* hit_score, const int* n_hits_dev, int n_hits_host, float* partials,
                               int grid, cudaStream_t st) {
-    if (up.fmt != down.fmt || up.cols != down.cols) return cudaErrorInvalidValue;
-    const size_t smem = (size_t)up.cols * sizeof(float);
-#define CALL(F)                                                                                                  \
-    {                                                                                                            \
-        static bool attr = false;                                                                                \
-        if (!attr) {                                                                                             \
-            cudaError_t e = cudaFuncSetAttribute(gather_fmt_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                                 64 * 1024);                                                     \
-            if (e != cudaSuccess) return e;                                                                      \
-            attr = true;                                                                                         \
-        }                                                                                                        \
-        gather_fmt_kernel<F><<<grid, FK_THREADS, smem, st>>>(up, down, xp, hit_idx, hit_score, n_hits_dev,       \
-                                                            n_hits_host, partials);                             \
+    if (up.fmt != down.fmt || up.cols != down.cols || up.cols % 32 != 0 || up.cols > 16384) return cudaErrorInvalidValue;
+    const int bpt = (up.cols / 32 + FK_THREADS - 1) / FK_THREADS;  // 32-column blocks per thread: 1 or 2
+#define CALL(F)                                                                                                \
+    {                                                                                                          \
+        if (bpt <= 1)                                                                                          \
+            gather_fmt_kernel<F, 1><<<grid, FK_THREADS, 0, st>>>(up, down, xp, hit_idx, hit_score, n_hits_dev,  \
+                                                                n_hits_host, partials);                        \
+        else                                                                                                   \
+            gather_fmt_kernel<F, 2><<<grid, FK_THREADS, 0, st>>>(up, down, xp, hit_idx, hit_score, n_hits_dev,  \
+                                                                n_hits_host, partials);                        \
     }
     FMT_DISPATCH(up.fmt, CALL)
 #undef CALL
