@@ -281,6 +281,50 @@ struct StagedGeom {
     static constexpr int WARP_BYTES = 32 * ROWB + 32 * 32;
 };
 
+// The 32 reference products (decoded weight times activation, each rounded as the reference
+// rounds it) of one 32-element block of a staged row chunk.
+template <int FMT>
+__device__ __forceinline__ void block_products(const uint8_t* mine, const uint8_t* sc, float ts, int b, const float* xc,
+                                               float (&p)[32]) {
+    float xe[32];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float4 x4 = *reinterpret_cast<const float4*>(xc + b * 32 + 4 * j);
+        xe[4 * j] = x4.x; xe[4 * j + 1] = x4.y; xe[4 * j + 2] = x4.z; xe[4 * j + 3] = x4.w;
+    }
+    if (FMT == LQ_FMT_Q8_0) {
+        const uint16_t* q = reinterpret_cast<const uint16_t*>(mine + b * 34);
+        const float d = f16_bits_to_f32(q[0]);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const uint32_t w = q[1 + j];
+            p[2 * j] = __fmul_rn(__fmul_rn((float)(int)(int8_t)(w & 0xff), d), xe[2 * j]);
+            p[2 * j + 1] = __fmul_rn(__fmul_rn((float)(int)(int8_t)(w >> 8), d), xe[2 * j + 1]);
+        }
+    } else {
+        const uint4 w = *reinterpret_cast<const uint4*>(mine + b * 16);
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+        if (FMT == LQ_FMT_MXFP4) {
+            const float scale = e8m0_to_f32(sc[b]);
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+                p[e] = __fmul_rn(__fmul_rn(e2m1_to_f32((ww[e >> 3] >> (4 * (e & 7))) & 15u), scale), xe[e]);
+        } else {
+            const float s0 = __fmul_rn(ts, e4m3_to_f32(sc[2 * b])), s1 = __fmul_rn(ts, e4m3_to_f32(sc[2 * b + 1]));
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+                p[e] = __fmul_rn(__fmul_rn(e < 16 ? s0 : s1, e2m1_to_f32((ww[e >> 3] >> (4 * (e & 7))) & 15u)), xe[e]);
+        }
+    }
+}
+
+__device__ __forceinline__ void cp_async16_f(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async8_f(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+
 template <int FMT>
 __global__ void __launch_bounds__(128) scan_exact_staged_kernel(FmtMat m, const float* __restrict__ xn,
                                                                float* __restrict__ scores, int* err) {
@@ -288,8 +332,7 @@ __global__ void __launch_bounds__(128) scan_exact_staged_kernel(FmtMat m, const 
     extern __shared__ __align__(16) uint8_t smem_raw[];
     float* xs = reinterpret_cast<float*>(smem_raw);  // [cols]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    uint8_t* wbuf = smem_raw + (size_t)m.cols * 4 + (size_t)warp * SG::WARP_BYTES;
-    uint8_t* sbuf = wbuf + 32 * SG::ROWB;  // [32][32] scale bytes
+    uint8_t* wbase = smem_raw + (size_t)m.cols * 4 + (size_t)warp * 2 * SG::WARP_BYTES;  // two buffers per warp
     for (int i = threadIdx.x; i < m.cols; i += blockDim.x) xs[i] = xn[i];
     __syncthreads();
     const int row0 = (blockIdx.x * 4 + warp) * 32;
@@ -299,65 +342,49 @@ __global__ void __launch_bounds__(128) scan_exact_staged_kernel(FmtMat m, const 
     const size_t data_stride = (size_t)n_chunks * SG::CHB;
     const size_t sc_stride = (size_t)n_chunks * SG::SCB;
     constexpr int PIECES = SG::CHB / 16;  // 16-byte pieces per row and chunk
-    float acc = 0.0f;
-    for (int c = 0; c < n_chunks; ++c) {
-        // coalesced: consecutive lanes take consecutive 16-byte pieces of a row
+    // coalesced asynchronous copy of chunk c of this warp's 32 rows into buffer (c & 1)
+    auto stage = [&](int c) {
+        uint8_t* wbuf = wbase + (c & 1) * SG::WARP_BYTES;
         for (int p = lane; p < 32 * PIECES; p += 32) {
             const int r = p / PIECES, piece = p % PIECES;
             const int rr = min(row0 + r, m.rows - 1);
-            const uint4 v = *reinterpret_cast<const uint4*>(m.data + (size_t)rr * data_stride + (size_t)c * SG::CHB + piece * 16);
-            *reinterpret_cast<uint4*>(wbuf + r * SG::ROWB + piece * 16) = v;
+            cp_async16_f(wbuf + r * SG::ROWB + piece * 16, m.data + (size_t)rr * data_stride + (size_t)c * SG::CHB + piece * 16);
         }
-        if (SG::SCB == 16) {
+        if (SG::SCB) {
             const int rr = min(row0 + lane, m.rows - 1);
-            *reinterpret_cast<uint4*>(sbuf + lane * 32) =
-                *reinterpret_cast<const uint4*>(m.scales + (size_t)rr * sc_stride + (size_t)c * 16);
-        } else if (SG::SCB == 8) {
-            const int rr = min(row0 + lane, m.rows - 1);
-            *reinterpret_cast<uint2*>(sbuf + lane * 32) =
-                *reinterpret_cast<const uint2*>(m.scales + (size_t)rr * sc_stride + (size_t)c * 8);
+            uint8_t* sdst = wbuf + 32 * SG::ROWB + lane * 32;
+            const uint8_t* ssrc = m.scales + (size_t)rr * sc_stride + (size_t)c * SG::SCB;
+            if (SG::SCB == 16) cp_async16_f(sdst, ssrc);
+            else cp_async8_f(sdst, ssrc);
         }
-        __syncwarp();
-        const uint8_t* mine = wbuf + lane * SG::ROWB;
-        const float* xc = xs + c * 256;
-        if (FMT == LQ_FMT_Q8_0) {
-#pragma unroll 2
-            for (int b = 0; b < 8; ++b) {
-                const uint16_t* p = reinterpret_cast<const uint16_t*>(mine + b * 34);
-                const float d = f16_bits_to_f32(p[0]);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const uint32_t q = (uint32_t)p[1 + 2 * j] | ((uint32_t)p[2 + 2 * j] << 16);
-                    const float4 x4 = *reinterpret_cast<const float4*>(xc + b * 32 + 4 * j);
-                    const float xe[4] = {x4.x, x4.y, x4.z, x4.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e)
-                        acc = __fadd_rn(acc, __fmul_rn(__fmul_rn((float)(int)(int8_t)(q >> (8 * e)), d), xe[e]));
-                }
-            }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float acc = 0.0f;
+    stage(0);
+    for (int c = 0; c < n_chunks; ++c) {
+        if (c + 1 < n_chunks) {
+            stage(c + 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
-            constexpr int GE = FMT == LQ_FMT_MXFP4 ? 32 : 16;  // elements per scale
-#pragma unroll 2
-            for (int w8 = 0; w8 < 8; ++w8) {  // 16 bytes = 32 elements
-                const uint4 w = *reinterpret_cast<const uint4*>(mine + w8 * 16);
-                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int e0 = w8 * 32 + j * 8;
-                    const uint32_t sb = sbuf[lane * 32 + e0 / GE];
-                    const float scale = FMT == LQ_FMT_MXFP4 ? e8m0_to_f32(sb) : __fmul_rn(m.ts, e4m3_to_f32(sb));
-                    const float4 xa4 = *reinterpret_cast<const float4*>(xc + e0), xb4 = *reinterpret_cast<const float4*>(xc + e0 + 4);
-                    const float xe[8] = {xa4.x, xa4.y, xa4.z, xa4.w, xb4.x, xb4.y, xb4.z, xb4.w};
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const float v = e2m1_to_f32((ww[j] >> (4 * e)) & 15u);
-                        const float t = FMT == LQ_FMT_MXFP4 ? __fmul_rn(v, scale) : __fmul_rn(scale, v);
-                        acc = __fadd_rn(acc, __fmul_rn(t, xe[e]));
-                    }
-                }
-            }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncwarp();
+        const uint8_t* wbuf = wbase + (c & 1) * SG::WARP_BYTES;
+        const uint8_t* mine = wbuf + lane * SG::ROWB;
+        const uint8_t* sc = wbuf + 32 * SG::ROWB + lane * 32;
+        const float* xc = xs + c * 256;
+        // products of block b+1 are independent of the running sum: they fill the issue slots that
+        // the chain of dependent adds of block b leaves empty
+        float p[32], pn[32];
+        block_products<FMT>(mine, sc, m.ts, 0, xc, p);
+        for (int b = 0; b < 8; ++b) {
+            if (b + 1 < 8) block_products<FMT>(mine, sc, m.ts, b + 1, xc, pn);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) acc = __fadd_rn(acc, p[e]);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) p[e] = pn[e];
+        }
+        __syncwarp();  // every lane is done with this buffer before chunk c+2 is copied into it
     }
     if (row < m.rows) {
         scores[row] = acc;
@@ -490,7 +517,7 @@ cudaError_t launch_scan_exact_fmt(const FmtMat& m, const float* xn, float* score
         const int sgrid = (m.rows + 127) / 128;
 #define SCALL(F)                                                                                                   \
     {                                                                                                              \
-        const size_t sm = (size_t)m.cols * 4 + 4 * (size_t)StagedGeom<F>::WARP_BYTES;                              \
+        const size_t sm = (size_t)m.cols * 4 + 8 * (size_t)StagedGeom<F>::WARP_BYTES;                              \
         static bool attr = false;                                                                                  \
         if (!attr) {                                                                                               \
             cudaError_t e = cudaFuncSetAttribute(scan_exact_staged_kernel<F>,                                      \
