@@ -232,6 +232,10 @@ LQ_API int lq_dev_shard_gather(lq_ctx* ctx, const lq_matrix* up_shard, const lq_
                                const int32_t* packs, int world, int rank, size_t cap, size_t top_k,
                                size_t row_offset, float* out_partial);
 
+/* The rows this rank selected in its last lq_dev_shard_gather, LOCAL to its shard (add the shard's row
+ * offset for global rows), unordered; *count is their number, at most cap of them are copied to the host. */
+LQ_API int lq_dev_shard_hits(lq_ctx* ctx, uint32_t* idx_out_host, size_t cap, size_t* count);
+
 /* MoE expert walk (cpu_moe_forward's combine, crates/larql-compute/src/cpu/ops/moe/forward.rs:24-140,
  * over walked experts): out[t] = sum_j w[t,j] * walk(expert idx[t,j], x[t]) with lq_moe_route's
  * selection and lq_walk_ffn's per-expert top_k.  gates/ups/downs_fm: n_experts matrices each.

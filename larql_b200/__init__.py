@@ -37,7 +37,7 @@ EXPORTS = [
     "lq_stack_create", "lq_stack_run", "lq_stack_destroy", "lq_last_walk_stats", "lq_dev_quantize_q4k",
     "lq_profile_walk", "lq_fused_phase_us", "lq_q4k_matvec_static", "lq_dev_shard_scan", "lq_dev_shard_classify",
     "lq_dev_shard_gather", "lq_gemv", "lq_q8_0_gemv", "lq_mxfp4_gemv", "lq_nvfp4_gemv", "lq_moe_route",
-    "lq_moe_walk_ffn", "lq_stack_run_host",
+    "lq_moe_walk_ffn", "lq_stack_run_host", "lq_dev_shard_hits",
 ]
 
 
@@ -93,6 +93,7 @@ def load_library() -> C.CDLL:
         "lq_stack_create": (C.c_int, [vp, mp, mp, mp, sz, sz, sz, C.c_uint32, C.POINTER(vp)]),
         "lq_stack_run": (C.c_int, [vp, vp, f32p, f32p]),
         "lq_stack_run_host": (C.c_int, [vp, vp, f32p, f32p]),
+        "lq_dev_shard_hits": (C.c_int, [vp, u32p, sz, C.POINTER(sz)]),
         "lq_stack_destroy": (None, [vp, vp]),
         "lq_last_walk_stats": (C.c_int, [vp, C.POINTER(WalkStats)]),
         "lq_dev_quantize_q4k": (C.c_int, [vp, f32p, sz, vp]),
@@ -407,6 +408,14 @@ class CudaBackend:
     def dev_shard_scan(self, gate, x_ptr: int, flags: int, rank: int, world: int, hist_ptr: int):
         g = gate.c()
         return self._status(self._lib.lq_dev_shard_scan(self._h, C.byref(g), x_ptr, flags, rank, world, hist_ptr))
+
+    def last_shard_hits(self, row_offset: int = 0):
+        """Global rows this rank selected in its last shard gather (unordered)."""
+        cnt = C.c_size_t(0)
+        self._status(self._lib.lq_dev_shard_hits(self._h, None, 0, C.byref(cnt)))
+        idx = np.zeros(max(cnt.value, 1), np.uint32)
+        self._status(self._lib.lq_dev_shard_hits(self._h, idx.ctypes.data, cnt.value, C.byref(cnt)))
+        return [int(i) + int(row_offset) for i in idx[:cnt.value]]
 
     def dev_shard_classify(self, gate, hist_ptr: int, world: int, top_k: int, row_offset: int, pack_ptr: int, cap: int):
         g = gate.c()

@@ -1029,9 +1029,10 @@ int lq_profile_walk(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, con
 static int shard_check(lq_ctx* ctx, const lq_matrix* m, const char* name) {
     int rc = check_matrix(ctx, m, name);
     if (rc) return rc;
-    if ((m->fmt & 0xff) != LQ_FMT_Q4_K) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "sharded walk: Q4_K only");
-    if (m->cols > 16384 || m->cols == 0 || m->rows == 0) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "sharded walk: shape");
-    if (((uintptr_t)m->data & 15) != 0) return fail(ctx, LQ_ERR_ARGUMENT, "sharded walk: weights not 16-byte aligned");
+    if (m->cols > 16384 || m->cols == 0 || m->cols % 32 != 0 || m->rows == 0)
+        return fail(ctx, LQ_REFUSED_UNSUPPORTED, "sharded walk: shape");
+    if ((m->fmt & 0xff) == LQ_FMT_Q4_K ? (((uintptr_t)m->data & 15) != 0) : !fmt_aligned(*m))
+        return fail(ctx, LQ_ERR_ARGUMENT, "sharded walk: weights not block aligned");
     return LQ_OK;
 }
 
@@ -1049,6 +1050,13 @@ int lq_dev_shard_scan(lq_ctx* ctx, const lq_matrix* gate_shard, const float* x, 
     launch_prep(x, 1, H, (flags & LQ_WALK_RMSNORM) ? 1 : 0, 1e-6, w.xn, w.xa, w.xb, w.bscale, w.bsum, w.babs, 0,
                 ctx->d_err, st);
     CK(cudaGetLastError());
+    if ((gate_shard->fmt & 0xff) != LQ_FMT_Q4_K) {
+        // exact-order scores: the bound slot stays zero
+        CK(launch_scan_exact_fmt(fmtmat_of(*gate_shard), w.xn, w.scores, ctx->d_err, st));
+        CK(launch_hist_abs(w.scores, N, hist_buf, st));
+        ctx->launches += 3;
+        return LQ_OK;
+    }
     const Q4kMat g{(const uint8_t*)gate_shard->data, N, H};
     CK(launch_scan_q4k(g, xprep_of(w), w.scores, hist_buf, &w.sel->bound_bits, bound_c1(H), ctx->d_err, ctx->sm_count,
                        st));
@@ -1071,9 +1079,13 @@ int lq_dev_shard_classify(lq_ctx* ctx, const lq_matrix* gate_shard, uint32_t* hi
     TokenWs wh = w;
     wh.hist = hist_buf;  // global histogram; the classify kernel clears it for the next layer
     CK(launch_classify(w.scores, N, (int)top_k, wh, ctx->d_err, st));
-    const Q4kMat g{(const uint8_t*)gate_shard->data, N, H};
-    CK(launch_rescore_q4k(g, w.xn, w.band_idx, &w.sel->n_band, 0, w.band_exact, w, (int)top_k, 0, ctx->d_err,
-                          ctx->sm_count, st));
+    if ((gate_shard->fmt & 0xff) != LQ_FMT_Q4_K) {
+        CK(launch_rescore_fmt(fmtmat_of(*gate_shard), w.xn, w.band_idx, &w.sel->n_band, 0, w.band_exact, ctx->sm_count, st));
+    } else {
+        const Q4kMat g{(const uint8_t*)gate_shard->data, N, H};
+        CK(launch_rescore_q4k(g, w.xn, w.band_idx, &w.sel->n_band, 0, w.band_exact, w, (int)top_k, 0, ctx->d_err,
+                              ctx->sm_count, st));
+    }
     CK(launch_shard_pack(w, (uint32_t)row_offset, (int)cap, pack, ctx->d_err, st));
     ctx->launches += 4;
     return LQ_OK;
@@ -1091,11 +1103,31 @@ int lq_dev_shard_gather(lq_ctx* ctx, const lq_matrix* up_shard, const lq_matrix*
     TokenWs w = ctx->tok[0];
     cudaStream_t st = ctx->stream;
     CK(launch_shard_pick(packs, world, rank, (int)cap, (int)top_k, (uint32_t)row_offset, w, ctx->d_err, st));
-    const Q4kMat u{(const uint8_t*)up_shard->data, N, H}, d{(const uint8_t*)down_shard->data, N, H};
-    CK(launch_gather_q4k(u, d, xprep_of(w), w.hit_idx, w.hit_score, &w.sel->n_sel, N, ctx->partials, ctx->gather_grid,
-                         ctx->d_err, st));
+    if ((up_shard->fmt & 0xff) != (down_shard->fmt & 0xff))
+        return fail(ctx, LQ_REFUSED_UNSUPPORTED, "sharded walk: up/down formats differ");
+    if ((up_shard->fmt & 0xff) != LQ_FMT_Q4_K) {
+        CK(launch_gather_fmt(fmtmat_of(*up_shard), fmtmat_of(*down_shard), xprep_of(w), w.hit_idx, w.hit_score,
+                             &w.sel->n_sel, N, ctx->partials, ctx->gather_grid, st));
+    } else {
+        const Q4kMat u{(const uint8_t*)up_shard->data, N, H}, d{(const uint8_t*)down_shard->data, N, H};
+        CK(launch_gather_q4k(u, d, xprep_of(w), w.hit_idx, w.hit_score, &w.sel->n_sel, N, ctx->partials,
+                             ctx->gather_grid, ctx->d_err, st));
+    }
     CK(launch_finish(ctx->partials, ctx->gather_grid, H, nullptr, out_partial, st));
     ctx->launches += 3;
+    return LQ_OK;
+}
+
+int lq_dev_shard_hits(lq_ctx* ctx, uint32_t* idx_out_host, size_t cap, size_t* count) {
+    if (!ctx || !count || ctx->tok.empty()) return LQ_ERR_ARGUMENT;
+    TokenWs w = ctx->tok[0];
+    int n = 0;
+    CK(cudaMemcpyAsync(&n, &w.sel->n_sel, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    CK(cudaStreamSynchronize(ctx->stream));
+    if (n < 0 || (size_t)n > ctx->ws_feat) return fail(ctx, LQ_ERR_CUDA, "shard_hits: bad count");
+    *count = (size_t)n;
+    const size_t m = std::min((size_t)n, cap);
+    if (m && idx_out_host) CK(cudaMemcpy(idx_out_host, w.hit_idx, m * 4, cudaMemcpyDeviceToHost));
     return LQ_OK;
 }
 

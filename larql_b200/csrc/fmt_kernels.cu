@@ -392,6 +392,13 @@ __global__ void __launch_bounds__(128) scan_exact_staged_kernel(FmtMat m, const 
     }
 }
 
+// Coarse histogram of |score| keys (the classification's input) for scores that did not come from
+// a scan kernel that builds it on the fly.
+__global__ void hist_abs_kernel(const float* __restrict__ scores, int n, uint32_t* __restrict__ hist) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) atomicAdd(&hist[__float_as_uint(fabsf(scores[i])) >> LQ_HIST_SHIFT], 1u);
+}
+
 // Gather: each CTA takes a contiguous slice of the hit list, 64 hits at a time.  First the up dots
 // of the chunk, one warp per hit (fast form), and the activations; then, hit by hit, every thread
 // adds act * down[row] for its own 32-column block(s) - one vector load of the block, the 32 values
@@ -507,6 +514,12 @@ cudaError_t launch_scan_fmt(const FmtMat& m, const XPrep& xp, float* scores, uin
 #define CALL(F) scan_fmt_kernel<F><<<grid, FK_THREADS, 0, st>>>(m, xp, scores, hist, bound_bits, c1, err)
     FMT_DISPATCH(m.fmt, CALL)
 #undef CALL
+    return cudaGetLastError();
+}
+
+cudaError_t launch_hist_abs(const float* scores, int n, uint32_t* hist, cudaStream_t st) {
+    if (n <= 0) return cudaSuccess;
+    hist_abs_kernel<<<(n + 255) / 256, 256, 0, st>>>(scores, n, hist);
     return cudaGetLastError();
 }
 

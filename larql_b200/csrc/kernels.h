@@ -86,6 +86,7 @@ struct FmtMat {
 // fmt_kernels.cu
 cudaError_t launch_scan_fmt(const FmtMat& m, const XPrep& xp, float* scores, uint32_t* hist, uint32_t* bound_bits,
                             float c1, int* err, int sm_count, cudaStream_t st);
+cudaError_t launch_hist_abs(const float* scores, int n, uint32_t* hist, cudaStream_t st);
 // Scores in the reference's exact element order (one thread per row).
 cudaError_t launch_scan_exact_fmt(const FmtMat& m, const float* xn, float* scores, int* err, cudaStream_t st);
 cudaError_t launch_rescore_fmt(const FmtMat& m, const float* xn, const uint32_t* rows_idx, const int* n_rows_dev,

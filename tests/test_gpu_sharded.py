@@ -10,18 +10,21 @@ from conftest import rel_l2, seeded_weights, seeded_x
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("world,h,n,k", [(2, 1024, 3072, 512), (4, 2560, 2048, 300), (8, 8192, 4096, 600)])
-def test_emulated_ranks_match_unsharded_oracle(world, h, n, k):
+@pytest.mark.parametrize("world,h,n,k,fmt", [(2, 1024, 3072, 512, oracle.FMT_Q4_K), (4, 2560, 2048, 300, oracle.FMT_Q4_K),
+                                             (8, 8192, 4096, 600, oracle.FMT_Q4_K), (2, 1024, 3072, 512, oracle.FMT_NVFP4),
+                                             (4, 2048, 2048, 300, oracle.FMT_MXFP4), (3, 1024, 1000, 128, oracle.FMT_Q8_0)])
+def test_emulated_ranks_match_unsharded_oracle(world, h, n, k, fmt):
     import torch
 
     import larql_b200
     from larql_b200 import sharded
 
     dev = torch.device("cuda", 0)
-    mats = [oracle.quantize_matrix(oracle.FMT_Q4_K, seeded_weights(31 * world + j, n, h)) for j in range(3)]
+    mats = [oracle.quantize_matrix(fmt, seeded_weights(31 * world + j, n, h)) for j in range(3)]
     hin = seeded_x(5 + world, h)
     want, want_idx = oracle.run_ffn_token(*mats, hin, k)
-    row = h // 256 * 144
+    row = mats[0].row_bytes()
+    srow = {oracle.FMT_MXFP4: h // 32, oracle.FMT_NVFP4: h // 16}.get(fmt, 0)   # scale bytes per row
     cap = 1024
     stride = 2 + 2 * cap
     flags = larql_b200.WALK_RMSNORM | larql_b200.WALK_FORCE_SPARSE
@@ -33,7 +36,9 @@ def test_emulated_ranks_match_unsharded_oracle(world, h, n, k):
         dm = []
         for m in mats:
             t = torch.from_numpy(m.data[lo * row:hi * row].copy()).to(dev)
-            dm.append(larql_b200.DeviceMatrix(larql_b200.FMT_Q4_K, hi - lo, h, t.data_ptr(), t.numel(), keepalive=t))
+            sc = torch.from_numpy(m.scales[lo * srow:hi * srow].copy()).to(dev) if srow else None
+            dm.append(larql_b200.DeviceMatrix(fmt, hi - lo, h, t.data_ptr(), t.numel(), sc.data_ptr() if srow else 0,
+                                              sc.numel() if srow else 0, float(m.tensor_scale), keepalive=(t, sc)))
         shards.append(dm)
     x_d = torch.from_numpy(hin).to(dev)
     hists = [torch.zeros(sharded.HIST_WORDS, dtype=torch.int32, device=dev) for _ in range(world)]
@@ -60,7 +65,13 @@ def test_emulated_ranks_match_unsharded_oracle(world, h, n, k):
         out = torch.stack(outs).sum(0).cpu().numpy() + hin           # "all-reduce" + residual
         assert rel_l2(out - hin, want - hin) < 1e-3
         n_in = packs[:, 0].sum().item()
-        assert 0 < n_in < k
+        assert 0 < n_in <= k
+        # the union of the ranks' selections is the unsharded reference's top-K set
+        got_idx = []
+        for r in range(world):
+            st = bes[r].last_shard_hits(spans[r][0])
+            got_idx += st
+        assert sorted(got_idx) == sorted(want_idx.tolist())
     finally:
         for b in bes:
             b.close()
