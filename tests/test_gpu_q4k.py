@@ -296,3 +296,20 @@ def test_stack_run_host_matches_layer_by_layer_oracle(be):
         want, _ = oracle.run_ffn_token(*ls[l], want, k)
     assert rel_l2(out[0] - hin[0], want - hin[0]) < OUT_TOL
     be.stack_destroy(st)
+
+
+@pytest.mark.parametrize("n,k", [(4096, 100), (10000, 37)])
+def test_massive_ties_resolve_to_lowest_rows(be, n, k):
+    # every gate row identical: all |scores| tie, the band is the whole layer (beyond what the final pick
+    # can rank by counting, and for n = 10000 beyond what it can stage in shared memory)
+    import larql_b200
+    h = 256
+    base = oracle.quantize_matrix(oracle.FMT_Q4_K, seeded_weights(0x71E5, 1, h))
+    gate = oracle.Matrix(oracle.FMT_Q4_K, n, h, np.tile(base.data[:144], n))
+    up = oracle.quantize_matrix(oracle.FMT_Q4_K, seeded_weights(0x71E6, n, h))
+    down = oracle.quantize_matrix(oracle.FMT_Q4_K, seeded_weights(0x71E7, n, h))
+    x = oracle.rms_norm(seeded_x(0x71E8, h))
+    out, hits = be.walk_ffn(host(gate), host(up), host(down), x, k, larql_b200.WALK_FORCE_SPARSE)
+    assert sorted(hits[0].tolist()) == list(range(k))
+    want, idx, _ = oracle.walk_token(gate, up, down, x, k)
+    assert sorted(idx.tolist()) == list(range(k)) and rel_l2(out, want) < OUT_TOL
