@@ -75,6 +75,9 @@ struct FusedArgs {
     uint32_t* ctrs;        // see CTR_* below
     uint32_t* band_row;    // [n_rows]
     float* band_exact;     // [n_rows]
+    uint32_t* pool_row;    // [grid][max_slots]: certainly-in rows a CTA hands over (beyond its fair share)
+    float* pool_score;     // [grid][max_slots]
+    uint32_t* pool_cnt;    // [grid]
     float* partials;       // [grid][H]
     uint32_t* hit_out;     // optional [top_k] selected rows of the LAST layer (unordered)
     uint32_t* count_out;   // optional: number of rows selected in the last layer
@@ -118,7 +121,7 @@ __host__ inline bool fused_geom(int hidden, int n_rows, int grid_hint, FusedGeom
     const int grid = grid_hint < n_tiles ? grid_hint : (n_tiles > 0 ? n_tiles : 1);
     g.max_slots = ((n_tiles + grid - 1) / grid) * g.R;
     g.off_scores = off;  off += fw_align(g.max_slots * 4, 128);
-    g.off_lists = off;   off += fw_align(4 * g.max_slots * 4, 128);
+    g.off_lists = off;   off += fw_align(7 * g.max_slots * 4, 128);
     g.off_ring = off;
     const int budget = 224 * 1024;
     g.ring_bytes = (budget - off) / 128 * 128;
@@ -243,14 +246,15 @@ struct Rings {
 };
 
 __device__ __forceinline__ void producer_gather(const Rings& rg, const FusedGeom& gm, const FusedLayer& ly,
-                                                const int* list, int n, uint32_t& g_it, int first_tile, int lane,
-                                                bool& failed) {
+                                                const int* list, bool rows_direct, int n, uint32_t& g_it,
+                                                int first_tile, int lane, bool& failed) {
     for (int i = 0; i < n; ++i) {
         const uint32_t gi = g_it + i;
         const int slot = gi % gm.D;
         if (gi >= (uint32_t)gm.D && !failed && !mbar_wait(&rg.gempty[slot], ((gi / gm.D) - 1) & 1)) failed = true;
-        const int m = list[i];
-        const size_t row = (size_t)(first_tile + (m / gm.R) * (int)gridDim.x) * gm.R + (m % gm.R);
+        const int m = list[i];  // a score slot of this CTA, or (rows_direct) a global row
+        const size_t row = rows_direct ? (size_t)(uint32_t)m
+                                       : (size_t)(first_tile + (m / gm.R) * (int)gridDim.x) * gm.R + (m % gm.R);
         uint8_t* dst = rg.ring + (size_t)slot * gm.slot_bytes;
         if (lane == 0) mbar_expect_tx(&rg.gfull[slot], (uint32_t)gm.slot_bytes);
         __syncwarp();
@@ -312,7 +316,7 @@ __device__ __forceinline__ void consumer_gather(const Rings& rg, const FusedGeom
         bar_sync(1 + team, gm.TS);
         float upv = 0.0f;
         for (int w = 0; w < gm.Wt; ++w) upv += wp[w];
-        const float gs = scores[list[i]];
+        const float gs = list ? scores[list[i]] : scores[i];  // list == nullptr: scores are per item
         const float sig = __fdiv_rn(1.0f, 1.0f + expf(-gs));
         float act = (gs * sig) * upv;
         if (!(fabsf(act) > FW_NOISE_FLOOR)) act = 0.0f;
@@ -367,8 +371,9 @@ __global__ void __launch_bounds__(FW_THREADS, 1) walk_fused_q4k_kernel(FusedGeom
     float* my_scores = reinterpret_cast<float*>(smem + gm.off_scores);
     int* in_list = reinterpret_cast<int*>(smem + gm.off_lists);
     int* band_list = in_list + gm.max_slots;
-    int* g2_list = band_list + gm.max_slots;
-    float* band_ex = reinterpret_cast<float*>(g2_list + gm.max_slots);
+    float* band_ex = reinterpret_cast<float*>(band_list + gm.max_slots);
+    int* g2_rows = reinterpret_cast<int*>(band_ex + gm.max_slots);         // [2 * max_slots] global rows of the second gather
+    float* g2_scores = reinterpret_cast<float*>(g2_rows + 2 * gm.max_slots);  // [2 * max_slots] their gate scores
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool is_producer = tid >= FW_CONSUMERS;
@@ -417,9 +422,11 @@ __global__ void __launch_bounds__(FW_THREADS, 1) walk_fused_q4k_kernel(FusedGeom
             // the gather ring aliases the scan ring: wait until every scan tile has been consumed
             for (uint32_t it = scan_it > (uint32_t)gm.S ? scan_it - gm.S : 0; it < scan_it; ++it)
                 if (!failed && !mbar_wait(&rg.empty[it % gm.S], (it / gm.S) & 1)) failed = true;
-            producer_gather(rg, gm, ly, in_list, s_ctl[0], g_it, first_tile, lane, failed);
+            producer_gather(rg, gm, ly, in_list, false,
+                            min(s_ctl[0], (a.top_k + (int)gridDim.x - 1) / (int)gridDim.x + 2), g_it, first_tile, lane,
+                            failed);
             bar_sync(FW_BAR_ALL, FW_THREADS);  // B: band winners ready (ring is idle: the pick staged in it)
-            producer_gather(rg, gm, ly, g2_list, s_ctl[2], g_it, first_tile, lane, failed);
+            producer_gather(rg, gm, ly, g2_rows, true, s_ctl[2], g_it, first_tile, lane, failed);
             bar_sync(FW_BAR_ALL, FW_THREADS);  // C: every gather slot consumed -> next layer's tiles may land
         }
         if (failed) set_err(a.err, DEV_ERR_TMA_TIMEOUT);
@@ -718,6 +725,21 @@ __global__ void __launch_bounds__(FW_THREADS, 1) walk_fused_q4k_kernel(FusedGeom
             }
         }
 
+        // A CTA gathers at most its fair share (+2) of certainly-in rows itself; the rest goes to a pool
+        // that all CTAs share out after the next barrier, so one heavy CTA does not hold everybody up.
+        const int n_fair = (a.top_k + (int)gridDim.x - 1) / (int)gridDim.x + 2;
+        const int n_keep = min(n_in_mine, n_fair), n_over = n_in_mine - n_keep;
+        {
+            uint32_t* pr = a.pool_row + (size_t)blockIdx.x * gm.max_slots;
+            float* ps = a.pool_score + (size_t)blockIdx.x * gm.max_slots;
+            for (int i = tid; i < n_over; i += FW_CONSUMERS) {
+                const int m = in_list[n_keep + i];
+                pr[i] = (uint32_t)((first_tile + (m / R) * (int)gridDim.x) * R + (m % R));
+                ps[i] = my_scores[m];
+            }
+            if (tid == 0) a.pool_cnt[blockIdx.x] = (uint32_t)n_over;
+        }
+
         FW_STAMP(5);
         // ---- gather the certainly-in rows ---------------------------------------------
         float acc_lo[32], acc_hi[32];
@@ -725,10 +747,10 @@ __global__ void __launch_bounds__(FW_THREADS, 1) walk_fused_q4k_kernel(FusedGeom
         for (int j = 0; j < 32; ++j) acc_lo[j] = acc_hi[j] = 0.0f;
         float corr_lo = 0.0f, corr_hi = 0.0f;
         if (in_team)
-            consumer_gather(rg, gm, in_list, n_in_mine, my_scores, g_it, xa_s, xb_s, blk_s, wpart, team, c, active,
+            consumer_gather(rg, gm, in_list, n_keep, my_scores, g_it, xa_s, xb_s, blk_s, wpart, team, c, active,
                             acc_lo, acc_hi, corr_lo, corr_hi, failed);
         else
-            g_it += n_in_mine;
+            g_it += n_keep;
         FW_STAMP(6);
         grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[6]);
         FW_STAMP(7);
@@ -801,13 +823,51 @@ __global__ void __launch_bounds__(FW_THREADS, 1) walk_fused_q4k_kernel(FusedGeom
                         const uint32_t row = (uint32_t)((first_tile + (m / R) * (int)gridDim.x) * R + (m % R));
                         win = by_rank ? (win_s[i] != 0)
                                       : (take_all || key > tau_key || (key == tau_key && row <= row_cut));
-                        if (win) my_scores[m] = band_ex[i];  // the gather uses the exact gate score
                     }
                     const uint32_t bal = __ballot_sync(0xffffffffu, win);
-                    if (win) g2_list[cnt + __popc(bal & ((1u << lane) - 1u))] = m;
+                    if (win) {
+                        const int pos = cnt + __popc(bal & ((1u << lane) - 1u));
+                        g2_rows[pos] = (first_tile + (m / R) * (int)gridDim.x) * R + (m % R);
+                        g2_scores[pos] = band_ex[i];  // the gather uses the exact gate score
+                    }
                     cnt += __popc(bal);
                 }
                 if (lane == 0) s_ctl[2] = cnt;
+            }
+            // this CTA's share of the pooled certainly-in rows: pool items j = cta, cta + grid, ... of the
+            // per-CTA segments taken in CTA order (a fixed order: results stay run-to-run identical)
+            {
+                const int NC = (int)gridDim.x;
+                int* prefix = reinterpret_cast<int*>(red) + 1280;  // [NC + 1]
+                int* wtot = reinterpret_cast<int*>(red) + 1200;    // [FW_NWARPS]
+                int inc = tid < NC ? (int)__ldcg(&a.pool_cnt[tid]) : 0;
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int v = __shfl_up_sync(0xffffffffu, inc, o);
+                    if (lane >= o) inc += v;
+                }
+                if (lane == 31) wtot[warp] = inc;
+                bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+                int lower = 0;
+                for (int w = 0; w < warp; ++w) lower += wtot[w];
+                if (tid < NC) prefix[tid + 1] = lower + inc;
+                if (tid == 0) prefix[0] = 0;
+                bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+                const int total = prefix[NC], n_win = s_ctl[2];
+                const int n_pool_mine = total > (int)blockIdx.x ? (total - (int)blockIdx.x + NC - 1) / NC : 0;
+                for (int i = tid; i < n_pool_mine; i += FW_CONSUMERS) {
+                    const int j = (int)blockIdx.x + i * NC;
+                    int sa = 0, sb = NC;  // prefix[sa] <= j < prefix[sb]
+                    while (sb - sa > 1) {
+                        const int mid = (sa + sb) >> 1;
+                        if (prefix[mid] <= j) sa = mid;
+                        else sb = mid;
+                    }
+                    const size_t src = (size_t)sa * gm.max_slots + (size_t)(j - prefix[sa]);
+                    g2_rows[n_win + i] = (int)__ldcg(&a.pool_row[src]);
+                    g2_scores[n_win + i] = __ldcg(&a.pool_score[src]);
+                }
+                bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+                if (tid == 0) s_ctl[2] = n_win + n_pool_mine;
             }
             if (l + 1 == a.n_layers && a.stats && blockIdx.x == 0 && tid == 0) {
                 a.stats->n_certain = n_in_tot;
@@ -824,7 +884,7 @@ __global__ void __launch_bounds__(FW_THREADS, 1) walk_fused_q4k_kernel(FusedGeom
         FW_STAMP(8);
         const int n_g2 = s_ctl[2];
         if (in_team)
-            consumer_gather(rg, gm, g2_list, n_g2, my_scores, g_it, xa_s, xb_s, blk_s, wpart, team, c, active, acc_lo,
+            consumer_gather(rg, gm, nullptr, n_g2, g2_scores, g_it, xa_s, xb_s, blk_s, wpart, team, c, active, acc_lo,
                             acc_hi, corr_lo, corr_hi, failed);
         else
             g_it += n_g2;
@@ -833,13 +893,18 @@ __global__ void __launch_bounds__(FW_THREADS, 1) walk_fused_q4k_kernel(FusedGeom
 
         // optional: selected rows of the last layer (unordered)
         if (l + 1 == a.n_layers && a.hit_out) {
-            if (tid == 0) s_ctl[5] = (int)atomicAdd(&a.ctrs[CTR_HITS], (uint32_t)(n_in_mine + n_g2));
+            if (tid == 0) s_ctl[5] = (int)atomicAdd(&a.ctrs[CTR_HITS], (uint32_t)(n_keep + n_g2));
             bar_sync(FW_BAR_CONS, FW_CONSUMERS);
             const int base = s_ctl[5];
-            for (int i = tid; i < n_in_mine + n_g2; i += FW_CONSUMERS) {
-                const int m = i < n_in_mine ? in_list[i] : g2_list[i - n_in_mine];
-                if (base + i < a.top_k)
-                    a.hit_out[base + i] = (uint32_t)((first_tile + (m / R) * (int)gridDim.x) * R + (m % R));
+            for (int i = tid; i < n_keep + n_g2; i += FW_CONSUMERS) {
+                uint32_t row;
+                if (i < n_keep) {
+                    const int m = in_list[i];
+                    row = (uint32_t)((first_tile + (m / R) * (int)gridDim.x) * R + (m % R));
+                } else {
+                    row = (uint32_t)g2_rows[i - n_keep];
+                }
+                if (base + i < a.top_k) a.hit_out[base + i] = row;
             }
         }
 
@@ -938,8 +1003,11 @@ bool fused_q4k_supported(int hidden, int n_rows, int top_k, int sm_count) {
 }
 
 size_t fused_q4k_ws_bytes(int hidden, int n_rows, int sm_count) {
-    return (size_t)2 * LQ_HIST_BINS * 4 + CTR_WORDS * 4 + (size_t)n_rows * 8 + (size_t)sm_count * hidden * 4 +
-           (size_t)2 * hidden * 4 + 4096;
+    FusedGeom g;
+    size_t pool = 0;
+    if (fused_geom(hidden, n_rows, sm_count, g)) pool = ((size_t)sm_count * g.max_slots * 4 + 255) / 256 * 256;
+    return (size_t)2 * LQ_HIST_BINS * 4 + CTR_WORDS * 4 + (size_t)n_rows * 8 + 2 * pool + 4096 +
+           (size_t)sm_count * hidden * 4 + (size_t)2 * hidden * 4 + 4096;
 }
 
 // ws: fused_q4k_ws_bytes() of zero-initialised device memory, 256-byte aligned.  layers_dev:
@@ -975,6 +1043,10 @@ cudaError_t launch_walk_fused_q4k(const void* layers_dev, const uint8_t* const* 
     a.ctrs = reinterpret_cast<uint32_t*>(p);        p += 256;
     a.band_row = reinterpret_cast<uint32_t*>(p);    p += ((size_t)n_rows * 4 + 255) / 256 * 256;
     a.band_exact = reinterpret_cast<float*>(p);     p += ((size_t)n_rows * 4 + 255) / 256 * 256;
+    const size_t pool = ((size_t)sm_count * g.max_slots * 4 + 255) / 256 * 256;
+    a.pool_row = reinterpret_cast<uint32_t*>(p);    p += pool;
+    a.pool_score = reinterpret_cast<float*>(p);     p += pool;
+    a.pool_cnt = reinterpret_cast<uint32_t*>(p);    p += 4096;
     a.hbuf0 = reinterpret_cast<float*>(p);          p += (size_t)hidden * 4;
     a.hbuf1 = reinterpret_cast<float*>(p);          p += (size_t)hidden * 4;
     a.partials = reinterpret_cast<float*>(p);
