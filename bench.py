@@ -406,8 +406,8 @@ def run_ours(args, wl):
     # layer, so its launch duration is the step time measured above with CUDA events on its stream.
     flags = larql_b200.WALK_RMSNORM | larql_b200.WALK_RESIDUAL | larql_b200.WALK_FORCE_SPARSE
     phase_us = be.fused_phase_us()
-    names = ["prepare", "scan", "barrier1", "classify", "rescore", "gather", "barrier2", "pick", "gather_band",
-             "merge", "barrier3", "finish"]
+    names = ["prepare", "scan", "barrier_a", "select", "rescore", "gather", "barrier_b_wait", "pick", "gather_band",
+             "merge", "barrier_c", "finish", "barrier_d"]
     phase = dict(zip(names, [float(v) for v in phase_us])) if phase_us else {}
     peak, peak_kind = measured_peaks()
     achieved = step_bytes / (ms_step * 1e-3) / 1e9

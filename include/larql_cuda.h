@@ -18,6 +18,12 @@
  *     Activations are copied per call; outputs are written to caller memory.
  *   - Device entry points (lq_dev_*) take DEVICE pointers, enqueue on the context's
  *     stream and do not synchronise; call lq_synchronize() to wait and collect errors.
+ *   - Device weight pointers are block aligned: 16 bytes for Q4_K and MXFP4 codes, 8 for NVFP4
+ *     codes, 2 for Q8_0 blocks (LQ_ERR_ARGUMENT / LQ_REFUSED_UNSUPPORTED otherwise, before any
+ *     launch).  Host weight ranges may sit at any address: a range that would land misaligned
+ *     inside a registered region is given an aligned device copy of its own.
+ *   - Every call makes its context's device current for its duration: one process may hold
+ *     contexts on several GPUs.
  *   - There is no CPU fallback anywhere: without a CUDA device lq_create fails.
  *   - A context is used by one thread at a time (the reference serialises device
  *     calls behind a mutex, crates/larql-vindex/src/format/vindex3/opplan/exec/device.rs:39-42).
@@ -126,13 +132,15 @@ LQ_API int lq_q4k_matvec_exact(lq_ctx* ctx, const uint8_t* w, size_t w_len, cons
  * q4k_matvec.  Refuses (LQ_REFUSED_SHAPE) where those return None. */
 LQ_API int lq_gemv(lq_ctx* ctx, const lq_matrix* m, const float* x, size_t x_len, float* out, size_t out_len,
                    int exact);
-/* QuantMatVec::q8_0_gemv (backend/quant_matvec.rs:378-395): blocks [n, k/32, 34]. */
+/* q8_0_gemv (crates/larql-compute/src/cpu/kquant_gemv.rs:67-109; the reference calls it directly, no
+ * trait method carries ggml Q8_0 with f32 activations): blocks [n, k/32, 34]. */
 LQ_API int lq_q8_0_gemv(lq_ctx* ctx, const uint8_t* blocks, size_t blocks_len, const float* x, size_t x_len, size_t n,
                         size_t k, float* out);
 /* MatMul::mxfp4_gemv (backend/matmul.rs:226-235): packed [n, k/2], e8m0 scales [n, k/32]. */
 LQ_API int lq_mxfp4_gemv(lq_ctx* ctx, const uint8_t* packed, size_t packed_len, const uint8_t* scales,
                          size_t scales_len, const float* x, size_t x_len, size_t n, size_t k, float* out);
-/* QuantMatVec::nvfp4_gemv (backend/quant_matvec.rs:397-427): packed [n, k/2], e4m3 scales [n, k/16]. */
+/* MatMul::nvfp4_gemv (backend/matmul.rs:263-273) -> cpu/nvfp4_gemv.rs:29-65: packed [n, k/2], e4m3 scales
+ * [n, k/16], one f32 tensor scale. */
 LQ_API int lq_nvfp4_gemv(lq_ctx* ctx, const uint8_t* packed, size_t packed_len, const uint8_t* scales,
                          size_t scales_len, float tensor_scale, const float* x, size_t x_len, size_t n, size_t k,
                          float* out);
@@ -210,8 +218,9 @@ typedef struct lq_walk_stats {
 } lq_walk_stats;
 LQ_API int lq_last_walk_stats(lq_ctx* ctx, lq_walk_stats* out);
 
-/* Phase times (microseconds, CTA 0, last layer) of the last fused persistent walk: prepare, scan,
- * barrier, classify, re-score, gather, barrier, pick, gather of band winners, merge, barrier, finish.
+/* Phase times (microseconds, CTA 0, last layer but one when the launch covers several) of the last
+ * fused persistent walk, 13 values: prepare, scan, barrier A, threshold + classify, re-score,
+ * gather, wait for barrier B, pick, gather of band winners, merge, barrier C, finish, barrier D.
  * The reference's counterpart is PhaseTimingsHandle (crates/larql-inference/src/vindex/walk_ffn/timings.rs:12-33). */
 LQ_API int lq_fused_phase_us(lq_ctx* ctx, float* us, size_t n);
 

@@ -374,8 +374,8 @@ class CudaBackend:
         return out.reshape(x.shape), hits
 
     def fused_phase_us(self):
-        us = (C.c_float * 12)()
-        ok = self._status(self._lib.lq_fused_phase_us(self._h, us, 12))
+        us = (C.c_float * 13)()
+        ok = self._status(self._lib.lq_fused_phase_us(self._h, us, 13))
         return list(us) if ok else None
 
     def last_walk_stats(self) -> WalkStats:

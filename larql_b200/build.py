@@ -34,6 +34,8 @@ def _newer(a: Path, deps) -> bool:
 
 
 def build(force: bool = False, ptxas_verbose: bool = False) -> Path:
+    extra = os.environ.get("LARQL_B200_NVCC_FLAGS", "").split()  # e.g. -DFW_CFG_THREADS=512 for tuning builds
+    force = force or bool(extra)
     srcs = sorted(CSRC.glob("*.cu"))
     hdrs = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + sorted((HERE.parent / "include").glob("*.h"))
     OBJ.mkdir(exist_ok=True)
@@ -41,7 +43,7 @@ def build(force: bool = False, ptxas_verbose: bool = False) -> Path:
     for s in srcs:
         o = OBJ / (s.stem + ".o")
         if force or ptxas_verbose or not _newer(o, [s] + hdrs):
-            cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if ptxas_verbose else []) + ["-c", str(s), "-o", str(o)]
+            cmd = [NVCC] + FLAGS + extra + (["-Xptxas", "-v"] if ptxas_verbose else []) + ["-c", str(s), "-o", str(o)]
             jobs.append((s, cmd))
 
     def run(job):

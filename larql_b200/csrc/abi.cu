@@ -85,6 +85,22 @@ struct lq_ctx {
 
 namespace {
 
+// Every entry point runs with its context's device current (a host may hold contexts on several
+// GPUs in one process and call them from any thread) and puts the caller's device back afterwards.
+struct DevGuard {
+    int prev = -1;
+    explicit DevGuard(const lq_ctx* c) {
+        if (!c) return;
+        int cur = -1;
+        if (cudaGetDevice(&cur) == cudaSuccess && cur != c->device && cudaSetDevice(c->device) == cudaSuccess) prev = cur;
+    }
+    ~DevGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+    DevGuard(const DevGuard&) = delete;
+    DevGuard& operator=(const DevGuard&) = delete;
+};
+
 int fail(lq_ctx* c, int code, const std::string& msg) {
     if (c) c->last_error = msg;
     return code;
@@ -213,9 +229,10 @@ int ensure_fused(lq_ctx* ctx, size_t hidden, size_t feat) {
     CK(cudaMalloc(&ctx->fws, need));
     CK(cudaMemsetAsync(ctx->fws, 0, need, ctx->stream));
     ctx->fws_cap = need;
+
     if (!ctx->stats_dev) {
-        CK(cudaMalloc(&ctx->stats_dev, 256));
-        CK(cudaMemsetAsync(ctx->stats_dev, 0, 256, ctx->stream));
+        CK(cudaMalloc(&ctx->stats_dev, 8192));  // lq_walk_stats, (at +64) clock stamps, (at +1024) per-CTA durations
+        CK(cudaMemsetAsync(ctx->stats_dev, 0, 8192, ctx->stream));
     }
     return LQ_OK;
 }
@@ -256,12 +273,20 @@ int resolve(lq_ctx* ctx, const void* host, size_t len, const uint8_t** dev) {
     *dev = nullptr;
     if (len == 0) return LQ_OK;
     const uint8_t* h = (const uint8_t*)host;
+    // A range at an offset inside a registered region that is not a multiple of 16 bytes would hand the
+    // kernels a misaligned device pointer (they use 16-byte vector loads and bulk copies): such a
+    // range gets a private, aligned copy, cached by (address, length) like any other range.
+    bool inside_unaligned = false;
     for (auto& r : ctx->regions)
         if (h >= r.host && h + len <= r.host + r.len) {
-            *dev = r.dev + (h - r.host);
-            return LQ_OK;
+            const uint8_t* cand = r.dev + (h - r.host);
+            if (((uintptr_t)cand & 15) == 0) {
+                *dev = cand;
+                return LQ_OK;
+            }
+            inside_unaligned = true;
         }
-    if (ctx->sealed) return fail(ctx, LQ_ERR_ARGUMENT, "weight range outside the sealed regions");
+    if (ctx->sealed && !inside_unaligned) return fail(ctx, LQ_ERR_ARGUMENT, "weight range outside the sealed regions");
     uint8_t* d = nullptr;
     CK(cudaMalloc(&d, a256(len) + 256));  // slack: bulk copies may round a ragged tail up to 16 B
     cudaError_t e = cudaMemcpyAsync(d, host, len, cudaMemcpyHostToDevice, ctx->stream);
@@ -424,6 +449,10 @@ int dev_walk(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const lq_m
     if (batch == 0 || H == 0) return LQ_OK;
     if (H > 16384) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "walk: hidden > 16384");
     if (H % 32 != 0) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "walk: hidden not a multiple of 32");
+    // every Q4_K kernel moves rows with 16-byte vector loads and bulk copies
+    for (const lq_matrix* m : {gate, up, down})
+        if ((m->fmt & 0xff) == LQ_FMT_Q4_K && N > 0 && ((uintptr_t)m->data & 15) != 0)
+            return fail(ctx, LQ_ERR_ARGUMENT, "walk: Q4_K weights not 16-byte aligned");
     int rc = ensure_ws(ctx, batch, H, N);
     if (rc) return rc;
     const size_t k = effective_k(top_k, N, flags);
@@ -532,6 +561,7 @@ int lq_create(int device, lq_ctx** out) {
 }
 
 void lq_destroy(lq_ctx* ctx) {
+    DevGuard dev_guard(ctx);
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
@@ -549,17 +579,20 @@ void lq_destroy(lq_ctx* ctx) {
 const char* lq_last_error(lq_ctx* ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
 
 int lq_device_info(lq_ctx* ctx, char* buf, size_t cap) {
+    DevGuard dev_guard(ctx);
     if (!ctx || !buf || cap == 0) return LQ_ERR_ARGUMENT;
     snprintf(buf, cap, "%s", ctx->info.c_str());
     return LQ_OK;
 }
 
 int lq_supports_quant(lq_ctx* ctx, int fmt) {
+    DevGuard dev_guard(ctx);
     (void)ctx;
     return (fmt == LQ_FMT_Q4_K || fmt == LQ_FMT_Q8_0 || fmt == LQ_FMT_MXFP4 || fmt == LQ_FMT_NVFP4) ? 1 : 0;
 }
 
 int lq_synchronize(lq_ctx* ctx) {
+    DevGuard dev_guard(ctx);
     if (!ctx) return LQ_ERR_ARGUMENT;
     CK(cudaStreamSynchronize(ctx->stream));
     return check_device_err(ctx);
@@ -569,17 +602,20 @@ void* lq_stream(lq_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
 uint64_t lq_launch_count(lq_ctx* ctx) { return ctx ? ctx->launches : 0; }
 
 int lq_register_weight_region(lq_ctx* ctx, const void* host, size_t len) {
+    DevGuard dev_guard(ctx);
     if (!ctx || (!host && len)) return LQ_ERR_ARGUMENT;
     if (ctx->sealed) return fail(ctx, LQ_ERR_ARGUMENT, "regions are sealed");
     const uint8_t* d;
     return resolve(ctx, host, len, &d);
 }
 int lq_seal_weight_regions(lq_ctx* ctx) {
+    DevGuard dev_guard(ctx);
     if (!ctx) return LQ_ERR_ARGUMENT;
     ctx->sealed = true;
     return LQ_OK;
 }
 int lq_drop_weight_regions(lq_ctx* ctx) {
+    DevGuard dev_guard(ctx);
     if (!ctx) return LQ_ERR_ARGUMENT;
     CK(cudaStreamSynchronize(ctx->stream));
     for (auto& r : ctx->regions) cudaFree(r.dev);
@@ -588,6 +624,7 @@ int lq_drop_weight_regions(lq_ctx* ctx) {
     return LQ_OK;
 }
 const void* lq_device_ptr(lq_ctx* ctx, const void* host, size_t len) {
+    DevGuard dev_guard(ctx);
     if (!ctx) return nullptr;
     const uint8_t* h = (const uint8_t*)host;
     for (auto& r : ctx->regions)
@@ -598,6 +635,7 @@ const void* lq_device_ptr(lq_ctx* ctx, const void* host, size_t len) {
 // ------------------------------------------------------------ matvec / matmul ----
 int lq_dev_q4k_matvec(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t num_rows, size_t hidden,
                       float* out) {
+    DevGuard dev_guard(ctx);
     if (!ctx) return LQ_ERR_ARGUMENT;
     if (hidden % 256 != 0 || w_len < num_rows * (hidden / 256) * 144)
         return fail(ctx, LQ_REFUSED_SHAPE, "q4k_matvec: geometry");
@@ -678,19 +716,23 @@ static int q4k_host_common(lq_ctx* ctx, const uint8_t* w, size_t w_len, const fl
 
 int lq_q4k_matvec(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t num_rows,
                   size_t hidden, float* out, size_t out_len) {
+    DevGuard dev_guard(ctx);
     return q4k_host_common(ctx, w, w_len, x, x_len, num_rows, hidden, 1, out, out_len, 0);
 }
 int lq_q4k_matvec_exact(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t num_rows,
                         size_t hidden, float* out, size_t out_len) {
+    DevGuard dev_guard(ctx);
     return q4k_host_common(ctx, w, w_len, x, x_len, num_rows, hidden, 1, out, out_len, 1);
 }
 int lq_q4k_matmul(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t num_rows,
                   size_t hidden, size_t seq_len, float* out, size_t out_len) {
+    DevGuard dev_guard(ctx);
     return q4k_host_common(ctx, w, w_len, x, x_len, num_rows, hidden, seq_len, out, out_len, 0);
 }
 
 // Dense gemv of one block-format matrix (host pointers): fast path, or the reference's exact order.
 int lq_gemv(lq_ctx* ctx, const lq_matrix* m, const float* x, size_t x_len, float* out, size_t out_len, int exact) {
+    DevGuard dev_guard(ctx);
     if (!ctx) return LQ_ERR_ARGUMENT;
     int rc = check_matrix(ctx, m, "gemv");
     if (rc) return rc;
@@ -729,22 +771,26 @@ int lq_gemv(lq_ctx* ctx, const lq_matrix* m, const float* x, size_t x_len, float
 
 int lq_q8_0_gemv(lq_ctx* ctx, const uint8_t* blocks, size_t blocks_len, const float* x, size_t x_len, size_t n,
                  size_t k, float* out) {
+    DevGuard dev_guard(ctx);
     const lq_matrix m{LQ_FMT_Q8_0, blocks, blocks_len, nullptr, 0, 1.0f, (int64_t)n, (int64_t)k};
     return lq_gemv(ctx, &m, x, x_len, out, n, 0);
 }
 int lq_mxfp4_gemv(lq_ctx* ctx, const uint8_t* packed, size_t packed_len, const uint8_t* scales, size_t scales_len,
                   const float* x, size_t x_len, size_t n, size_t k, float* out) {
+    DevGuard dev_guard(ctx);
     const lq_matrix m{LQ_FMT_MXFP4, packed, packed_len, scales, scales_len, 1.0f, (int64_t)n, (int64_t)k};
     return lq_gemv(ctx, &m, x, x_len, out, n, 0);
 }
 int lq_nvfp4_gemv(lq_ctx* ctx, const uint8_t* packed, size_t packed_len, const uint8_t* scales, size_t scales_len,
                   float tensor_scale, const float* x, size_t x_len, size_t n, size_t k, float* out) {
+    DevGuard dev_guard(ctx);
     const lq_matrix m{LQ_FMT_NVFP4, packed, packed_len, scales, scales_len, tensor_scale, (int64_t)n, (int64_t)k};
     return lq_gemv(ctx, &m, x, x_len, out, n, 0);
 }
 
 int lq_moe_route(lq_ctx* ctx, const float* logits, size_t n_tokens, size_t n_experts, size_t top_k, int renormalise,
                  uint32_t* idx_out, float* w_out) {
+    DevGuard dev_guard(ctx);
     if (!ctx || !logits || !idx_out || !w_out) return LQ_ERR_ARGUMENT;
     if (n_experts == 0 || n_experts > 256) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "moe_route: 1..256 experts");
     if (n_tokens == 0 || top_k == 0) return LQ_OK;
@@ -764,6 +810,7 @@ int lq_moe_route(lq_ctx* ctx, const float* logits, size_t n_tokens, size_t n_exp
 
 int lq_topk_abs(lq_ctx* ctx, const float* scores, size_t n, size_t top_k, uint32_t* idx_out, float* val_out,
                 size_t* count) {
+    DevGuard dev_guard(ctx);
     if (!ctx || !count) return LQ_ERR_ARGUMENT;
     *count = 0;
     if (n == 0 || top_k == 0) return LQ_OK;
@@ -791,6 +838,7 @@ int lq_topk_abs(lq_ctx* ctx, const float* scores, size_t n, size_t top_k, uint32
 }
 
 int lq_rms_norm(lq_ctx* ctx, const float* x, size_t rows, size_t cols, double eps, float* out) {
+    DevGuard dev_guard(ctx);
     if (!ctx) return LQ_ERR_ARGUMENT;
     if (rows == 0 || cols == 0) return LQ_OK;
     if (cols % 32 != 0 || cols > 16384) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "rms_norm: cols % 32 != 0");
@@ -811,6 +859,7 @@ int lq_rms_norm(lq_ctx* ctx, const float* x, size_t rows, size_t cols, double ep
 }
 
 int lq_dequantize(lq_ctx* ctx, const lq_matrix* m, float* out, size_t out_len) {
+    DevGuard dev_guard(ctx);
     if (!ctx) return LQ_ERR_ARGUMENT;
     int rc = check_matrix(ctx, m, "dequantize");
     if (rc) return rc;
@@ -832,6 +881,7 @@ int lq_dequantize(lq_ctx* ctx, const lq_matrix* m, float* out, size_t out_len) {
 int lq_dev_walk_ffn(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const lq_matrix* down_fm,
                     const float* x, size_t batch, size_t top_k, uint32_t flags, float* out, uint32_t* idx_out,
                     uint32_t* count_out) {
+    DevGuard dev_guard(ctx);
     if (!ctx) return LQ_ERR_ARGUMENT;
     int rc;
     if ((rc = check_matrix(ctx, gate, "gate")) || (rc = check_matrix(ctx, up, "up")) ||
@@ -846,6 +896,7 @@ int lq_dev_walk_ffn(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, con
 
 int lq_walk_ffn(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const lq_matrix* down_fm, const float* x,
                 size_t batch, size_t top_k, uint32_t flags, float* out, uint32_t* idx_out, uint32_t* count_out) {
+    DevGuard dev_guard(ctx);
     if (!ctx) return LQ_ERR_ARGUMENT;
     int rc;
     if ((rc = check_matrix(ctx, gate, "gate")) || (rc = check_matrix(ctx, up, "up")) ||
@@ -893,6 +944,7 @@ int lq_walk_ffn(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const l
 int lq_moe_walk_ffn(lq_ctx* ctx, const lq_matrix* gates, const lq_matrix* ups, const lq_matrix* downs_fm,
                     size_t n_experts, const float* logits, const float* x, size_t batch, size_t top_e, int renormalise,
                     size_t top_k, uint32_t flags, float* out, uint32_t* expert_idx_out, float* expert_w_out) {
+    DevGuard dev_guard(ctx);
     if (!ctx || !gates || !ups || !downs_fm || !logits || !x || !out) return LQ_ERR_ARGUMENT;
     if (n_experts == 0 || n_experts > 256) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "moe_walk: 1..256 experts");
     if (flags & (LQ_WALK_RMSNORM | LQ_WALK_RESIDUAL))
@@ -948,25 +1000,56 @@ int lq_moe_walk_ffn(lq_ctx* ctx, const lq_matrix* gates, const lq_matrix* ups, c
 }
 
 int lq_fused_phase_us(lq_ctx* ctx, float* us, size_t n) {
+    DevGuard dev_guard(ctx);
     if (!ctx || !us) return LQ_ERR_ARGUMENT;
     if (!ctx->stats_dev) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "no fused walk has run");
     CK(cudaStreamSynchronize(ctx->stream));
     int khz = 0;
     CK(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx->device));
     const double clk_mhz = khz > 0 ? khz * 1e-3 : 1965.0;  // stamps are SM cycles
-    unsigned long long t[16];
+    unsigned long long t[25];
     CK(cudaMemcpy(t, (uint8_t*)ctx->stats_dev + 64, sizeof t, cudaMemcpyDeviceToHost));
-    for (size_t i = 0; i < n && i < 12; ++i) us[i] = (float)((double)(t[i + 1] - t[i]) / clk_mhz);
+    const size_t n_phase = (size_t)fused_q4k_stamp_count() - 1;
+    for (size_t i = 0; i < n; ++i) us[i] = i < n_phase ? (float)((double)(t[i + 1] - t[i]) / clk_mhz) : 0.0f;
+    if (getenv("LARQL_B200_FUSED_DEBUG")) {
+        fprintf(stderr, "gather: rows %llu issue %.2f updots %.2f wait %.2f axpy %.2f | prepare: load %.2f rms %.2f quant %.2f us\n",
+                t[18], (double)(t[14] - t[13]) / clk_mhz, (double)(t[15] - t[14]) / clk_mhz,
+                (double)(t[16] - t[15]) / clk_mhz, (double)(t[17] - t[16]) / clk_mhz, (double)(t[19] - t[0]) / clk_mhz,
+                (double)(t[20] - t[19]) / clk_mhz, (double)(t[1] - t[20]) / clk_mhz);
+        if (ctx->fws) {
+            // per-CTA durations of the stamped layer (see the kernel): pick, gather + merge, rows gathered, band rows
+            std::vector<uint32_t> d(148 * 8);
+            if (cudaMemcpy(d.data(), (uint8_t*)ctx->stats_dev + 1024, d.size() * 4, cudaMemcpyDeviceToHost) == cudaSuccess) {
+                const char* nm[6] = {"pick", "gather+merge", "rows", "band rows", "scan", "select"};
+                for (int f = 0; f < 6; ++f) {
+                    double mn = 1e30, mx = 0, av = 0;
+                    int arg = 0;
+                    for (int c = 0; c < ctx->sm_count && c < 148; ++c) {
+                        double v = d[c * 8 + f];
+                        if (f != 2 && f != 3) v /= clk_mhz;
+                        if (v > mx) { mx = v; arg = c; }
+                        mn = std::min(mn, v);
+                        av += v;
+                    }
+                    fprintf(stderr, "  per CTA %-13s min %.2f avg %.2f max %.2f (cta %d)\n", nm[f], mn, av / ctx->sm_count, mx, arg);
+                }
+            }
+        }
+        fprintf(stderr, "scan (thread 0): rows %.2f data wait %.2f team barrier %.2f release %.2f us\n",
+                (double)t[21] / clk_mhz, (double)t[22] / clk_mhz, (double)t[23] / clk_mhz, (double)t[24] / clk_mhz);
+    }
     return LQ_OK;
 }
 
 int lq_last_walk_stats(lq_ctx* ctx, lq_walk_stats* out) {
+    DevGuard dev_guard(ctx);
     if (!ctx || !out) return LQ_ERR_ARGUMENT;
     *out = ctx->stats;
     return LQ_OK;
 }
 
 int lq_dev_quantize_q4k(lq_ctx* ctx, const float* src, size_t n_elems, uint8_t* dst) {
+    DevGuard dev_guard(ctx);
     if (!ctx) return LQ_ERR_ARGUMENT;
     if (n_elems % 256 != 0) return fail(ctx, LQ_REFUSED_SHAPE, "quantize_q4k: length % 256 != 0");
     if (((uintptr_t)dst & 15) != 0) return fail(ctx, LQ_ERR_ARGUMENT, "quantize_q4k: dst not 16-byte aligned");
@@ -977,6 +1060,7 @@ int lq_dev_quantize_q4k(lq_ctx* ctx, const float* src, size_t n_elems, uint8_t* 
 
 int lq_profile_walk(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const lq_matrix* down_fm,
                     const float* x, size_t top_k, uint32_t flags, float* out, float* ms) {
+    DevGuard dev_guard(ctx);
     if (!ctx || !ms) return LQ_ERR_ARGUMENT;
     int rc;
     if ((rc = check_matrix(ctx, gate, "gate")) || (rc = check_matrix(ctx, up, "up")) ||
@@ -1038,6 +1122,7 @@ static int shard_check(lq_ctx* ctx, const lq_matrix* m, const char* name) {
 
 int lq_dev_shard_scan(lq_ctx* ctx, const lq_matrix* gate_shard, const float* x, uint32_t flags, int rank, int world,
                       uint32_t* hist_buf) {
+    DevGuard dev_guard(ctx);
     if (!ctx || !hist_buf || rank < 0 || world < 1 || rank >= world || world > 16) return LQ_ERR_ARGUMENT;
     int rc = shard_check(ctx, gate_shard, "gate shard");
     if (rc) return rc;
@@ -1067,6 +1152,7 @@ int lq_dev_shard_scan(lq_ctx* ctx, const lq_matrix* gate_shard, const float* x, 
 
 int lq_dev_shard_classify(lq_ctx* ctx, const lq_matrix* gate_shard, uint32_t* hist_buf, int world, size_t top_k,
                           size_t row_offset, int32_t* pack, size_t cap) {
+    DevGuard dev_guard(ctx);
     if (!ctx || !hist_buf || !pack || world < 1 || world > 16 || cap == 0) return LQ_ERR_ARGUMENT;
     int rc = shard_check(ctx, gate_shard, "gate shard");
     if (rc) return rc;
@@ -1093,6 +1179,7 @@ int lq_dev_shard_classify(lq_ctx* ctx, const lq_matrix* gate_shard, uint32_t* hi
 
 int lq_dev_shard_gather(lq_ctx* ctx, const lq_matrix* up_shard, const lq_matrix* down_shard, const int32_t* packs,
                         int world, int rank, size_t cap, size_t top_k, size_t row_offset, float* out_partial) {
+    DevGuard dev_guard(ctx);
     if (!ctx || !packs || !out_partial || world < 1 || world > 16 || rank < 0 || rank >= world) return LQ_ERR_ARGUMENT;
     int rc;
     if ((rc = shard_check(ctx, up_shard, "up shard")) || (rc = shard_check(ctx, down_shard, "down shard"))) return rc;
@@ -1119,6 +1206,7 @@ int lq_dev_shard_gather(lq_ctx* ctx, const lq_matrix* up_shard, const lq_matrix*
 }
 
 int lq_dev_shard_hits(lq_ctx* ctx, uint32_t* idx_out_host, size_t cap, size_t* count) {
+    DevGuard dev_guard(ctx);
     if (!ctx || !count || ctx->tok.empty()) return LQ_ERR_ARGUMENT;
     TokenWs w = ctx->tok[0];
     int n = 0;
@@ -1159,6 +1247,7 @@ static int stack_enqueue(lq_ctx* ctx, lq_stack* s) {
 
 int lq_stack_create(lq_ctx* ctx, const lq_matrix* gates, const lq_matrix* ups, const lq_matrix* downs_fm,
                     size_t n_layers, size_t batch, size_t top_k, uint32_t flags, lq_stack** out) {
+    DevGuard dev_guard(ctx);
     if (!ctx || !out || !n_layers || !batch) return LQ_ERR_ARGUMENT;
     *out = nullptr;
     int rc;
@@ -1252,6 +1341,7 @@ int lq_stack_create(lq_ctx* ctx, const lq_matrix* gates, const lq_matrix* ups, c
 }
 
 int lq_stack_run(lq_ctx* ctx, lq_stack* s, const float* h_in, float* h_out) {
+    DevGuard dev_guard(ctx);
     if (!ctx || !s || (!s->exec && !s->fused)) return LQ_ERR_ARGUMENT;
     const size_t bytes = s->batch * s->hidden * 4;
     CK(cudaMemcpyAsync(s->h_in, h_in, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
@@ -1265,6 +1355,7 @@ int lq_stack_run(lq_ctx* ctx, lq_stack* s, const float* h_in, float* h_out) {
 }
 
 int lq_stack_run_host(lq_ctx* ctx, lq_stack* s, const float* h_in_host, float* h_out_host) {
+    DevGuard dev_guard(ctx);
     if (!ctx || !s || (!s->exec && !s->fused) || !h_in_host || !h_out_host) return LQ_ERR_ARGUMENT;
     const size_t bytes = s->batch * s->hidden * 4;
     CK(cudaMemcpyAsync(s->h_in, h_in_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
@@ -1278,6 +1369,7 @@ int lq_stack_run_host(lq_ctx* ctx, lq_stack* s, const float* h_in_host, float* h
 }
 
 void lq_stack_destroy(lq_ctx* ctx, lq_stack* s) {
+    DevGuard dev_guard(ctx);
     if (!s) return;
     if (ctx) cudaStreamSynchronize(ctx->stream);
     if (s->exec) cudaGraphExecDestroy(s->exec);

@@ -53,12 +53,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The same with a suspend-time hint: the hardware may park the thread for up to `ns` nanoseconds
+// (it is woken when the phase completes), so a waiting warp does not spend issue slots and
+// shared-memory bandwidth on polling while its neighbours work.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after ~2^31 clocks (about a second) and reports it.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t it = 0; it < (1u << 26); ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
         if (clock64() - t0 > (1ll << 31)) break;
     }
     return false;

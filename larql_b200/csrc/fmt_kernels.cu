@@ -531,13 +531,8 @@ cudaError_t launch_scan_exact_fmt(const FmtMat& m, const float* xn, float* score
 #define SCALL(F)                                                                                                   \
     {                                                                                                              \
         const size_t sm = (size_t)m.cols * 4 + 8 * (size_t)StagedGeom<F>::WARP_BYTES;                              \
-        static bool attr = false;                                                                                  \
-        if (!attr) {                                                                                               \
-            cudaError_t e = cudaFuncSetAttribute(scan_exact_staged_kernel<F>,                                      \
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);         \
-            if (e != cudaSuccess) return e;                                                                        \
-            attr = true;                                                                                           \
-        }                                                                                                          \
+        cudaError_t e = set_max_dyn_smem((const void*)scan_exact_staged_kernel<F>, 128 * 1024);                    \
+        if (e != cudaSuccess) return e;                                                                            \
         scan_exact_staged_kernel<F><<<sgrid, 128, sm, st>>>(m, xn, scores, err);                                   \
     }
         FMT_DISPATCH(m.fmt, SCALL)
@@ -548,13 +543,8 @@ cudaError_t launch_scan_exact_fmt(const FmtMat& m, const float* xn, float* score
     const size_t smem = (size_t)m.cols * sizeof(float);
 #define CALL(F)                                                                                                     \
     {                                                                                                               \
-        static bool attr = false;                                                                                   \
-        if (!attr) {                                                                                                \
-            cudaError_t e = cudaFuncSetAttribute(scan_exact_fmt_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                                 64 * 1024);                                                        \
-            if (e != cudaSuccess) return e;                                                                         \
-            attr = true;                                                                                            \
-        }                                                                                                           \
+        cudaError_t e = set_max_dyn_smem((const void*)scan_exact_fmt_kernel<F>, 64 * 1024);                         \
+        if (e != cudaSuccess) return e;                                                                             \
         scan_exact_fmt_kernel<F><<<grid, 64, smem, st>>>(m, xn, scores, err);                                        \
     }
     FMT_DISPATCH(m.fmt, CALL)

@@ -276,13 +276,8 @@ cudaError_t launch_gather_q4k(const Q4kMat& up, const Q4kMat& down, const XPrep&
                               int grid, int* err, cudaStream_t st, int batch, TokStride ts) {
     GatherGeom g;
     if (up.cols != down.cols || !gather_geom(up.cols, g)) return cudaErrorInvalidValue;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gather_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             220 * 1024);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    cudaError_t e = set_max_dyn_smem((const void*)gather_q4k_kernel, 220 * 1024);
+    if (e != cudaSuccess) return e;
     gather_q4k_kernel<<<dim3(grid, batch), GATHER_THREADS, g.smem_bytes, st>>>(up.w, down.w, g, xp, hit_idx, hit_score,
                                                                               n_hits_dev, n_hits_host, partials, err, ts);
     return cudaGetLastError();

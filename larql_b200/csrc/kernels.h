@@ -83,6 +83,9 @@ struct FmtMat {
     int rows, cols;
 };
 
+// launch_util.cu: cudaFuncAttributeMaxDynamicSharedMemorySize, set once per (device, kernel)
+cudaError_t set_max_dyn_smem(const void* func, int bytes);
+
 // fmt_kernels.cu
 cudaError_t launch_scan_fmt(const FmtMat& m, const XPrep& xp, float* scores, uint32_t* hist, uint32_t* bound_bits,
                             float c1, int* err, int sm_count, cudaStream_t st);
@@ -142,4 +145,5 @@ cudaError_t launch_finish(const float* partials, int n_partials, int hidden, con
 // walk_fused_q4k.cu — the fused persistent walk (one token, all layers, one cooperative launch)
 bool fused_q4k_supported(int hidden, int n_rows, int top_k, int sm_count);
 size_t fused_q4k_ws_bytes(int hidden, int n_rows, int sm_count);
+int fused_q4k_stamp_count();
 }  // namespace lq

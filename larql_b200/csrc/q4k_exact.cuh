@@ -11,14 +11,26 @@ namespace lq {
 __device__ __forceinline__ float exact_row_q4k(const uint8_t* __restrict__ row, const float* __restrict__ xs, int nsb,
                                                float* sb_part /* [nsb] per-warp scratch */, int lane) {
     const int g = lane & 3;
+    // The loads of the next eight super-blocks are issued before the current eight are summed, so the
+    // passes of a row overlap their memory latency (the arithmetic and its order are unchanged).
+    uint4 n_hdr = make_uint4(0u, 0u, 0u, 0u), n_q0 = n_hdr, n_q1 = n_hdr;
+    if ((lane >> 2) < nsb) {
+        const uint8_t* cell = row + (size_t)(lane >> 2) * 144;
+        n_hdr = __ldg(reinterpret_cast<const uint4*>(cell));
+        n_q0 = __ldg(reinterpret_cast<const uint4*>(cell + 16 + g * 32));
+        n_q1 = __ldg(reinterpret_cast<const uint4*>(cell + 32 + g * 32));
+    }
     for (int s0 = 0; s0 < nsb; s0 += 8) {
         const int s = s0 + (lane >> 2);
+        const uint4 hdr = n_hdr, q0 = n_q0, q1 = n_q1;
+        if (s + 8 < nsb) {
+            const uint8_t* cell = row + (size_t)(s + 8) * 144;
+            n_hdr = __ldg(reinterpret_cast<const uint4*>(cell));
+            n_q0 = __ldg(reinterpret_cast<const uint4*>(cell + 16 + g * 32));
+            n_q1 = __ldg(reinterpret_cast<const uint4*>(cell + 32 + g * 32));
+        }
         float u_lo = 0.0f, u_hi = 0.0f;
         if (s < nsb) {
-            const uint8_t* cell = row + (size_t)s * 144;
-            const uint4 hdr = *reinterpret_cast<const uint4*>(cell);
-            const uint4 q0 = *reinterpret_cast<const uint4*>(cell + 16 + g * 32);
-            const uint4 q1 = *reinterpret_cast<const uint4*>(cell + 32 + g * 32);
             const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
             const float* x_lo = xs + (s * 4 + g) * 68;
             const float* x_hi = x_lo + 32;

@@ -257,13 +257,8 @@ cudaError_t launch_scan_q4k(const Q4kMat& m, const XPrep& xp, float* scores, uin
     ScanGeom g;
     if (!scan_geom(m.cols, g)) return cudaErrorInvalidValue;
     if (m.rows == 0) return cudaSuccess;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(scan_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             SCAN_SMEM_BUDGET + 4096);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    cudaError_t e = set_max_dyn_smem((const void*)scan_q4k_kernel, SCAN_SMEM_BUDGET + 4096);
+    if (e != cudaSuccess) return e;
     const int n_tiles = (m.rows + g.R - 1) / g.R;
     const int grid = n_tiles < sm_count ? n_tiles : sm_count;
     scan_q4k_kernel<<<grid, SCAN_THREADS, g.smem_bytes, st>>>(m.w, m.rows, g, xp, scores, hist, bound_bits, c1, err);
@@ -284,12 +279,8 @@ cudaError_t launch_rescore_q4k(const Q4kMat& m, const float* xn, const uint32_t*
         if (grid < 1) grid = 1;
     }
     const size_t smem = ((size_t)(RESCORE_THREADS / 32) * nsb + (size_t)4 * nsb * 68) * sizeof(float);
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(rescore_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    cudaError_t e = set_max_dyn_smem((const void*)rescore_q4k_kernel, 96 * 1024);
+    if (e != cudaSuccess) return e;
     rescore_q4k_kernel<<<dim3(grid, batch), RESCORE_THREADS, smem, st>>>(m.w, m.rows, nsb, xn, rows_idx, n_rows_dev,
                                                                         n_rows_host, out, ws, top_k, run_final, err,
                                                                         ws_stride);

@@ -238,14 +238,12 @@ cudaError_t launch_scan_q4k_mma(const Q4kMat& m, TokenWs ws0, size_t ws_stride, 
     const int grid = (m.rows + MS_ROWS - 1) / MS_ROWS;
     const int ntg = batch <= 16 ? 1 : (batch <= 32 ? 2 : 4);
     const size_t smem = (size_t)2 * (MS_W_BYTES + (size_t)ntg * 16 * MS_TOK_BYTES);
-    static bool attr_set = false;
-    if (!attr_set) {
+    {
         cudaError_t e;
-        if ((e = cudaFuncSetAttribute(scan_q4k_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)) ||
-            (e = cudaFuncSetAttribute(scan_q4k_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)) ||
-            (e = cudaFuncSetAttribute(scan_q4k_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)))
+        if ((e = set_max_dyn_smem((const void*)scan_q4k_mma_kernel<1>, 200 * 1024)) ||
+            (e = set_max_dyn_smem((const void*)scan_q4k_mma_kernel<2>, 200 * 1024)) ||
+            (e = set_max_dyn_smem((const void*)scan_q4k_mma_kernel<4>, 200 * 1024)))
             return e;
-        attr_set = true;
     }
     if (ntg == 1)
         scan_q4k_mma_kernel<1><<<grid, MS_THREADS, smem, st>>>(m.w, m.rows, nsb, ws0, ws_stride, batch, want_hist, c1, err);

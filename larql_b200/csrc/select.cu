@@ -211,13 +211,8 @@ __global__ void __launch_bounds__(1024) sort_hits_kernel(const uint32_t* hit_idx
 }  // namespace
 
 cudaError_t launch_select(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             SEL_SMEM_VALS_MAX * 4);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    cudaError_t e = set_max_dyn_smem((const void*)select_kernel, SEL_SMEM_VALS_MAX * 4);
+    if (e != cudaSuccess) return e;
     const int use_smem = n <= SEL_SMEM_VALS_MAX;
     const size_t smem = use_smem ? (size_t)((n + 3) / 4 * 4) * sizeof(float) : 0;
     select_kernel<<<1, SEL_T, smem, st>>>(scores, n, top_k, ws, err, use_smem);
@@ -226,13 +221,8 @@ cudaError_t launch_select(const float* scores, int n, int top_k, TokenWs ws, int
 
 cudaError_t launch_classify(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st, int batch,
                             size_t ws_stride) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(classify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             SEL_SMEM_VALS_MAX * 4);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    cudaError_t e = set_max_dyn_smem((const void*)classify_kernel, SEL_SMEM_VALS_MAX * 4);
+    if (e != cudaSuccess) return e;
     const int use_smem = n <= SEL_SMEM_VALS_MAX;
     const size_t smem = use_smem ? (size_t)((n + 3) / 4 * 4) * sizeof(float) : 0;
     classify_kernel<<<dim3(1, batch), SEL_T, smem, st>>>(scores, n, top_k, ws, err, use_smem, ws_stride);
@@ -258,12 +248,8 @@ cudaError_t launch_topk_abs_sorted(const float* scores, int n, int top_k, TokenW
     }
     int n_pad = 1;
     while (n_pad < count) n_pad <<= 1;
-    static bool attr_set = false;
-    if (!attr_set) {
-        e = cudaFuncSetAttribute(sort_hits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 8);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    e = set_max_dyn_smem((const void*)sort_hits_kernel, 16384 * 8);
+    if (e != cudaSuccess) return e;
     const int use_smem = n_pad <= 16384;
     sort_hits_kernel<<<1, 1024, use_smem ? (size_t)n_pad * 8 : 0, st>>>(ws.hit_idx, ws.hit_score, ws.sel, scores,
                                                                         sort_buf, n_pad, use_smem, idx_out, val_out,
