@@ -468,6 +468,7 @@ struct Smem {
     __device__ __forceinline__ float* g_scores() const { return reinterpret_cast<float*>(g_rows() + 2 * cx().gm.max_slots); }
     __device__ __forceinline__ uint8_t* ring() const { return base + cx().gm.off_ring; }
 };
+static_assert(FW_NWARPS <= 32, "per-warp scratch arrays hold 32 warps");
 static_assert(192 + sizeof(Ctx) <= 1024 - 128, "context does not fit the barrier page");
 
 #define FW_STAMP(i)                                                                                    \
@@ -664,26 +665,27 @@ __device__ __noinline__ void phase_scan(int l) {
         const uint8_t* tb = ring + (size_t)stg * gm.tile_bytes + (active ? s : 0) * 144;  // idle lanes stay inside the row
         float* wp = wpart + (size_t)k * R * gm.Wt;  // [row of the tile][warp of the team]
         if (in_team) {
-            // two rows per pass in one straight-line block (two independent dependency chains); rows past
-            // the end of a ragged last tile are computed on whatever the stage holds and discarded
+            // Two rows per pass, reduced together: lanes 0-15 sum row r0 and lanes 16-31 row r1, five shuffles
+            // for the pair instead of ten.  Rows past the end of a ragged last tile are computed on whatever
+            // the stage holds and discarded.
             int j = 0;
             for (; FW_CFG_ILP2 && j + 1 < gm.Rt; j += 2) {
                 const int r0 = team + j * P, r1 = r0 + P;
                 const bool ok0 = active && r0 < rows_here, ok1 = active && r1 < rows_here;
                 float b0, b1;
                 float v0 = cell_dot(tb + (size_t)(ok0 ? r0 : 0) * gm.row_bytes, g, x, b0);
+#if !FW_CFG_ILP2
+                asm volatile("" ::: "memory");  // one row after the other: interleaving them costs registers this build lacks
+#endif
                 float v1 = cell_dot(tb + (size_t)(ok1 ? r1 : 0) * gm.row_bytes, g, x, b1);
                 v0 = ok0 ? v0 : 0.0f;
                 v1 = ok1 ? v1 : 0.0f;
                 bmax = fmaxf(bmax, fmaxf(ok0 ? b0 : 0.0f, ok1 ? b1 : 0.0f));
-                for (int o = 16; o > 0; o >>= 1) {
-                    v0 += __shfl_xor_sync(0xffffffffu, v0, o);
-                    v1 += __shfl_xor_sync(0xffffffffu, v1, o);
-                }
-                if (lane == 0) {
-                    wp[r0 * gm.Wt + wt] = v0;
-                    wp[r1 * gm.Wt + wt] = v1;
-                }
+                const bool upper = (lane & 16) != 0;
+                float v = (upper ? v1 : v0) + __shfl_xor_sync(0xffffffffu, upper ? v0 : v1, 16);
+                for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) wp[r0 * gm.Wt + wt] = v;
+                if (lane == 16) wp[r1 * gm.Wt + wt] = v;
             }
             for (; j < gm.Rt; ++j) {
                 const int r0 = team + j * P;
@@ -837,7 +839,7 @@ __device__ __noinline__ void phase_select(int l) {
     // and a CTA's list fits the ring in one piece.
     int n_fair;
     {
-        int* wcnt = reinterpret_cast<int*>(red) + 64;  // [2][16]
+        int* wcnt = reinterpret_cast<int*>(red) + 64;  // [2][32]
         const int chunk = (n_slots + FW_NWARPS - 1) / FW_NWARPS;
         const int chunk32 = (chunk + 31) / 32 * 32;
         const int beg = warp * chunk32, end = min(n_slots, beg + chunk32);
@@ -855,17 +857,17 @@ __device__ __noinline__ void phase_select(int l) {
         }
         if (lane == 0) {
             wcnt[warp] = ca;
-            wcnt[16 + warp] = cb;
+            wcnt[32 + warp] = cb;
         }
         bar_sync(FW_BAR_CONS, FW_CONSUMERS);
         int oa = 0, ob = 0, ta = 0, tb2 = 0;
         for (int w = 0; w < FW_NWARPS; ++w) {
             if (w < warp) {
                 oa += wcnt[w];
-                ob += wcnt[16 + w];
+                ob += wcnt[32 + w];
             }
             ta += wcnt[w];
-            tb2 += wcnt[16 + w];
+            tb2 += wcnt[32 + w];
         }
         n_fair = max(0, (a.top_k + (int)gridDim.x - 1) / (int)gridDim.x + 1 - tb2);
         for (int m0 = beg; m0 < end; m0 += 32) {
@@ -961,16 +963,96 @@ __device__ __noinline__ void phase_pick(int l) {
     // entries by counting; large bands fall back to a radix select of the threshold.
     const bool by_rank = !take_all && need > 0 && n_band_tot <= FW_RANK_CAP;
     int* win_s = reinterpret_cast<int*>(ring + FW_PICK_CAP * 8);
+    int* ired = reinterpret_cast<int*>(red);
+    int* scal = ired + 1240;     // my first pool item, my share
+    int* prefix = ired + 1280;   // [NC + 1] pool segments (start of every CTA's rows in the pool)
+    constexpr int STAGERS = FW_CONSUMERS - 32;  // the last warp shares out the pool meanwhile
+    if (warp == FW_NWARPS - 1) {
+        // This CTA's share of the pooled certainly-in rows.  Every CTA computes the same assignment from the
+        // published counts: CTA c has load e_c (own rows + band rows) and the pool is poured over the CTAs
+        // like water, the least loaded first, up to a common level L; a CTA below the level takes L - e_c
+        // pool rows (one fewer for the last few, so that the shares add up to the pool), as a contiguous
+        // range of the pool in CTA order.  A fixed rule: results stay run-to-run identical.  One warp,
+        // lane j holding CTAs j*cpl .. j*cpl + cpl - 1.
+        const int NC = (int)gridDim.x, cpl = (NC + 31) / 32;
+        auto wsum = [](int v) {
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            return v;
+        };
+        auto wscan_excl = [&](int v) {  // exclusive prefix over the lanes
+            int inc = v;
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += t;
+            }
+            return inc - v;
+        };
+        int ov[8], ev[8];
+        int lane_over = 0, lane_e = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = lane * cpl + i;
+            const bool valid = i < cpl && c < NC;
+            ov[i] = valid ? (int)__ldcg(&a.pool_cnt[c]) : 0;
+            ev[i] = valid ? (int)__ldcg(&a.pool_cnt[512 + c]) : 0x3fffffff;
+            lane_over += ov[i];
+            lane_e += valid ? ev[i] : 0;
+        }
+        const int total = wsum(lane_over), sum_e = wsum(lane_e);
+        {
+            int run = wscan_excl(lane_over);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int c = lane * cpl + i;
+                if (i < cpl && c < NC) prefix[c] = run;
+                run += ov[i];
+            }
+            if (lane == 0) prefix[NC] = total;
+        }
+        auto fill_at = [&](int level) {  // sum over CTAs of max(0, level - e_c)
+            int f = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f += max(0, level - ev[i]);
+            return wsum(f);
+        };
+        // the level is the smallest L with fill(L) >= total; ceil((sum e + total) / NC) is an upper bound
+        int level = total > 0 ? (sum_e + total + NC - 1) / NC : 0;
+        while (level > 0 && fill_at(level - 1) >= total) level -= 1;
+        const int excess = fill_at(level) - total;
+        int lane_below = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) lane_below += ev[i] < level ? 1 : 0;
+        const int n_below = wsum(lane_below);
+        int rank = wscan_excl(lane_below);
+        int share[8], lane_share = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const bool below = ev[i] < level;
+            share[i] = below ? level - ev[i] - (rank >= n_below - excess ? 1 : 0) : 0;
+            rank += below ? 1 : 0;
+            lane_share += share[i];
+        }
+        int first = wscan_excl(lane_share);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (i < cpl && lane * cpl + i == (int)blockIdx.x) {
+                scal[0] = first;
+                scal[1] = share[i];
+            }
+            first += share[i];
+        }
+    }
     if (!take_all && need > 0) {
         // stage (|v| key, row) of every band entry in the idle ring
         uint32_t* keys = reinterpret_cast<uint32_t*>(ring);
         uint32_t* rows = keys + FW_PICK_CAP;
         const bool staged = n_band_tot <= FW_PICK_CAP;
         if (staged) {
-            for (int i = tid; i < n_band_tot; i += FW_CONSUMERS) {
-                keys[i] = abs_key(__ldcg(&a.band_exact[i]));
-                rows[i] = __ldcg(&a.band_row[i]);
-            }
+            if (tid < STAGERS)
+                for (int i = tid; i < n_band_tot; i += STAGERS) {
+                    keys[i] = abs_key(__ldcg(&a.band_exact[i]));
+                    rows[i] = __ldcg(&a.band_row[i]);
+                }
             bar_sync(FW_BAR_CONS, FW_CONSUMERS);
         }
         if (by_rank) {
@@ -1025,73 +1107,11 @@ __device__ __noinline__ void phase_pick(int l) {
         }
         if (lane == 0) s_ctl[SC_N_G2] = n_keep + cnt;
     }
-    // This CTA's share of the pooled certainly-in rows.  Every CTA computes the same assignment from the
-    // published counts: CTA c has load e_c (own rows + band rows) and the pool is poured over the CTAs
-    // like water, the least loaded first, up to a common level L; a CTA below the level takes L - e_c
-    // pool rows (one fewer for the last few, so that the shares add up to the pool), as a contiguous
-    // range of the pool in CTA order.  A fixed rule: results stay run-to-run identical.
+    bar_sync(FW_BAR_CONS, FW_CONSUMERS);  // winners and the pool assignment are in place
     {
         const int NC = (int)gridDim.x;
-        int* ired = reinterpret_cast<int*>(red);
-        int* wtot = ired + 1200;     // [FW_NWARPS]
-        int* scal = ired + 1216;     // level, excess, CTAs below the level, my first item, my share
-        int* prefix = ired + 1280;   // [NC + 1] pool segments
-        int* lhist = ired + 1800;    // [256] CTAs per load
-        // exclusive prefix sum over the threads of the CTA (value v of thread tid), with the total
-        auto block_scan = [&](int v, int& total) -> int {
-            int inc = v;
-            for (int o = 1; o < 32; o <<= 1) {
-                const int t = __shfl_up_sync(0xffffffffu, inc, o);
-                if (lane >= o) inc += t;
-            }
-            if (lane == 31) wtot[warp] = inc;
-            bar_sync(FW_BAR_CONS, FW_CONSUMERS);
-            int lower = 0;
-            total = 0;
-            for (int w = 0; w < FW_NWARPS; ++w) {
-                const int t = wtot[w];
-                if (w < warp) lower += t;
-                total += t;
-            }
-            bar_sync(FW_BAR_CONS, FW_CONSUMERS);
-            return lower + inc - v;
-        };
-        const int over = tid < NC ? (int)__ldcg(&a.pool_cnt[tid]) : 0;
-        const int e = tid < NC ? min((int)__ldcg(&a.pool_cnt[512 + tid]), 255) : 0;
-        if (tid < 256) lhist[tid] = 0;
-        int total;
-        const int over_before = block_scan(over, total);  // (the scan's barriers also order the histogram clear)
-        if (tid < NC) {
-            prefix[tid] = over_before;
-            atomicAdd(&lhist[e], 1);
-        }
-        if (tid == 0) prefix[NC] = total;
-        bar_sync(FW_BAR_CONS, FW_CONSUMERS);
-        if (tid == 0) {
-            int level = 0, fill = 0, below = 0;  // fill = sum over CTAs of max(0, level - e_c); below = CTAs with e_c < level
-            while (fill < total) {
-                below += level < 256 ? lhist[level] : 0;
-                level += 1;
-                fill += below;
-            }
-            scal[0] = level;
-            scal[1] = fill - total;
-            scal[2] = below;
-        }
-        bar_sync(FW_BAR_CONS, FW_CONSUMERS);
-        const int level = scal[0], excess = scal[1], n_below = scal[2];
-        const int is_below = (tid < NC && e < level) ? 1 : 0;
-        int dummy;
-        const int rank_below = block_scan(is_below, dummy);
-        const int share = is_below ? level - e - (rank_below >= n_below - excess ? 1 : 0) : 0;
-        const int first = block_scan(share, dummy);
-        if (tid == (int)blockIdx.x) {
-            scal[3] = first;
-            scal[4] = share;
-        }
-        bar_sync(FW_BAR_CONS, FW_CONSUMERS);
         const int n_win = s_ctl[SC_N_G2];  // own rows and winners so far
-        const int my_first = scal[3], n_pool_mine = scal[4];
+        const int my_first = scal[0], n_pool_mine = scal[1];
         for (int i = tid; i < n_pool_mine; i += FW_CONSUMERS) {
             const int j = my_first + i;
             int sa = 0, sb = NC;  // prefix[sa] <= j < prefix[sb]
@@ -1104,7 +1124,7 @@ __device__ __noinline__ void phase_pick(int l) {
             g2_rows[n_win + i] = (int)__ldcg(&a.pool_row[src]);
             g2_scores[n_win + i] = __ldcg(&a.pool_score[src]);
         }
-        bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+        bar_sync(FW_BAR_CONS, FW_CONSUMERS);  // (every thread has read the counts above)
         if (tid == 0) s_ctl[SC_N_G2] = n_win + n_pool_mine;
     }
     if (l + 1 == a.n_layers && a.stats && blockIdx.x == 0 && tid == 0) {
@@ -1365,14 +1385,16 @@ cudaError_t launch_walk_fused_q4k(const void* layers_dev, const uint8_t* const* 
     a.top_k = top_k;
     a.flags = flags;
     a.c1 = c1;
-    // Next-layer gate prefetch into L2: by default about two thirds of each CTA's share, started
-    // once the first gather's rows have landed (the gather is on the critical path, the prefetch is not).
+    // L2 prefetch of gate tiles ahead of the ring (within a layer: LARQL_B200_FUSED_PFD tiles; across layers,
+    // during the previous layer's tail: LARQL_B200_FUSED_PF tiles).  Off by default: measured on B200 the scan
+    // waits for data only a tenth of its time, and the prefetch traffic slows the gather by more than it saves.
     static const int pf_env = [] { const char* v = getenv("LARQL_B200_FUSED_PF"); return v ? atoi(v) : -1; }();
     static const int pf_late_env = [] { const char* v = getenv("LARQL_B200_FUSED_PF_LATE"); return v ? atoi(v) : 1; }();
-    static const int pf_dist_env = [] { const char* v = getenv("LARQL_B200_FUSED_PFD"); return v ? atoi(v) : 8; }();
+    static const int pf_dist_env = [] { const char* v = getenv("LARQL_B200_FUSED_PFD"); return v ? atoi(v) : 0; }();
     a.pf_dist = pf_dist_env;
     const int tiles_per_cta = (n_tiles + grid - 1) / grid;
-    a.pf_tiles = (a.layers && n_layers > 1) ? (pf_env >= 0 ? pf_env : (2 * tiles_per_cta + 2) / 3) : 0;
+    (void)tiles_per_cta;
+    a.pf_tiles = (a.layers && n_layers > 1 && pf_env > 0) ? pf_env : 0;
     a.pf_late = pf_late_env ? 1 : 0;
     a.h_in = h_in;
     a.h_out = h_out;
