@@ -122,6 +122,41 @@ public:
                    ? std::optional(std::move(out))
                    : std::nullopt;
     }
+    // MatMul::f16_gemv / bf16_gemv (kind 0 / 1): w holds n*k little-endian 16-bit words
+    std::optional<std::vector<float>> gemv16(int kind, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t n,
+                                             size_t k, bool exact = false) {
+        std::vector<float> out(n);
+        return ok(lq_gemv16(ctx_, kind, w, w_len, x, x_len, n, k, out.data(), exact ? 1 : 0)) ? std::optional(std::move(out))
+                                                                                           : std::nullopt;
+    }
+    // MatMul::mxfp4_gemv_multi / nvfp4_gemv_multi: several matrices against one input, one submission
+    std::optional<std::vector<std::vector<float>>> gemv_multi(const std::vector<QuantMatrix>& mats, const float* x,
+                                                              size_t x_len, bool exact = false) {
+        std::vector<lq_matrix> cm;
+        std::vector<std::vector<float>> outs;
+        std::vector<float*> ptrs;
+        for (const auto& m : mats) {
+            cm.push_back(m.c());
+            outs.emplace_back(static_cast<size_t>(m.rows));
+        }
+        for (auto& o : outs) ptrs.push_back(o.data());
+        return ok(lq_gemv_multi(ctx_, cm.data(), cm.size(), x, x_len, ptrs.data(), exact ? 1 : 0)) ? std::optional(std::move(outs))
+                                                                                                : std::nullopt;
+    }
+    // QuantMatVec::q4k_matvec_topk: (row, score) sorted by score descending, ties to the lower row
+    std::optional<std::vector<std::pair<uint32_t, float>>> q4k_matvec_topk(const uint8_t* w, size_t w_len, const float* x,
+                                                                           size_t x_len, size_t num_rows, size_t hidden,
+                                                                           size_t top_k) {
+        const size_t k = top_k < num_rows ? top_k : num_rows;
+        std::vector<uint32_t> idx(k ? k : 1);
+        std::vector<float> val(k ? k : 1);
+        size_t count = 0;
+        if (!ok(lq_q4k_matvec_topk(ctx_, w, w_len, x, x_len, num_rows, hidden, top_k, idx.data(), val.data(), &count)))
+            return std::nullopt;
+        std::vector<std::pair<uint32_t, float>> r(count);
+        for (size_t i = 0; i < count; ++i) r[i] = {idx[i], val[i]};
+        return r;
+    }
     // top_k_by_abs: (index, signed score) of the top_k largest |score|, ties to the lower index
     std::optional<std::vector<std::pair<uint32_t, float>>> top_k_by_abs(const float* scores, size_t n, size_t top_k) {
         const size_t k = top_k < n ? top_k : n;

@@ -145,6 +145,43 @@ LQ_API int lq_nvfp4_gemv(lq_ctx* ctx, const uint8_t* packed, size_t packed_len, 
                          size_t scales_len, float tensor_scale, const float* x, size_t x_len, size_t n, size_t k,
                          float* out);
 
+/* Several block-format matrices against ONE input vector, one submission (the input is uploaded once, the
+ * call waits once): MatMul::mxfp4_gemv_multi / nvfp4_gemv_multi (backend/matmul.rs:242-251, 279-286) as
+ * DevicePlanBackend calls them (crates/larql-vindex/src/format/vindex3/opplan/exec/device.rs:256-341).  Every
+ * matrix's cols must equal x_len; outs[i] receives rows_i floats.  Results are those of the single gemvs. */
+LQ_API int lq_gemv_multi(lq_ctx* ctx, const lq_matrix* mats, size_t n_mats, const float* x, size_t x_len,
+                         float* const* outs, int exact);
+LQ_API int lq_mxfp4_gemv_multi(lq_ctx* ctx, const lq_matrix* mats, size_t n_mats, const float* x, size_t x_len,
+                               float* const* outs);
+LQ_API int lq_nvfp4_gemv_multi(lq_ctx* ctx, const lq_matrix* mats, size_t n_mats, const float* x, size_t x_len,
+                               float* const* outs);
+
+/* Dense gemv over f16 (kind 0) or bf16 (kind 1) weights [n, k], little-endian 16-bit words:
+ * MatMul::f16_gemv(_force) / bf16_gemv(_force) / f16_gemv_multi / bf16_gemv_multi (backend/matmul.rs:124-205).
+ * Refuses (LQ_REFUSED_SHAPE) when w_len < n*k*2 or x_len != k.  exact = 1: one running f32 sum per row, k
+ * ascending, the loop of the reference's test device (…/opplan/exec/tests/device.rs:68-84; the CPU backend has
+ * no f16 / bf16 gemv of its own); exact = 0: warp-per-row tree sum (any order, f32). */
+LQ_API int lq_gemv16(lq_ctx* ctx, int kind, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t n,
+                     size_t k, float* out, int exact);
+LQ_API int lq_gemv16_multi(lq_ctx* ctx, int kind, size_t n_mats, const uint8_t* const* ws, const size_t* w_lens,
+                           const size_t* ns, size_t k, const float* x, size_t x_len, float* const* outs, int exact);
+LQ_API int lq_f16_gemv(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t n, size_t k,
+                       float* out);
+LQ_API int lq_bf16_gemv(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t n, size_t k,
+                        float* out);
+
+/* LM-head style scan + top-k: QuantMatVec::q4k_matvec_topk (backend/quant_matvec.rs:268-277) and
+ * MatMul::f16_gemv_topk (backend/matmul.rs:100-109).  Up to top_k (row, score) pairs sorted by score
+ * descending, ties to the lower row; *count = min(top_k, rows).  Scores are computed in the reference
+ * order (q4k_matvec's / the f16 loop's), so the rows are the ones the caller's fallback (full matvec + CPU
+ * reduce) would pick.  top_k <= 16384.  LQ_ERR_NAN_SCORE if a score is NaN. */
+LQ_API int lq_q4k_matvec_topk(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t num_rows,
+                              size_t hidden, size_t top_k, uint32_t* idx_out, float* val_out, size_t* count);
+LQ_API int lq_gemv16_topk(lq_ctx* ctx, int kind, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t n,
+                          size_t k, size_t top_k, uint32_t* idx_out, float* val_out, size_t* count);
+LQ_API int lq_f16_gemv_topk(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t n,
+                            size_t k, size_t top_k, uint32_t* idx_out, float* val_out, size_t* count);
+
 /* MoE routing (crates/larql-compute/src/cpu/ops/moe/math.rs:130-164, mod.rs:127-189): per token a
  * max-subtracted softmax over n_experts logits, the top_k experts by probability (ties to the lower
  * index, descending), weights renormalised over the selected when renormalise != 0.

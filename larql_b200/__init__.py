@@ -37,7 +37,9 @@ EXPORTS = [
     "lq_stack_create", "lq_stack_run", "lq_stack_destroy", "lq_last_walk_stats", "lq_dev_quantize_q4k",
     "lq_profile_walk", "lq_fused_phase_us", "lq_q4k_matvec_static", "lq_dev_shard_scan", "lq_dev_shard_classify",
     "lq_dev_shard_gather", "lq_gemv", "lq_q8_0_gemv", "lq_mxfp4_gemv", "lq_nvfp4_gemv", "lq_moe_route",
-    "lq_moe_walk_ffn", "lq_stack_run_host", "lq_dev_shard_hits",
+    "lq_moe_walk_ffn", "lq_stack_run_host", "lq_dev_shard_hits", "lq_gemv_multi", "lq_mxfp4_gemv_multi",
+    "lq_nvfp4_gemv_multi", "lq_gemv16", "lq_gemv16_multi", "lq_f16_gemv", "lq_bf16_gemv", "lq_q4k_matvec_topk",
+    "lq_gemv16_topk", "lq_f16_gemv_topk",
 ]
 
 
@@ -110,6 +112,16 @@ def load_library() -> C.CDLL:
         "lq_moe_walk_ffn": (C.c_int, [vp, mp, mp, mp, sz, f32p, f32p, sz, sz, C.c_int, sz, C.c_uint32, f32p, u32p,
                                       f32p]),
         "lq_q4k_matvec_static": (C.c_int, [vp, sz, f32p, sz, sz, f32p, vp, C.c_char_p, sz]),
+        "lq_gemv_multi": (C.c_int, [vp, vp, sz, f32p, sz, vp, C.c_int]),
+        "lq_mxfp4_gemv_multi": (C.c_int, [vp, vp, sz, f32p, sz, vp]),
+        "lq_nvfp4_gemv_multi": (C.c_int, [vp, vp, sz, f32p, sz, vp]),
+        "lq_gemv16": (C.c_int, [vp, C.c_int, vp, sz, f32p, sz, sz, sz, f32p, C.c_int]),
+        "lq_gemv16_multi": (C.c_int, [vp, C.c_int, sz, vp, vp, vp, sz, f32p, sz, vp, C.c_int]),
+        "lq_f16_gemv": (C.c_int, [vp, vp, sz, f32p, sz, sz, sz, f32p]),
+        "lq_bf16_gemv": (C.c_int, [vp, vp, sz, f32p, sz, sz, sz, f32p]),
+        "lq_q4k_matvec_topk": (C.c_int, [vp, vp, sz, f32p, sz, sz, sz, sz, u32p, f32p, C.POINTER(sz)]),
+        "lq_gemv16_topk": (C.c_int, [vp, C.c_int, vp, sz, f32p, sz, sz, sz, sz, u32p, f32p, C.POINTER(sz)]),
+        "lq_f16_gemv_topk": (C.c_int, [vp, vp, sz, f32p, sz, sz, sz, sz, u32p, f32p, C.POINTER(sz)]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -296,6 +308,62 @@ class CudaBackend:
         ok = self._status(self._lib.lq_nvfp4_gemv(self._h, _ptr(w), w.size, _ptr(sc), sc.size, float(tensor_scale),
                                                   _ptr(x), x.size, n, k, _ptr(out)))
         return out if ok else None
+
+    def gemv_multi(self, mats, x, exact: bool = False):
+        """MatMul::mxfp4_gemv_multi / nvfp4_gemv_multi (any block format): several matrices, one input, one
+        submission.  Returns a list of outputs, or None on refusal."""
+        x = _f32(x).reshape(-1)
+        n = len(mats)
+        arr = (LqMatrix * max(n, 1))(*[m.c() for m in mats])
+        outs = [np.empty(m.rows, np.float32) for m in mats]
+        ptrs = (C.c_void_p * max(n, 1))(*[o.ctypes.data for o in outs])
+        ok = self._status(self._lib.lq_gemv_multi(self._h, arr, n, _ptr(x), x.size, ptrs, int(exact)))
+        return outs if ok else None
+
+    def gemv16(self, w_bits, x, n: int, k: int, kind: str = "f16", exact: bool = False):
+        """MatMul::f16_gemv / bf16_gemv: w_bits holds n*k little-endian 16-bit words."""
+        w = np.ascontiguousarray(w_bits).view(np.uint8).reshape(-1)
+        x = _f32(x).reshape(-1)
+        out = np.empty(n, np.float32)
+        ok = self._status(self._lib.lq_gemv16(self._h, 0 if kind == "f16" else 1, _ptr(w), w.size, _ptr(x), x.size, n, k,
+                                              _ptr(out), int(exact)))
+        return out if ok else None
+
+    def gemv16_multi(self, weights, x, kind: str = "f16", exact: bool = False):
+        """MatMul::f16_gemv_multi / bf16_gemv_multi: weights = [(w_bits, n, k), ...], every k == len(x)."""
+        x = _f32(x).reshape(-1)
+        ws = [np.ascontiguousarray(w).view(np.uint8).reshape(-1) for w, _, _ in weights]
+        ns = [int(n) for _, n, _ in weights]
+        if any(int(k) != x.size for _, _, k in weights):
+            return None
+        m = len(weights)
+        outs = [np.empty(n, np.float32) for n in ns]
+        wp = (C.c_void_p * max(m, 1))(*[w.ctypes.data for w in ws])
+        wl = (C.c_size_t * max(m, 1))(*[w.size for w in ws])
+        nn = (C.c_size_t * max(m, 1))(*ns)
+        op = (C.c_void_p * max(m, 1))(*[o.ctypes.data for o in outs])
+        ok = self._status(self._lib.lq_gemv16_multi(self._h, 0 if kind == "f16" else 1, m, wp, wl, nn, x.size, _ptr(x),
+                                                    x.size, op, int(exact)))
+        return outs if ok else None
+
+    def q4k_matvec_topk(self, q4k_data, x, num_rows: int, hidden: int, top_k: int):
+        """QuantMatVec::q4k_matvec_topk: [(row, score)] sorted by score descending, ties to the lower row."""
+        w, x = _u8(q4k_data), _f32(x).reshape(-1)
+        k = max(1, min(int(top_k), num_rows))
+        idx, val, cnt = np.empty(k, np.uint32), np.empty(k, np.float32), C.c_size_t(0)
+        ok = self._status(self._lib.lq_q4k_matvec_topk(self._h, _ptr(w), w.size, _ptr(x), x.size, num_rows, hidden,
+                                                       int(top_k), idx.ctypes.data, val.ctypes.data, C.byref(cnt)))
+        return list(zip(idx[:cnt.value].tolist(), val[:cnt.value].tolist())) if ok else None
+
+    def f16_gemv_topk(self, w_bits, x, n: int, k: int, top_k: int, kind: str = "f16"):
+        """MatMul::f16_gemv_topk (and its bf16 sibling)."""
+        w = np.ascontiguousarray(w_bits).view(np.uint8).reshape(-1)
+        x = _f32(x).reshape(-1)
+        kk = max(1, min(int(top_k), n))
+        idx, val, cnt = np.empty(kk, np.uint32), np.empty(kk, np.float32), C.c_size_t(0)
+        ok = self._status(self._lib.lq_gemv16_topk(self._h, 0 if kind == "f16" else 1, _ptr(w), w.size, _ptr(x), x.size,
+                                                   n, k, int(top_k), idx.ctypes.data, val.ctypes.data, C.byref(cnt)))
+        return list(zip(idx[:cnt.value].tolist(), val[:cnt.value].tolist())) if ok else None
 
     # -- MoE --------------------------------------------------------------------
     def moe_route(self, logits, top_k: int, renormalise: bool = True):

@@ -788,6 +788,210 @@ int lq_nvfp4_gemv(lq_ctx* ctx, const uint8_t* packed, size_t packed_len, const u
     return lq_gemv(ctx, &m, x, x_len, out, n, 0);
 }
 
+// Several block-format matrices against ONE input vector in one submission: the input is uploaded
+// once, every gemv is enqueued back to back and the call waits once.
+int lq_gemv_multi(lq_ctx* ctx, const lq_matrix* mats, size_t n_mats, const float* x, size_t x_len, float* const* outs,
+                  int exact) {
+    DevGuard dev_guard(ctx);
+    if (!ctx || (n_mats && (!mats || !outs))) return LQ_ERR_ARGUMENT;
+    if (n_mats == 0) return LQ_OK;
+    size_t total_out = 0;
+    int rc;
+    std::vector<lq_matrix> dm(n_mats);
+    for (size_t i = 0; i < n_mats; ++i) {
+        if ((rc = check_matrix(ctx, &mats[i], "gemv_multi"))) return rc;
+        const int fmt = mats[i].fmt & 0xff;
+        const size_t k = (size_t)mats[i].cols;
+        if (x_len != k) return fail(ctx, LQ_REFUSED_SHAPE, "gemv_multi: every k must equal x_len");
+        if (fmt == LQ_FMT_Q4_K ? (k % 256 != 0) : (k % 32 != 0) || k > 16384 || k == 0)
+            return fail(ctx, LQ_REFUSED_UNSUPPORTED, "gemv_multi: k must be a block multiple, 1..16384");
+        if ((rc = resolve_matrix(ctx, &mats[i], &dm[i]))) return rc;
+        if (fmt == LQ_FMT_Q4_K ? (((uintptr_t)dm[i].data & 15) != 0) : !fmt_aligned(dm[i]))
+            return fail(ctx, LQ_REFUSED_UNSUPPORTED, "gemv_multi: weight base address not block aligned");
+        total_out += a256((size_t)mats[i].rows * 4);
+    }
+    const size_t k = x_len;
+    if ((rc = ensure_ws(ctx, 1, k, 32))) return rc;
+    if ((rc = ensure_stage(ctx, a256(k * 4) + total_out + 512))) return rc;
+    float* dx = (float*)ctx->stage;
+    uint8_t* dout = ctx->stage + a256(k * 4);
+    TokenWs& t = ctx->tok[0];
+    CK(cudaMemcpyAsync(dx, x, k * 4, cudaMemcpyHostToDevice, ctx->stream));
+    if (!exact) {
+        launch_prep(dx, 1, (int)k, 0, 0.0, t.xn, t.xa, t.xb, t.bscale, t.bsum, t.babs, 0, nullptr, ctx->stream);
+        CK(cudaGetLastError());
+        ctx->launches += 1;
+    }
+    size_t off = 0;
+    for (size_t i = 0; i < n_mats; ++i) {
+        const size_t n = (size_t)dm[i].rows;
+        float* o = (float*)(dout + off);
+        if (n) {
+            if ((dm[i].fmt & 0xff) == LQ_FMT_Q4_K) {
+                const Q4kMat m{(const uint8_t*)dm[i].data, (int)n, (int)k};
+                if (exact)
+                    CK(launch_rescore_q4k(m, dx, nullptr, nullptr, (int)n, o, t, 0, 0, ctx->d_err, ctx->sm_count,
+                                          ctx->stream));
+                else
+                    CK(launch_scan_q4k(m, xprep_of(t), o, nullptr, nullptr, 0.0f, ctx->d_err, ctx->sm_count, ctx->stream));
+            } else {
+                const FmtMat fm = fmtmat_of(dm[i]);
+                if (exact) CK(launch_rescore_fmt(fm, dx, nullptr, nullptr, (int)n, o, ctx->sm_count, ctx->stream));
+                else CK(launch_scan_fmt(fm, xprep_of(t), o, nullptr, nullptr, 0.0f, ctx->d_err, ctx->sm_count, ctx->stream));
+            }
+            ctx->launches += 1;
+            CK(cudaMemcpyAsync(outs[i], o, n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        }
+        off += a256(n * 4);
+    }
+    return lq_synchronize(ctx);
+}
+
+int lq_mxfp4_gemv_multi(lq_ctx* ctx, const lq_matrix* mats, size_t n_mats, const float* x, size_t x_len,
+                        float* const* outs) {
+    for (size_t i = 0; mats && i < n_mats; ++i)
+        if ((mats[i].fmt & 0xff) != LQ_FMT_MXFP4) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "mxfp4_gemv_multi: not MXFP4");
+    return lq_gemv_multi(ctx, mats, n_mats, x, x_len, outs, 0);
+}
+int lq_nvfp4_gemv_multi(lq_ctx* ctx, const lq_matrix* mats, size_t n_mats, const float* x, size_t x_len,
+                        float* const* outs) {
+    for (size_t i = 0; mats && i < n_mats; ++i)
+        if ((mats[i].fmt & 0xff) != LQ_FMT_NVFP4) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "nvfp4_gemv_multi: not NVFP4");
+    return lq_gemv_multi(ctx, mats, n_mats, x, x_len, outs, 0);
+}
+
+// f16 (kind 0) / bf16 (kind 1) gemv, single and multi, and the LM-head top-k forms.
+static int gemv16_check(lq_ctx* ctx, size_t w_len, size_t x_len, size_t n, size_t k, int kind, int exact) {
+    if (kind != 0 && kind != 1) return fail(ctx, LQ_ERR_ARGUMENT, "gemv16: kind must be 0 (f16) or 1 (bf16)");
+    if (w_len < n * k * 2 || x_len != k) return fail(ctx, LQ_REFUSED_SHAPE, "gemv16: w_len < n*k*2 or x_len != k");
+    if (n > 0x7fffffffu || k > 0x7fffffffu || (exact && k > 32768))
+        return fail(ctx, LQ_REFUSED_UNSUPPORTED, "gemv16: size");
+    return LQ_OK;
+}
+
+int lq_gemv16_multi(lq_ctx* ctx, int kind, size_t n_mats, const uint8_t* const* ws, const size_t* w_lens,
+                    const size_t* ns, size_t k, const float* x, size_t x_len, float* const* outs, int exact) {
+    DevGuard dev_guard(ctx);
+    if (!ctx || (n_mats && (!ws || !w_lens || !ns || !outs))) return LQ_ERR_ARGUMENT;
+    int rc;
+    size_t total_out = 0;
+    std::vector<const uint8_t*> dw(n_mats);
+    for (size_t i = 0; i < n_mats; ++i) {
+        if ((rc = gemv16_check(ctx, w_lens[i], x_len, ns[i], k, kind, exact))) return rc;
+        if ((rc = resolve(ctx, ws[i], ns[i] * k * 2, &dw[i]))) return rc;
+        if (((uintptr_t)dw[i] & 1) != 0) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "gemv16: weights not 2-byte aligned");
+        total_out += a256(ns[i] * 4);
+    }
+    if (n_mats == 0 || k == 0) {
+        for (size_t i = 0; i < n_mats; ++i) memset(outs[i], 0, ns[i] * 4);
+        return LQ_OK;
+    }
+    if ((rc = ensure_stage(ctx, a256(k * 4) + total_out + 512))) return rc;
+    float* dx = (float*)ctx->stage;
+    uint8_t* dout = ctx->stage + a256(k * 4);
+    CK(cudaMemcpyAsync(dx, x, k * 4, cudaMemcpyHostToDevice, ctx->stream));
+    size_t off = 0;
+    for (size_t i = 0; i < n_mats; ++i) {
+        float* o = (float*)(dout + off);
+        if (ns[i]) {
+            CK(launch_gemv16(dw[i], dx, (int)ns[i], (int)k, kind, exact, o, ctx->stream));
+            ctx->launches += 1;
+            CK(cudaMemcpyAsync(outs[i], o, ns[i] * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        }
+        off += a256(ns[i] * 4);
+    }
+    return lq_synchronize(ctx);
+}
+
+int lq_gemv16(lq_ctx* ctx, int kind, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t n, size_t k,
+              float* out, int exact) {
+    return lq_gemv16_multi(ctx, kind, 1, &w, &w_len, &n, k, x, x_len, &out, exact);
+}
+int lq_f16_gemv(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t n, size_t k,
+                float* out) {
+    return lq_gemv16(ctx, 0, w, w_len, x, x_len, n, k, out, 0);
+}
+int lq_bf16_gemv(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t n, size_t k,
+                 float* out) {
+    return lq_gemv16(ctx, 1, w, w_len, x, x_len, n, k, out, 0);
+}
+
+// Scores on the device (reference order), top-k by value on the device, k pairs back.
+static int topk_from_scores(lq_ctx* ctx, float* dscores, size_t n, size_t top_k, uint32_t* idx_out, float* val_out,
+                            size_t* count) {
+    const size_t kk = std::min(top_k, n);
+    uint32_t* di = (uint32_t*)((uint8_t*)dscores + a256(n * 4));
+    float* dv = (float*)((uint8_t*)di + a256(kk * 4));
+    CK(launch_topk_value_sorted(dscores, (int)n, (int)kk, di, dv, ctx->d_err, ctx->stream));
+    ctx->launches += 1;
+    CK(cudaMemcpyAsync(idx_out, di, kk * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CK(cudaMemcpyAsync(val_out, dv, kk * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    int rc = lq_synchronize(ctx);
+    if (rc) return rc;
+    *count = kk;
+    return LQ_OK;
+}
+
+int lq_q4k_matvec_topk(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t num_rows,
+                       size_t hidden, size_t top_k, uint32_t* idx_out, float* val_out, size_t* count) {
+    DevGuard dev_guard(ctx);
+    if (!ctx || !count) return LQ_ERR_ARGUMENT;
+    *count = 0;
+    const size_t needed = (hidden / 256) * 144 * num_rows;
+    if (!(x_len == hidden && hidden % 256 == 0 && w_len >= needed))
+        return fail(ctx, LQ_REFUSED_SHAPE, "q4k_matvec_topk: shape (KernelShapeError)");
+    if (num_rows == 0 || top_k == 0) return LQ_OK;
+    if (hidden == 0 || hidden > 16384 || num_rows > 0x7fffffffu)
+        return fail(ctx, LQ_REFUSED_UNSUPPORTED, "q4k_matvec_topk: hidden 256..16384");
+    if (std::min(top_k, num_rows) > 16384) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "q4k_matvec_topk: top_k > 16384");
+    if (!idx_out || !val_out) return LQ_ERR_ARGUMENT;
+    const uint8_t* dw;
+    int rc = resolve(ctx, w, needed, &dw);
+    if (rc) return rc;
+    if (((uintptr_t)dw & 15) != 0) return fail(ctx, LQ_ERR_ARGUMENT, "q4k_matvec_topk: weights not 16-byte aligned");
+    const size_t kk = std::min(top_k, num_rows);
+    if ((rc = ensure_ws(ctx, 1, hidden, 32))) return rc;
+    if ((rc = ensure_stage(ctx, a256(hidden * 4) + a256(num_rows * 4) + 2 * a256(kk * 4) + 512))) return rc;
+    float* dx = (float*)ctx->stage;
+    float* ds = (float*)(ctx->stage + a256(hidden * 4));
+    CK(cudaMemcpyAsync(dx, x, hidden * 4, cudaMemcpyHostToDevice, ctx->stream));
+    const Q4kMat m{dw, (int)num_rows, (int)hidden};
+    // scores in the CPU backend's exact order, so that the selected rows are the ones q4k_matvec + a CPU
+    // reduce would pick
+    CK(launch_rescore_q4k(m, dx, nullptr, nullptr, (int)num_rows, ds, ctx->tok[0], 0, 0, ctx->d_err, ctx->sm_count,
+                          ctx->stream));
+    ctx->launches += 1;
+    return topk_from_scores(ctx, ds, num_rows, top_k, idx_out, val_out, count);
+}
+
+int lq_gemv16_topk(lq_ctx* ctx, int kind, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t n,
+                   size_t k, size_t top_k, uint32_t* idx_out, float* val_out, size_t* count) {
+    DevGuard dev_guard(ctx);
+    if (!ctx || !count) return LQ_ERR_ARGUMENT;
+    *count = 0;
+    int rc = gemv16_check(ctx, w_len, x_len, n, k, kind, 1);
+    if (rc) return rc;
+    if (n == 0 || top_k == 0) return LQ_OK;
+    if (k == 0) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "gemv16_topk: k == 0");
+    if (std::min(top_k, n) > 16384) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "gemv16_topk: top_k > 16384");
+    if (!idx_out || !val_out) return LQ_ERR_ARGUMENT;
+    const uint8_t* dw;
+    if ((rc = resolve(ctx, w, n * k * 2, &dw))) return rc;
+    if (((uintptr_t)dw & 1) != 0) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "gemv16_topk: weights not 2-byte aligned");
+    const size_t kk = std::min(top_k, n);
+    if ((rc = ensure_stage(ctx, a256(k * 4) + a256(n * 4) + 2 * a256(kk * 4) + 512))) return rc;
+    float* dx = (float*)ctx->stage;
+    float* ds = (float*)(ctx->stage + a256(k * 4));
+    CK(cudaMemcpyAsync(dx, x, k * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CK(launch_gemv16(dw, dx, (int)n, (int)k, kind, 1, ds, ctx->stream));
+    ctx->launches += 1;
+    return topk_from_scores(ctx, ds, n, top_k, idx_out, val_out, count);
+}
+int lq_f16_gemv_topk(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t n, size_t k,
+                     size_t top_k, uint32_t* idx_out, float* val_out, size_t* count) {
+    return lq_gemv16_topk(ctx, 0, w, w_len, x, x_len, n, k, top_k, idx_out, val_out, count);
+}
+
 int lq_moe_route(lq_ctx* ctx, const float* logits, size_t n_tokens, size_t n_experts, size_t top_k, int renormalise,
                  uint32_t* idx_out, float* w_out) {
     DevGuard dev_guard(ctx);

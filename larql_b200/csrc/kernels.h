@@ -133,6 +133,12 @@ cudaError_t launch_classify(const float* scores, int n, int top_k, TokenWs ws, i
 cudaError_t launch_topk_abs_sorted(const float* scores, int n, int top_k, uint32_t* idx_out, float* val_out,
                                    int* count_out, void* scratch, int* err, cudaStream_t st);
 
+// Top-K by value (descending, ties to the lower index), sorted; top_k <= 16384.
+cudaError_t launch_topk_value_sorted(const float* scores, int n, int top_k, uint32_t* idx_out, float* val_out, int* err,
+                                     cudaStream_t st);
+// dense16.cu: gemv over f16 (kind 0) / bf16 (kind 1) weights [n, k]; exact = the reference loop's order
+cudaError_t launch_gemv16(const void* w, const float* x, int n, int k, int kind, int exact, float* out, cudaStream_t st);
+
 // gather_q4k.cu
 int gather_q4k_grid(int sm_count);
 cudaError_t launch_gather_q4k(const Q4kMat& up, const Q4kMat& down, const XPrep& xp, const uint32_t* hit_idx,

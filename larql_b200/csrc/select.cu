@@ -208,7 +208,97 @@ __global__ void __launch_bounds__(1024) sort_hits_kernel(const uint32_t* hit_idx
     if (tid == 0 && count_out) *count_out = count;
 }
 
+// Top-K by VALUE (descending, ties to the lower index), sorted: the order of the LM-head style calls
+// q4k_matvec_topk / f16_gemv_topk (crates/larql-compute/src/backend/quant_matvec.rs:268-277,
+// backend/matmul.rs:100-109).  One CTA: radix select of the K-th largest ordered key, index-ordered
+// compaction of the winners into 64-bit (key, row) words, bitonic sort in shared memory.
+__device__ __forceinline__ uint32_t value_key(float v) {  // larger value -> larger key
+    const uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__global__ void __launch_bounds__(SEL_T, 1)
+topk_value_kernel(const float* __restrict__ scores, int n, int top_k, int n_pad, uint32_t* __restrict__ idx_out,
+                  float* __restrict__ val_out, int* err) {
+    extern __shared__ __align__(16) unsigned long long t_buf[];  // [n_pad]
+    __shared__ SelectSmem<SEL_T> sm;
+    __shared__ int s_cut, s_nan;
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        s_cut = n;
+        s_nan = 0;
+    }
+    for (int i = tid; i < n_pad; i += SEL_T) t_buf[i] = ~0ull;  // pads sort to the end
+    __syncthreads();
+    bool nan = false;
+    for (int i = tid; i < n; i += SEL_T) nan |= scores[i] != scores[i];
+    if (nan) s_nan = 1;
+    __syncthreads();
+    if (s_nan) {
+        set_err(err, DEV_ERR_NAN_SCORE);
+        return;
+    }
+    const int k = min(top_k, n);
+    auto keyf = [scores](int i) { return value_key(scores[i]); };
+    uint32_t tau_key = 0;
+    int cnt_gt = 0, need_eq = k;
+    if (k < n) block_kth_largest_keys<SEL_T, 0>(keyf, n, k, sm, tau_key, cnt_gt, need_eq);
+    int na, nb;
+    if (k < n) {
+        // the need_eq lowest rows among those equal to the threshold
+        block_compact2<SEL_T>(
+            n, sm, need_eq, [&](int i) { return keyf(i) == tau_key ? 2 : 0; }, [&](int, int) {},
+            [&](int pos, int i) { if (pos == need_eq - 1) s_cut = i + 1; }, na, nb);
+        __syncthreads();
+    }
+    const int cut = s_cut;
+    block_compact2<SEL_T>(
+        n, sm, 0,
+        [&](int i) {
+            if (k >= n) return 1;
+            const uint32_t key = keyf(i);
+            return (key > tau_key || (key == tau_key && i < cut)) ? 1 : 0;
+        },
+        [&](int pos, int i) { t_buf[pos] = ((unsigned long long)(~keyf(i)) << 32) | (unsigned long long)(uint32_t)i; },
+        [&](int, int) {}, na, nb);
+    __syncthreads();
+    for (int size = 2; size <= n_pad; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int t = tid; t < n_pad / 2; t += SEL_T) {
+                const int lo = 2 * t - (t & (stride - 1));
+                const int hi = lo + stride;
+                const bool up = ((lo & size) == 0);
+                const unsigned long long a = t_buf[lo], b = t_buf[hi];
+                if ((a > b) == up) {
+                    t_buf[lo] = b;
+                    t_buf[hi] = a;
+                }
+            }
+            __syncthreads();
+        }
+    }
+    for (int i = tid; i < k; i += SEL_T) {
+        const uint32_t r = (uint32_t)(t_buf[i] & 0xffffffffull);
+        idx_out[i] = r;
+        val_out[i] = scores[r];
+    }
+}
+
 }  // namespace
+
+// top_k <= 16384 (the sort runs in shared memory)
+cudaError_t launch_topk_value_sorted(const float* scores, int n, int top_k, uint32_t* idx_out, float* val_out, int* err,
+                                     cudaStream_t st) {
+    const int k = top_k < n ? top_k : n;
+    if (k <= 0) return cudaSuccess;
+    if (k > 16384) return cudaErrorInvalidValue;
+    int n_pad = 1;
+    while (n_pad < k) n_pad <<= 1;
+    cudaError_t e = set_max_dyn_smem((const void*)topk_value_kernel, 16384 * 8);
+    if (e != cudaSuccess) return e;
+    topk_value_kernel<<<1, SEL_T, (size_t)n_pad * 8, st>>>(scores, n, top_k, n_pad, idx_out, val_out, err);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_select(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st) {
     cudaError_t e = set_max_dyn_smem((const void*)select_kernel, SEL_SMEM_VALS_MAX * 4);

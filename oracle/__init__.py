@@ -267,6 +267,28 @@ def mxfp4_gemv(packed, scales, x, n: int, k: int):
     return None if rc else out
 
 
+def gemv16(w_bits, x, n: int, k: int, kind: int):
+    """f16 (kind 0) / bf16 (kind 1) gemv in the reference test device's order; None on a shape mismatch."""
+    w = np.ascontiguousarray(w_bits).view(np.uint8).reshape(-1)
+    x = _f32(x)
+    out = np.empty(n, np.float32)
+    rc = lib().orc_gemv16(_p(w), _sz(w.size), _p(x), _sz(x.size), _sz(n), _sz(k), C.c_int(kind), _p(out))
+    return None if rc else out
+
+
+def top_k_by_value(scores, top_k: int):
+    """(idx, val) of the top_k largest values, descending, ties to the lower index. Raises on NaN."""
+    s = _f32(scores).reshape(-1)
+    k = min(int(top_k), s.size)
+    idx = np.empty(max(k, 1), np.uint32)
+    val = np.empty(max(k, 1), np.float32)
+    lib().orc_top_k_by_value.restype = C.c_long
+    got = lib().orc_top_k_by_value(_p(s), _sz(s.size), _sz(top_k), _p(idx), _p(val))
+    if got < 0:
+        raise ValueError("NaN score")
+    return idx[:got].copy(), val[:got].copy()
+
+
 # ---------------------------------------------------------------- top-K
 def top_k_by_abs(scores, top_k: int, heap: bool = False):
     """Returns (idx uint32[k'], val float32[k']) sorted (|v| desc, idx asc). Raises on NaN."""

@@ -496,6 +496,56 @@ ORC_API int orc_q8_0_gemv(const uint8_t *blocks, size_t blocks_len, const float 
     return 0;
 }
 
+/* f16 / bf16 gemv as the reference's test device computes it (the CPU backend has no f16 / bf16 gemv:
+ * trait default None, crates/larql-compute/src/backend/matmul.rs:124-147):
+ * crates/larql-vindex/src/format/vindex3/opplan/exec/tests/device.rs:68-84 — per row the products
+ * widen(w) * x[col] folded by Iterator::sum (sequential from 0.0, col ascending).  bf16 widens exactly
+ * (the top 16 bits of the f32 it denotes, matmul.rs:133-139).  kind 0 = f16, 1 = bf16. */
+ORC_API int orc_gemv16(const uint8_t *w, size_t w_len, const float *x, size_t x_len, size_t n, size_t k, int kind,
+                       float *out) {
+    if (w_len < n * k * 2 || x_len != k) return 1;
+    for (size_t r = 0; r < n; r++) {
+        float acc = 0.0f;
+        for (size_t c = 0; c < k; c++) {
+            const uint8_t *p = w + (r * k + c) * 2;
+            uint16_t bits = (uint16_t)(p[0] | (p[1] << 8));
+            float wv;
+            if (kind == 0) wv = orc_f16_to_f32(bits);
+            else {
+                uint32_t u = (uint32_t)bits << 16;
+                memcpy(&wv, &u, 4);
+            }
+            acc += wv * x[c];
+        }
+        out[r] = acc;
+    }
+    return 0;
+}
+
+/* Top-k by value, descending, ties to the lower index: the order q4k_matvec_topk / f16_gemv_topk return
+ * (crates/larql-compute/src/backend/quant_matvec.rs:268-277: "sorted descending"; the caller's fallback is
+ * the full matvec + a CPU reduce).  Returns the count, or -1 on NaN. */
+ORC_API long orc_top_k_by_value(const float *v, size_t n, size_t top_k, uint32_t *idx_out, float *val_out) {
+    size_t k = top_k < n ? top_k : n;
+    for (size_t i = 0; i < n; i++)
+        if (v[i] != v[i]) return -1;
+    /* selection by repeated maximum over the remaining entries is O(n k); n k stays small in the tests */
+    uint8_t *taken = (uint8_t *)calloc(n ? n : 1, 1);
+    if (!taken) return -2;
+    for (size_t j = 0; j < k; j++) {
+        size_t best = n;
+        for (size_t i = 0; i < n; i++) {
+            if (taken[i]) continue;
+            if (best == n || v[i] > v[best]) best = i;
+        }
+        taken[best] = 1;
+        idx_out[j] = (uint32_t)best;
+        val_out[j] = v[best];
+    }
+    free(taken);
+    return (long)k;
+}
+
 /* ------------------------------------------------------------ NVFP4 ----- */
 
 /* crates/larql-models/src/quant/nvfp4.rs:111-117 (tensor_scale_for). */

@@ -193,3 +193,77 @@ def test_moe_expert_walk_gpt_oss_shape(be):
             o, _, _ = oracle.walk_token(*experts[int(e)], xs[t], K)
             want += np.float32(we) * o
         assert rel_l2(got[t], want) < OUT_TOL
+
+
+# ---------------------------------------------------- device seam: multi gemv, f16 / bf16, top-k by value
+def test_gemv_multi_matches_single_gemvs(be):
+    """mxfp4_gemv_multi / nvfp4_gemv_multi (backend/matmul.rs:242-286): the results of the single gemvs."""
+    k = 2880
+    x = oracle.rms_norm(seeded_x(0x301, k))
+    alive = []  # weights are cached on the device by host address: keep every matrix of this test alive
+    for fmt in (oracle.FMT_MXFP4, oracle.FMT_NVFP4, oracle.FMT_Q8_0, oracle.FMT_Q4_K):
+        kk = k if fmt != oracle.FMT_Q4_K else 2816
+        xx = np.ascontiguousarray(x[:kk])
+        mats = [oracle.quantize_matrix(fmt, seeded_weights(0x310 + i, n, kk)) for i, n in enumerate((96, 257, 33))]
+        alive.append(mats)
+        for exact in (True, False):
+            outs = be.gemv_multi([host(m) for m in mats], xx, exact=exact)
+            assert outs is not None and len(outs) == 3
+            for m, o in zip(mats, outs):
+                single = be.gemv(host(m), xx, exact=exact)
+                assert np.array_equal(bits(o), bits(single))
+                if exact:
+                    assert np.array_equal(bits(o), bits(m.gemv(xx)))
+    # a matrix whose k differs from the input's length: refusal, not a wrong answer
+    bad = oracle.quantize_matrix(oracle.FMT_MXFP4, seeded_weights(1, 8, 64))
+    assert be.gemv_multi([host(bad)], x) is None
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+def test_f16_bf16_gemv_exact_order_and_fast(be, kind):
+    """f16_gemv / bf16_gemv (backend/matmul.rs:124-147) against the reference test device's loop."""
+    rng = np.random.Generator(np.random.PCG64(0x16))
+    for n, k in ((37, 64), (300, 1000), (129, 4097)):
+        w = (rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.05))
+        if kind == "f16":
+            wb = w.astype(np.float16).view(np.uint16)
+        else:
+            wb = (w.view(np.uint32) >> 16).astype(np.uint16)
+        x = rng.standard_normal(k, dtype=np.float32)
+        want = oracle.gemv16(wb, x, n, k, 0 if kind == "f16" else 1)
+        got = be.gemv16(wb, x, n, k, kind, exact=True)
+        assert np.array_equal(bits(got), bits(want))
+        fast = be.gemv16(wb, x, n, k, kind, exact=False)
+        assert rel_l2(fast, want) < 1e-5
+        outs = be.gemv16_multi([(wb, n, k), (wb[: n // 2], n // 2, k)], x, kind, exact=True)
+        assert np.array_equal(bits(outs[0]), bits(want)) and np.array_equal(bits(outs[1]), bits(want[: n // 2]))
+    # shape refusals: short weights, wrong input length
+    assert be.gemv16(np.zeros(10, np.uint16), np.zeros(4, np.float32), 3, 4, kind) is None
+    assert be.gemv16(np.zeros(12, np.uint16), np.zeros(5, np.float32), 3, 4, kind) is None
+
+
+def test_q4k_matvec_topk_by_value(be):
+    """q4k_matvec_topk (backend/quant_matvec.rs:268-277): the rows a full q4k_matvec + CPU reduce picks."""
+    n, h = 5000, 1024
+    m = oracle.quantize_matrix(oracle.FMT_Q4_K, seeded_weights(0x7061, n, h))
+    x = oracle.rms_norm(seeded_x(0x7062, h))
+    scores = oracle.q4k_matvec(m.data, x, n, h)
+    for k in (1, 8, 100, 5000, 9000):
+        got = be.q4k_matvec_topk(m.data, x, n, h, k)
+        idx, val = oracle.top_k_by_value(scores, k)
+        assert [r for r, _ in got] == idx.tolist()
+        assert np.array_equal(bits(np.array([v for _, v in got], np.float32)), bits(val))
+    # ties resolve to the lower row: duplicate one row many times
+    d = np.asarray(m.data).reshape(n, -1).copy()
+    best = int(oracle.top_k_by_value(scores, 1)[0][0])
+    d[100:140] = d[best]
+    s2 = oracle.q4k_matvec(d.reshape(-1), x, n, h)
+    got = be.q4k_matvec_topk(d.reshape(-1), x, n, h, 7)
+    assert [r for r, _ in got] == oracle.top_k_by_value(s2, 7)[0].tolist()
+    # f16 LM-head form
+    rng = np.random.Generator(np.random.PCG64(0x7063))
+    wf = (rng.standard_normal((3000, 512), dtype=np.float32) * np.float32(0.05)).astype(np.float16).view(np.uint16)
+    xs = rng.standard_normal(512, dtype=np.float32)
+    sf = oracle.gemv16(wf, xs, 3000, 512, 0)
+    gotf = be.f16_gemv_topk(wf, xs, 3000, 512, 16)
+    assert [r for r, _ in gotf] == oracle.top_k_by_value(sf, 16)[0].tolist()
