@@ -97,7 +97,8 @@ LQ_API int lq_supports_quant(lq_ctx* ctx, int fmt);
 LQ_API int lq_synchronize(lq_ctx* ctx);
 /* The context's cudaStream_t (for callers that enqueue their own work around lq_dev_* calls). */
 LQ_API void* lq_stream(lq_ctx* ctx);
-/* MatMul::submission_clock (backend/matmul.rs:25-42,209-218): kernel launches issued by this context. */
+/* MatMul::submission_clock (backend/matmul.rs:209-218; the SubmissionClock it returns: 25-42): kernel launches
+ * issued by this context. */
 LQ_API uint64_t lq_launch_count(lq_ctx* ctx);
 
 /* ---- weight residency ---------------------------------------------------------- */
