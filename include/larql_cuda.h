@@ -279,6 +279,23 @@ LQ_API int lq_dev_shard_gather(lq_ctx* ctx, const lq_matrix* up_shard, const lq_
                                const int32_t* packs, int world, int rank, size_t cap, size_t top_k,
                                size_t row_offset, float* out_partial);
 
+/* The same protocol run by the library itself: one NCCL communicator per context, the three exchanges
+ * enqueued on the context's stream between the device steps (no host round trip per layer).
+ *   lq_comm_unique_id   rank 0 makes the 128-byte id and hands it to the other ranks by any channel
+ *   lq_comm_init        every rank, collectively (ncclCommInitRank); one rank = one context = one GPU
+ *   lq_stack_create_sharded   this rank's row range [row_offset, row_offset + rows) of every layer's gate / up /
+ *                       feature-major down, the GLOBAL top_k and feature count; cap = band rows a rank can publish
+ *                       per token (a band that does not fit fails the token on every rank: LQ_ERR_CUDA)
+ * lq_stack_run / lq_stack_run_host then run h <- h + walk_l(rmsnorm(h)) over all layers on every rank; all ranks
+ * call them in the same order and receive the same h.  libnccl.so.2 is loaded on the first of these calls. */
+LQ_API int lq_comm_unique_id(void* id_out, size_t cap);
+LQ_API int lq_comm_init(lq_ctx* ctx, int rank, int world, const void* unique_id, size_t id_len);
+LQ_API int lq_comm_destroy(lq_ctx* ctx);
+LQ_API int lq_stack_create_sharded(lq_ctx* ctx, const lq_matrix* gate_shards, const lq_matrix* up_shards,
+                                   const lq_matrix* down_shards_fm, size_t n_layers, size_t batch, size_t top_k,
+                                   size_t n_features_global, size_t row_offset, uint32_t flags, size_t cap,
+                                   lq_stack** out);
+
 /* The rows this rank selected in its last lq_dev_shard_gather, LOCAL to its shard (add the shard's row
  * offset for global rows), unordered; *count is their number, at most cap of them are copied to the host. */
 LQ_API int lq_dev_shard_hits(lq_ctx* ctx, uint32_t* idx_out_host, size_t cap, size_t* count);

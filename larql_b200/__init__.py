@@ -39,7 +39,8 @@ EXPORTS = [
     "lq_dev_shard_gather", "lq_gemv", "lq_q8_0_gemv", "lq_mxfp4_gemv", "lq_nvfp4_gemv", "lq_moe_route",
     "lq_moe_walk_ffn", "lq_stack_run_host", "lq_dev_shard_hits", "lq_gemv_multi", "lq_mxfp4_gemv_multi",
     "lq_nvfp4_gemv_multi", "lq_gemv16", "lq_gemv16_multi", "lq_f16_gemv", "lq_bf16_gemv", "lq_q4k_matvec_topk",
-    "lq_gemv16_topk", "lq_f16_gemv_topk",
+    "lq_gemv16_topk", "lq_f16_gemv_topk", "lq_comm_unique_id", "lq_comm_init", "lq_comm_destroy",
+    "lq_stack_create_sharded",
 ]
 
 
@@ -112,6 +113,10 @@ def load_library() -> C.CDLL:
         "lq_moe_walk_ffn": (C.c_int, [vp, mp, mp, mp, sz, f32p, f32p, sz, sz, C.c_int, sz, C.c_uint32, f32p, u32p,
                                       f32p]),
         "lq_q4k_matvec_static": (C.c_int, [vp, sz, f32p, sz, sz, f32p, vp, C.c_char_p, sz]),
+        "lq_comm_unique_id": (C.c_int, [vp, sz]),
+        "lq_comm_init": (C.c_int, [vp, C.c_int, C.c_int, vp, sz]),
+        "lq_comm_destroy": (C.c_int, [vp]),
+        "lq_stack_create_sharded": (C.c_int, [vp, mp, mp, mp, sz, sz, sz, sz, sz, C.c_uint32, sz, C.POINTER(vp)]),
         "lq_gemv_multi": (C.c_int, [vp, vp, sz, f32p, sz, vp, C.c_int]),
         "lq_mxfp4_gemv_multi": (C.c_int, [vp, vp, sz, f32p, sz, vp]),
         "lq_nvfp4_gemv_multi": (C.c_int, [vp, vp, sz, f32p, sz, vp]),
@@ -495,6 +500,35 @@ class CudaBackend:
         u, d = up.c(), down.c()
         return self._status(self._lib.lq_dev_shard_gather(self._h, C.byref(u), C.byref(d), packs_ptr, world, rank,
                                                           int(cap), int(top_k), int(row_offset), out_ptr))
+
+    # -- multi-GPU: one NCCL communicator per context, feature-sharded stacks ---------------
+    @staticmethod
+    def comm_unique_id() -> bytes:
+        """The 128-byte NCCL id rank 0 makes and hands to the other ranks (any channel)."""
+        buf = C.create_string_buffer(128)
+        rc = load_library().lq_comm_unique_id(buf, 128)
+        if rc != 0:
+            raise BackendError(f"lq_comm_unique_id failed ({rc}): libnccl.so.2 not loadable?")
+        return buf.raw
+
+    def comm_init(self, rank: int, world: int, unique_id: bytes):
+        buf = C.create_string_buffer(unique_id, len(unique_id))
+        return self._status(self._lib.lq_comm_init(self._h, rank, world, buf, len(unique_id)))
+
+    def comm_destroy(self):
+        return self._status(self._lib.lq_comm_destroy(self._h))
+
+    def stack_create_sharded(self, gates, ups, downs, batch: int, top_k: int, n_features_global: int, row_offset: int,
+                             cap: int, flags: int = 0):
+        """This rank's row range of every layer; run with stack_run / stack_run_host on every rank alike."""
+        n = len(gates)
+        arr = (LqMatrix * n)
+        ga, ua, da = arr(*[m.c() for m in gates]), arr(*[m.c() for m in ups]), arr(*[m.c() for m in downs])
+        h = C.c_void_p()
+        ok = self._status(self._lib.lq_stack_create_sharded(self._h, ga, ua, da, n, batch, int(top_k),
+                                                            int(n_features_global), int(row_offset), flags, int(cap),
+                                                            C.byref(h)))
+        return h if ok else None
 
     def stack_create(self, gates, ups, downs, batch: int, top_k: int, flags: int = 0):
         n = len(gates)

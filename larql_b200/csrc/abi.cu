@@ -3,6 +3,8 @@
 // in the kernels.  There is deliberately no CPU path here: a missing device is an
 // error, an unsupported case is a refusal status.
 #include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>  // types and prototypes only: the library itself is loaded on demand (lq_comm_init)
 
 #include <cmath>
 #include <cstdio>
@@ -43,6 +45,13 @@ struct lq_stack {
     cudaGraphExec_t exec = nullptr;
     void* layers_dev = nullptr;  // fused path: n_layers x {gate, up, down}
     bool fused = false;
+    // feature-sharded stack (one rank's row range of every layer)
+    bool sharded = false;
+    size_t row_offset = 0, cap = 0;
+    uint32_t* hist_buf = nullptr;   // [LQ_HIST_WORDS]
+    int32_t* pack = nullptr;        // [2 + 2 cap]
+    int32_t* packs = nullptr;       // [world][2 + 2 cap]
+    float* out_partial = nullptr;   // [hidden]
 };
 
 struct lq_ctx {
@@ -81,6 +90,9 @@ struct lq_ctx {
     lq_walk_stats* stats_dev = nullptr;
     bool use_fused = true;
     bool last_fused = false;
+    // multi-GPU: one NCCL communicator per context (lq_comm_init)
+    ncclComm_t comm = nullptr;
+    int rank = 0, world = 1;
 };
 
 namespace {
@@ -100,6 +112,44 @@ struct DevGuard {
     DevGuard(const DevGuard&) = delete;
     DevGuard& operator=(const DevGuard&) = delete;
 };
+
+// NCCL is loaded when the first communicator is made, so the library has no link-time dependency on it
+// (a single-GPU host needs none).
+struct NcclApi {
+    void* lib = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+};
+NcclApi* nccl_api() {
+    static NcclApi api;
+    static bool tried = false;
+    if (tried) return api.lib ? &api : nullptr;
+    tried = true;
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return nullptr;
+#define LQ_SYM(field, name)                                             \
+    api.field = reinterpret_cast<decltype(api.field)>(dlsym(h, name)); \
+    if (!api.field) return nullptr;
+    LQ_SYM(GetUniqueId, "ncclGetUniqueId")
+    LQ_SYM(CommInitRank, "ncclCommInitRank")
+    LQ_SYM(CommDestroy, "ncclCommDestroy")
+    LQ_SYM(AllReduce, "ncclAllReduce")
+    LQ_SYM(AllGather, "ncclAllGather")
+    LQ_SYM(GetErrorString, "ncclGetErrorString")
+#undef LQ_SYM
+    api.lib = h;
+    return &api;
+}
+
+__global__ void add_vec_kernel(float* __restrict__ out, const float* __restrict__ a, const float* __restrict__ b, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = a[i] + b[i];
+}
 
 int fail(lq_ctx* c, int code, const std::string& msg) {
     if (c) c->last_error = msg;
@@ -565,6 +615,10 @@ void lq_destroy(lq_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    if (ctx->comm) {
+        if (NcclApi* nc = nccl_api()) nc->CommDestroy(ctx->comm);
+        ctx->comm = nullptr;
+    }
     for (auto& r : ctx->regions) cudaFree(r.dev);
     cudaFree(ctx->ws_raw);
     cudaFree(ctx->fws);
@@ -1424,8 +1478,55 @@ int lq_dev_shard_hits(lq_ctx* ctx, uint32_t* idx_out_host, size_t cap, size_t* c
 }
 
 // ----------------------------------------------------------------- layer stack ----
+// One token of a feature-sharded stack: per layer three device steps with an NCCL exchange after each
+// (histogram + bound slots, band packs, partial outputs), all enqueued on the context's stream.
+static int sharded_enqueue_token(lq_ctx* ctx, lq_stack* s, const float* h_in, float* h_out) {
+    NcclApi* nc = nccl_api();
+    if (!nc || !ctx->comm) return fail(ctx, LQ_ERR_ARGUMENT, "sharded stack: lq_comm_init first");
+    const size_t L = s->gates.size();
+    const int H = s->hidden;
+    const size_t stride = 2 + 2 * s->cap;
+    const uint32_t flags = s->flags;
+    const float* cur = h_in;
+#define NCK(call)                                                                                   \
+    do {                                                                                            \
+        ncclResult_t r__ = (call);                                                                  \
+        if (r__ != ncclSuccess) return fail(ctx, LQ_ERR_CUDA, std::string(#call) + ": " + nc->GetErrorString(r__)); \
+    } while (0)
+    for (size_t l = 0; l < L; ++l) {
+        float* nxt = (l + 1 == L) ? h_out : s->h_buf[l & 1];
+        int rc = lq_dev_shard_scan(ctx, &s->gates[l], cur, flags & LQ_WALK_RMSNORM, ctx->rank, ctx->world, s->hist_buf);
+        if (rc) return rc;
+        NCK(nc->AllReduce(s->hist_buf, s->hist_buf, LQ_HIST_WORDS, ncclUint32, ncclSum, ctx->comm, ctx->stream));
+        rc = lq_dev_shard_classify(ctx, &s->gates[l], s->hist_buf, ctx->world, s->top_k, s->row_offset, s->pack, s->cap);
+        if (rc) return rc;
+        NCK(nc->AllGather(s->pack, s->packs, stride, ncclInt32, ctx->comm, ctx->stream));
+        rc = lq_dev_shard_gather(ctx, &s->ups[l], &s->downs[l], s->packs, ctx->world, ctx->rank, s->cap, s->top_k,
+                                 s->row_offset, s->out_partial);
+        if (rc) return rc;
+        NCK(nc->AllReduce(s->out_partial, s->out_partial, (size_t)H, ncclFloat, ncclSum, ctx->comm, ctx->stream));
+        if (flags & LQ_WALK_RESIDUAL) {
+            add_vec_kernel<<<(H + 255) / 256, 256, 0, ctx->stream>>>(nxt, cur, s->out_partial, H);
+            CK(cudaGetLastError());
+        } else {
+            CK(cudaMemcpyAsync(nxt, s->out_partial, (size_t)H * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+        }
+        ctx->launches += 4;
+        cur = nxt;
+    }
+#undef NCK
+    return LQ_OK;
+}
+
 static int stack_enqueue(lq_ctx* ctx, lq_stack* s) {
     const size_t L = s->gates.size();
+    if (s->sharded) {
+        for (size_t t = 0; t < s->batch; ++t) {
+            int rc = sharded_enqueue_token(ctx, s, s->h_in + t * s->hidden, s->h_out + t * s->hidden);
+            if (rc) return rc;
+        }
+        return LQ_OK;
+    }
     if (s->fused) {
         const int N = (int)s->gates[0].rows, H = s->hidden;
         const size_t k = effective_k(s->top_k, (size_t)N, s->flags);
@@ -1546,10 +1647,10 @@ int lq_stack_create(lq_ctx* ctx, const lq_matrix* gates, const lq_matrix* ups, c
 
 int lq_stack_run(lq_ctx* ctx, lq_stack* s, const float* h_in, float* h_out) {
     DevGuard dev_guard(ctx);
-    if (!ctx || !s || (!s->exec && !s->fused)) return LQ_ERR_ARGUMENT;
+    if (!ctx || !s || (!s->exec && !s->fused && !s->sharded)) return LQ_ERR_ARGUMENT;
     const size_t bytes = s->batch * s->hidden * 4;
     CK(cudaMemcpyAsync(s->h_in, h_in, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
-    if (s->fused) {
+    if (s->fused || s->sharded) {
         int rc = stack_enqueue(ctx, s);
         if (rc) return rc;
     } else
@@ -1560,16 +1661,119 @@ int lq_stack_run(lq_ctx* ctx, lq_stack* s, const float* h_in, float* h_out) {
 
 int lq_stack_run_host(lq_ctx* ctx, lq_stack* s, const float* h_in_host, float* h_out_host) {
     DevGuard dev_guard(ctx);
-    if (!ctx || !s || (!s->exec && !s->fused) || !h_in_host || !h_out_host) return LQ_ERR_ARGUMENT;
+    if (!ctx || !s || (!s->exec && !s->fused && !s->sharded) || !h_in_host || !h_out_host) return LQ_ERR_ARGUMENT;
     const size_t bytes = s->batch * s->hidden * 4;
     CK(cudaMemcpyAsync(s->h_in, h_in_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
-    if (s->fused) {
+    if (s->fused || s->sharded) {
         int rc = stack_enqueue(ctx, s);
         if (rc) return rc;
     } else
         CK(cudaGraphLaunch(s->exec, ctx->stream));
     CK(cudaMemcpyAsync(h_out_host, s->h_out, bytes, cudaMemcpyDeviceToHost, ctx->stream));
     return lq_synchronize(ctx);
+}
+
+// ------------------------------------------------------------- multi-GPU (NCCL) ----
+int lq_comm_unique_id(void* id_out, size_t cap) {
+    if (!id_out || cap < sizeof(ncclUniqueId)) return LQ_ERR_ARGUMENT;
+    NcclApi* nc = nccl_api();
+    if (!nc) return LQ_REFUSED_UNSUPPORTED;
+    ncclUniqueId id;
+    if (nc->GetUniqueId(&id) != ncclSuccess) return LQ_ERR_CUDA;
+    memcpy(id_out, &id, sizeof id);
+    return LQ_OK;
+}
+
+int lq_comm_init(lq_ctx* ctx, int rank, int world, const void* unique_id, size_t id_len) {
+    DevGuard dev_guard(ctx);
+    if (!ctx || !unique_id || id_len < sizeof(ncclUniqueId) || world < 1 || world > 16 || rank < 0 || rank >= world)
+        return LQ_ERR_ARGUMENT;
+    if (ctx->comm) return fail(ctx, LQ_ERR_ARGUMENT, "comm_init: this context already has a communicator");
+    NcclApi* nc = nccl_api();
+    if (!nc) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "comm_init: libnccl.so.2 could not be loaded");
+    ncclUniqueId id;
+    memcpy(&id, unique_id, sizeof id);
+    ncclResult_t r = nc->CommInitRank(&ctx->comm, world, id, rank);
+    if (r != ncclSuccess) {
+        ctx->comm = nullptr;
+        return fail(ctx, LQ_ERR_CUDA, std::string("ncclCommInitRank: ") + nc->GetErrorString(r));
+    }
+    ctx->rank = rank;
+    ctx->world = world;
+    return LQ_OK;
+}
+
+int lq_comm_destroy(lq_ctx* ctx) {
+    DevGuard dev_guard(ctx);
+    if (!ctx) return LQ_ERR_ARGUMENT;
+    if (ctx->comm) {
+        cudaStreamSynchronize(ctx->stream);
+        if (NcclApi* nc = nccl_api()) nc->CommDestroy(ctx->comm);
+        ctx->comm = nullptr;
+    }
+    ctx->rank = 0;
+    ctx->world = 1;
+    return LQ_OK;
+}
+
+int lq_stack_create_sharded(lq_ctx* ctx, const lq_matrix* gate_shards, const lq_matrix* up_shards,
+                            const lq_matrix* down_shards_fm, size_t n_layers, size_t batch, size_t top_k,
+                            size_t n_features_global, size_t row_offset, uint32_t flags, size_t cap, lq_stack** out) {
+    DevGuard dev_guard(ctx);
+    if (!ctx || !out || !n_layers || !batch || !cap) return LQ_ERR_ARGUMENT;
+    *out = nullptr;
+    if (!ctx->comm) return fail(ctx, LQ_ERR_ARGUMENT, "sharded stack: lq_comm_init first");
+    if (top_k == 0 || top_k >= n_features_global)
+        return fail(ctx, LQ_REFUSED_UNSUPPORTED, "sharded stack: 0 < top_k < global feature count");
+    int rc;
+    lq_stack* s = new lq_stack();
+    s->gates.resize(n_layers);
+    s->ups.resize(n_layers);
+    s->downs.resize(n_layers);
+    for (size_t l = 0; l < n_layers; ++l) {
+        if ((rc = shard_check(ctx, &gate_shards[l], "gate shard")) || (rc = shard_check(ctx, &up_shards[l], "up shard")) ||
+            (rc = shard_check(ctx, &down_shards_fm[l], "down shard")) ||
+            (rc = resolve_matrix(ctx, &gate_shards[l], &s->gates[l])) || (rc = resolve_matrix(ctx, &up_shards[l], &s->ups[l])) ||
+            (rc = resolve_matrix(ctx, &down_shards_fm[l], &s->downs[l]))) {
+            delete s;
+            return rc;
+        }
+        if (gate_shards[l].cols != gate_shards[0].cols || row_offset + (size_t)gate_shards[l].rows > n_features_global) {
+            delete s;
+            return fail(ctx, LQ_REFUSED_SHAPE, "sharded stack: shard geometry");
+        }
+    }
+    s->sharded = true;
+    s->batch = batch;
+    s->top_k = top_k;
+    s->flags = flags | LQ_WALK_RMSNORM | LQ_WALK_RESIDUAL;
+    s->hidden = (int)gate_shards[0].cols;
+    s->row_offset = row_offset;
+    s->cap = cap;
+    const size_t H = (size_t)s->hidden, stride = 2 + 2 * cap;
+    const size_t hb = a256(batch * H * 4);
+    cudaError_t e = cudaMalloc(&s->h_in, 4 * hb);
+    uint8_t* raw = nullptr;
+    const size_t aux = a256(LQ_HIST_WORDS * 4) + a256(stride * 4) + a256((size_t)ctx->world * stride * 4) + a256(H * 4);
+    if (e == cudaSuccess) e = cudaMalloc(&raw, aux);
+    if (e == cudaSuccess) e = cudaMemset(raw, 0, aux);
+    if (e != cudaSuccess) {
+        if (s->h_in) cudaFree(s->h_in);
+        if (raw) cudaFree(raw);
+        s->h_in = nullptr;
+        delete s;
+        return cuda_fail(ctx, e, "sharded stack buffers");
+    }
+    uint8_t* hraw = (uint8_t*)s->h_in;
+    s->h_out = (float*)(hraw + hb);
+    s->h_buf[0] = (float*)(hraw + 2 * hb);
+    s->h_buf[1] = (float*)(hraw + 3 * hb);
+    s->hist_buf = (uint32_t*)raw;
+    s->pack = (int32_t*)(raw + a256(LQ_HIST_WORDS * 4));
+    s->packs = (int32_t*)((uint8_t*)s->pack + a256(stride * 4));
+    s->out_partial = (float*)((uint8_t*)s->packs + a256((size_t)ctx->world * stride * 4));
+    *out = s;
+    return LQ_OK;
 }
 
 void lq_stack_destroy(lq_ctx* ctx, lq_stack* s) {
@@ -1580,6 +1784,7 @@ void lq_stack_destroy(lq_ctx* ctx, lq_stack* s) {
     if (s->graph) cudaGraphDestroy(s->graph);
     if (s->h_in) cudaFree(s->h_in);
     if (s->layers_dev) cudaFree(s->layers_dev);
+    if (s->hist_buf) cudaFree(s->hist_buf);
     delete s;
 }
 

@@ -31,13 +31,16 @@ __global__ void shard_bound_max_kernel(const uint32_t* slots, int world, uint32_
 __global__ void shard_pack_kernel(TokenWs ws, uint32_t row_offset, int cap, int32_t* pack, int* err) {
     const int n_in = ws.sel->n_in;
     int n_band = ws.sel->n_band;
-    if (n_band > cap) {
+    const bool overflow = n_band > cap;
+    if (overflow) {
+        // more band rows than a pack holds: published as n_band = -1, so that every rank sees it after
+        // the all-gather and fails the token (a truncated band would give a silently wrong top-K)
         if (threadIdx.x == 0 && blockIdx.x == 0) set_err(err, DEV_ERR_INTERNAL);
-        n_band = cap;
+        n_band = 0;
     }
     if (blockIdx.x == 0 && threadIdx.x == 0) {
         pack[0] = n_in;
-        pack[1] = n_band;
+        pack[1] = overflow ? -1 : n_band;
     }
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_band; i += gridDim.x * blockDim.x) {
         pack[2 + i] = (int32_t)(ws.band_idx[i] + row_offset);
@@ -62,7 +65,9 @@ __global__ void __launch_bounds__(PICK_T) shard_pick_kernel(const int32_t* __res
         int off = 0, nin = 0;
         for (int r = 0; r < world; ++r) {
             s_off[r] = off;
-            off += min(packs[(size_t)r * stride + 1], cap);
+            const int nb = packs[(size_t)r * stride + 1];
+            if (nb < 0) set_err(err, DEV_ERR_INTERNAL);  // that rank's band did not fit its pack
+            off += max(0, min(nb, cap));
             nin += packs[(size_t)r * stride];
         }
         s_off[world] = off;
