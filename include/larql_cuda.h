@@ -287,7 +287,15 @@ LQ_API int lq_dev_shard_gather(lq_ctx* ctx, const lq_matrix* up_shard, const lq_
  *                       feature-major down, the GLOBAL top_k and feature count; cap = band rows a rank can publish
  *                       per token (a band that does not fit fails the token on every rank: LQ_ERR_CUDA)
  * lq_stack_run / lq_stack_run_host then run h <- h + walk_l(rmsnorm(h)) over all layers on every rank; all ranks
- * call them in the same order and receive the same h.  libnccl.so.2 is loaded on the first of these calls. */
+ * call them in the same order and receive the same h.  libnccl.so.2 is loaded on the first of these calls.
+ *
+ * With one process per GPU, Q4_K layers of one shape and up to 8 ranks, a sharded stack runs on the fused
+ * persistent kernel (LQ_STACK_PATH_SHARDED_FUSED): each rank's kernel walks all layers in one launch and the
+ * ranks exchange histogram, band rows and partial outputs through each other's memory (CUDA IPC mappings,
+ * ordinary peer stores, flag barriers with bounded waits); NCCL then only carries the set-up records and a
+ * one-word rendezvous before each launch.  Otherwise (other formats, ranks that cannot map each other's
+ * memory, LARQL_B200_SHARDED_NCCL set) the three exchanges per layer are NCCL collectives
+ * (LQ_STACK_PATH_SHARDED_NCCL).  All ranks take the same path, and create and destroy a stack together. */
 LQ_API int lq_comm_unique_id(void* id_out, size_t cap);
 LQ_API int lq_comm_init(lq_ctx* ctx, int rank, int world, const void* unique_id, size_t id_len);
 LQ_API int lq_comm_destroy(lq_ctx* ctx);
@@ -296,7 +304,14 @@ LQ_API int lq_stack_create_sharded(lq_ctx* ctx, const lq_matrix* gate_shards, co
                                    size_t n_features_global, size_t row_offset, uint32_t flags, size_t cap,
                                    lq_stack** out);
 
-/* The rows this rank selected in its last lq_dev_shard_gather, LOCAL to its shard (add the shard's row
+/* Which implementation a stack runs on (lq_stack_create picks by shape, format and batch). */
+#define LQ_STACK_PATH_GRAPH 0          /* one CUDA graph of per-layer kernels */
+#define LQ_STACK_PATH_FUSED 1          /* one persistent kernel per token (Q4_K, batch 1) */
+#define LQ_STACK_PATH_SHARDED_NCCL 2   /* per-layer kernels with three NCCL exchanges per layer */
+#define LQ_STACK_PATH_SHARDED_FUSED 3  /* one persistent kernel per token and rank, exchange in peer memory */
+LQ_API int lq_stack_path(const lq_stack* stack);
+
+/* The rows this rank selected in its last lq_dev_shard_gather or in the last layer of its last sharded stack run, LOCAL to its shard (add the shard's row
  * offset for global rows), unordered; *count is their number, at most cap of them are copied to the host. */
 LQ_API int lq_dev_shard_hits(lq_ctx* ctx, uint32_t* idx_out_host, size_t cap, size_t* count);
 

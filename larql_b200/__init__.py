@@ -40,7 +40,7 @@ EXPORTS = [
     "lq_moe_walk_ffn", "lq_stack_run_host", "lq_dev_shard_hits", "lq_gemv_multi", "lq_mxfp4_gemv_multi",
     "lq_nvfp4_gemv_multi", "lq_gemv16", "lq_gemv16_multi", "lq_f16_gemv", "lq_bf16_gemv", "lq_q4k_matvec_topk",
     "lq_gemv16_topk", "lq_f16_gemv_topk", "lq_comm_unique_id", "lq_comm_init", "lq_comm_destroy",
-    "lq_stack_create_sharded",
+    "lq_stack_create_sharded", "lq_stack_path",
 ]
 
 
@@ -98,6 +98,7 @@ def load_library() -> C.CDLL:
         "lq_stack_run_host": (C.c_int, [vp, vp, f32p, f32p]),
         "lq_dev_shard_hits": (C.c_int, [vp, u32p, sz, C.POINTER(sz)]),
         "lq_stack_destroy": (None, [vp, vp]),
+        "lq_stack_path": (C.c_int, [vp]),
         "lq_last_walk_stats": (C.c_int, [vp, C.POINTER(WalkStats)]),
         "lq_dev_quantize_q4k": (C.c_int, [vp, f32p, sz, vp]),
         "lq_profile_walk": (C.c_int, [vp, mp, mp, mp, f32p, sz, C.c_uint32, f32p, f32p]),
@@ -529,6 +530,10 @@ class CudaBackend:
                                                             int(n_features_global), int(row_offset), flags, int(cap),
                                                             C.byref(h)))
         return h if ok else None
+
+    def stack_path(self, stack) -> int:
+        """STACK_PATH_*: which implementation the stack runs on."""
+        return int(self._lib.lq_stack_path(stack))
 
     def stack_create(self, gates, ups, downs, batch: int, top_k: int, flags: int = 0):
         n = len(gates)

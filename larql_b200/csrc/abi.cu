@@ -33,6 +33,14 @@ cudaError_t launch_walk_fused_q4k(const void* layers_dev, const uint8_t* const* 
                                   int hidden, int top_k, uint32_t flags, float c1, const float* h_in, float* h_out,
                                   uint8_t* ws, uint32_t* hit_out, uint32_t* count_out, lq_walk_stats* stats_dev,
                                   int* err, int sm_count, cudaStream_t st);
+size_t fused_q4k_xarea_bytes(int hidden, int n_rows_global, int world);
+bool fused_q4k_sharded_supported(int hidden, int n_rows_local, int n_rows_global, int top_k, int world, int sm_count);
+cudaError_t launch_walk_fused_q4k_sharded(const void* layers_dev, int n_layers, int n_rows_local, int n_rows_global,
+                                          int hidden, int top_k, uint32_t flags, float c1, const float* h_in,
+                                          float* h_out, uint8_t* ws, uint32_t* hit_out, uint32_t* count_out,
+                                          lq_walk_stats* stats_dev, int* err, int sm_count, int world, int rank,
+                                          uint8_t* const* areas, const int* row_offsets, uint32_t xepoch0,
+                                          cudaStream_t st);
 }  // namespace lq
 
 struct lq_stack {
@@ -52,6 +60,15 @@ struct lq_stack {
     int32_t* pack = nullptr;        // [2 + 2 cap]
     int32_t* packs = nullptr;       // [world][2 + 2 cap]
     float* out_partial = nullptr;   // [hidden]
+    // sharded stack on the fused persistent kernel: the ranks exchange through each other's memory
+    bool xfused = false;
+    size_t n_global = 0;
+    uint8_t* xarea = nullptr;             // this rank's exchange area
+    std::vector<uint8_t*> areas;          // every rank's area as mapped here (areas[rank] == xarea)
+    std::vector<int> row_offs;            // first global row of every rank
+    uint32_t xepoch = 0;                  // all-rank barriers passed so far on these areas
+    uint32_t* xhits = nullptr;            // [top_k] rows of the last layer's selection + [1] their count
+    uint32_t* sync_word = nullptr;        // one word for the launch rendezvous
 };
 
 struct lq_ctx {
@@ -93,6 +110,7 @@ struct lq_ctx {
     // multi-GPU: one NCCL communicator per context (lq_comm_init)
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1;
+    const lq_stack* last_xstack = nullptr;  // sharded fused stack that ran last (its selection: lq_dev_shard_hits)
 };
 
 namespace {
@@ -281,7 +299,7 @@ int ensure_fused(lq_ctx* ctx, size_t hidden, size_t feat) {
     ctx->fws_cap = need;
 
     if (!ctx->stats_dev) {
-        CK(cudaMalloc(&ctx->stats_dev, 8192));  // lq_walk_stats, (at +64) clock stamps, (at +1024) per-CTA durations
+        CK(cudaMalloc(&ctx->stats_dev, 8192));  // lq_walk_stats, then (at +64) the clock stamps
         CK(cudaMemsetAsync(ctx->stats_dev, 0, 8192, ctx->stream));
     }
     return LQ_OK;
@@ -1265,37 +1283,10 @@ int lq_fused_phase_us(lq_ctx* ctx, float* us, size_t n) {
     int khz = 0;
     CK(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx->device));
     const double clk_mhz = khz > 0 ? khz * 1e-3 : 1965.0;  // stamps are SM cycles
-    unsigned long long t[25];
+    unsigned long long t[16];
     CK(cudaMemcpy(t, (uint8_t*)ctx->stats_dev + 64, sizeof t, cudaMemcpyDeviceToHost));
     const size_t n_phase = (size_t)fused_q4k_stamp_count() - 1;
     for (size_t i = 0; i < n; ++i) us[i] = i < n_phase ? (float)((double)(t[i + 1] - t[i]) / clk_mhz) : 0.0f;
-    if (getenv("LARQL_B200_FUSED_DEBUG")) {
-        fprintf(stderr, "gather: rows %llu issue %.2f updots %.2f wait %.2f axpy %.2f | prepare: load %.2f rms %.2f quant %.2f us\n",
-                t[18], (double)(t[14] - t[13]) / clk_mhz, (double)(t[15] - t[14]) / clk_mhz,
-                (double)(t[16] - t[15]) / clk_mhz, (double)(t[17] - t[16]) / clk_mhz, (double)(t[19] - t[0]) / clk_mhz,
-                (double)(t[20] - t[19]) / clk_mhz, (double)(t[1] - t[20]) / clk_mhz);
-        if (ctx->fws) {
-            // per-CTA durations of the stamped layer (see the kernel): pick, gather + merge, rows gathered, band rows
-            std::vector<uint32_t> d(148 * 8);
-            if (cudaMemcpy(d.data(), (uint8_t*)ctx->stats_dev + 1024, d.size() * 4, cudaMemcpyDeviceToHost) == cudaSuccess) {
-                const char* nm[6] = {"pick", "gather+merge", "rows", "band rows", "scan", "select"};
-                for (int f = 0; f < 6; ++f) {
-                    double mn = 1e30, mx = 0, av = 0;
-                    int arg = 0;
-                    for (int c = 0; c < ctx->sm_count && c < 148; ++c) {
-                        double v = d[c * 8 + f];
-                        if (f != 2 && f != 3) v /= clk_mhz;
-                        if (v > mx) { mx = v; arg = c; }
-                        mn = std::min(mn, v);
-                        av += v;
-                    }
-                    fprintf(stderr, "  per CTA %-13s min %.2f avg %.2f max %.2f (cta %d)\n", nm[f], mn, av / ctx->sm_count, mx, arg);
-                }
-            }
-        }
-        fprintf(stderr, "scan (thread 0): rows %.2f data wait %.2f team barrier %.2f release %.2f us\n",
-                (double)t[21] / clk_mhz, (double)t[22] / clk_mhz, (double)t[23] / clk_mhz, (double)t[24] / clk_mhz);
-    }
     return LQ_OK;
 }
 
@@ -1465,7 +1456,18 @@ int lq_dev_shard_gather(lq_ctx* ctx, const lq_matrix* up_shard, const lq_matrix*
 
 int lq_dev_shard_hits(lq_ctx* ctx, uint32_t* idx_out_host, size_t cap, size_t* count) {
     DevGuard dev_guard(ctx);
-    if (!ctx || !count || ctx->tok.empty()) return LQ_ERR_ARGUMENT;
+    if (!ctx || !count) return LQ_ERR_ARGUMENT;
+    if (const lq_stack* xs = ctx->last_xstack) {
+        uint32_t n = 0;
+        CK(cudaMemcpyAsync(&n, xs->xhits + xs->top_k, 4, cudaMemcpyDeviceToHost, ctx->stream));
+        CK(cudaStreamSynchronize(ctx->stream));
+        if (n > xs->top_k) return fail(ctx, LQ_ERR_CUDA, "shard_hits: bad count");
+        *count = (size_t)n;
+        const size_t m = std::min((size_t)n, cap);
+        if (m && idx_out_host) CK(cudaMemcpy(idx_out_host, xs->xhits, m * 4, cudaMemcpyDeviceToHost));
+        return LQ_OK;
+    }
+    if (ctx->tok.empty()) return LQ_ERR_ARGUMENT;
     TokenWs w = ctx->tok[0];
     int n = 0;
     CK(cudaMemcpyAsync(&n, &w.sel->n_sel, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
@@ -1520,7 +1522,30 @@ static int sharded_enqueue_token(lq_ctx* ctx, lq_stack* s, const float* h_in, fl
 
 static int stack_enqueue(lq_ctx* ctx, lq_stack* s) {
     const size_t L = s->gates.size();
+    if (s->xfused) {
+        // The ranks' kernels wait for one another: a tiny all-reduce first, so that they start together
+        // (and after every rank's previous launch on these areas has ended).
+        NcclApi* nc = nccl_api();
+        if (!nc || !ctx->comm) return fail(ctx, LQ_ERR_ARGUMENT, "sharded stack: lq_comm_init first");
+        if (ctx->world > 1 &&
+            nc->AllReduce(s->sync_word, s->sync_word, 1, ncclUint32, ncclSum, ctx->comm, ctx->stream) != ncclSuccess)
+            return fail(ctx, LQ_ERR_CUDA, "sharded stack: launch rendezvous failed");
+        const int H = s->hidden, Nl = (int)s->gates[0].rows;
+        for (size_t t = 0; t < s->batch; ++t) {
+            const bool last = t + 1 == s->batch;
+            CK(launch_walk_fused_q4k_sharded(s->layers_dev, (int)L, Nl, (int)s->n_global, H, (int)s->top_k, s->flags,
+                                             bound_c1(H), s->h_in + t * H, s->h_out + t * H, ctx->fws,
+                                             last ? s->xhits : nullptr, last ? s->xhits + s->top_k : nullptr,
+                                             t == 0 ? ctx->stats_dev : nullptr, ctx->d_err, ctx->sm_count, ctx->world,
+                                             ctx->rank, s->areas.data(), s->row_offs.data(), s->xepoch, ctx->stream));
+            s->xepoch += 3u * (uint32_t)L;
+            ctx->launches += 1;
+        }
+        ctx->last_xstack = s;
+        return LQ_OK;
+    }
     if (s->sharded) {
+        ctx->last_xstack = nullptr;
         for (size_t t = 0; t < s->batch; ++t) {
             int rc = sharded_enqueue_token(ctx, s, s->h_in + t * s->hidden, s->h_out + t * s->hidden);
             if (rc) return rc;
@@ -1716,6 +1741,112 @@ int lq_comm_destroy(lq_ctx* ctx) {
     return LQ_OK;
 }
 
+// Puts a sharded stack on the fused persistent kernel when every rank can: Q4_K layers of one shape that the
+// kernel supports, and every rank's exchange area mapped into every other rank's process (CUDA IPC, one
+// process per GPU).  All ranks take the same decision (the conditions are all-reduced), so a stack never
+// runs fused on one rank and through NCCL on another.  Leaves s->xfused false and returns LQ_OK when the
+// fused path is not available; a non-zero status is a failure of the set-up itself.
+static int try_xfused(lq_ctx* ctx, lq_stack* s) {
+    NcclApi* nc = nccl_api();
+    const int world = ctx->world, rank = ctx->rank;
+    const size_t L = s->gates.size();
+    const int H = s->hidden, Nl = (int)s->gates[0].rows;
+    bool ok = ctx->use_fused && world <= 8 && getenv("LARQL_B200_SHARDED_NCCL") == nullptr;
+    for (size_t l = 0; ok && l < L; ++l)
+        ok = s->gates[l].fmt == LQ_FMT_Q4_K && s->ups[l].fmt == LQ_FMT_Q4_K && s->downs[l].fmt == LQ_FMT_Q4_K &&
+             s->gates[l].rows == s->gates[0].rows && s->ups[l].rows == s->gates[0].rows &&
+             s->downs[l].rows == s->gates[0].rows && s->gates[l].cols == s->gates[0].cols;
+    ok = ok && fused_q4k_sharded_supported(H, Nl, (int)s->n_global, (int)s->top_k, world, ctx->sm_count);
+    // scratch for the small exchanges: [0, 1024) send, [1024, ...) receive
+    uint8_t* tmp = nullptr;
+    CK(cudaMalloc(&tmp, 1024 + 1024 * 16));
+    struct Hello {
+        int ok, row_offset, n_rows, pad;
+        cudaIpcMemHandle_t handle;
+    };
+    static_assert(sizeof(Hello) <= 1024, "hello record");
+    Hello mine;
+    memset(&mine, 0, sizeof mine);
+    mine.row_offset = (int)s->row_offset;
+    mine.n_rows = Nl;
+    cudaError_t e = cudaSuccess;
+    if (ok) {
+        const size_t xb = fused_q4k_xarea_bytes(H, (int)s->n_global, world);
+        e = cudaMalloc(&s->xarea, xb);
+        if (e == cudaSuccess) e = cudaMemset(s->xarea, 0, xb);
+        if (e == cudaSuccess && world > 1) e = cudaIpcGetMemHandle(&mine.handle, s->xarea);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            ok = false;
+        }
+    }
+    mine.ok = ok ? 1 : 0;
+    std::vector<Hello> all((size_t)world);
+    auto exchange = [&]() -> int {
+        CK(cudaMemcpyAsync(tmp, &mine, sizeof mine, cudaMemcpyHostToDevice, ctx->stream));
+        if (nc->AllGather(tmp, tmp + 1024, sizeof(Hello), ncclChar, ctx->comm, ctx->stream) != ncclSuccess)
+            return fail(ctx, LQ_ERR_CUDA, "sharded stack: all-gather of the set-up records failed");
+        CK(cudaMemcpyAsync(all.data(), tmp + 1024, sizeof(Hello) * (size_t)world, cudaMemcpyDeviceToHost, ctx->stream));
+        CK(cudaStreamSynchronize(ctx->stream));
+        return LQ_OK;
+    };
+    int rc = exchange();
+    if (!rc) {
+        for (int r = 0; r < world; ++r) ok = ok && all[(size_t)r].ok;
+        s->row_offs.resize((size_t)world);
+        s->areas.assign((size_t)world, nullptr);
+        long long rows = 0;
+        for (int r = 0; r < world; ++r) {
+            s->row_offs[(size_t)r] = all[(size_t)r].row_offset;
+            rows += all[(size_t)r].n_rows;
+        }
+        ok = ok && rows == (long long)s->n_global;  // the ranks' row ranges make up the whole layer
+        if (ok) {
+            s->areas[(size_t)rank] = s->xarea;
+            for (int r = 0; r < world && ok; ++r) {
+                if (r == rank) continue;
+                void* ptr = nullptr;
+                e = cudaIpcOpenMemHandle(&ptr, all[(size_t)r].handle, cudaIpcMemLazyEnablePeerAccess);
+                if (e != cudaSuccess) {
+                    cudaGetLastError();
+                    ok = false;
+                } else
+                    s->areas[(size_t)r] = (uint8_t*)ptr;
+            }
+        }
+        // second round: did every rank map every area?
+        mine.ok = ok ? 1 : 0;
+        rc = exchange();
+        if (!rc)
+            for (int r = 0; r < world; ++r) ok = ok && all[(size_t)r].ok;
+    }
+    cudaFree(tmp);
+    if (rc) return rc;
+    if (!ok) {
+        for (int r = 0; r < world; ++r)
+            if (r != rank && r < (int)s->areas.size() && s->areas[(size_t)r]) cudaIpcCloseMemHandle(s->areas[(size_t)r]);
+        s->areas.clear();
+        if (s->xarea) cudaFree(s->xarea);
+        s->xarea = nullptr;
+        return LQ_OK;
+    }
+    rc = ensure_fused(ctx, (size_t)H, (size_t)Nl);
+    if (rc) return rc;
+    std::vector<const void*> ptrs(3 * L);
+    for (size_t l = 0; l < L; ++l) {
+        ptrs[3 * l] = s->gates[l].data;
+        ptrs[3 * l + 1] = s->ups[l].data;
+        ptrs[3 * l + 2] = s->downs[l].data;
+    }
+    CK(cudaMalloc(&s->layers_dev, ptrs.size() * sizeof(void*)));
+    CK(cudaMemcpy(s->layers_dev, ptrs.data(), ptrs.size() * sizeof(void*), cudaMemcpyHostToDevice));
+    CK(cudaMalloc(&s->xhits, (s->top_k + 2) * 4));
+    CK(cudaMemset(s->xhits, 0, (s->top_k + 2) * 4));
+    s->sync_word = s->xhits + s->top_k + 1;
+    s->xfused = true;
+    return LQ_OK;
+}
+
 int lq_stack_create_sharded(lq_ctx* ctx, const lq_matrix* gate_shards, const lq_matrix* up_shards,
                             const lq_matrix* down_shards_fm, size_t n_layers, size_t batch, size_t top_k,
                             size_t n_features_global, size_t row_offset, uint32_t flags, size_t cap, lq_stack** out) {
@@ -1772,8 +1903,27 @@ int lq_stack_create_sharded(lq_ctx* ctx, const lq_matrix* gate_shards, const lq_
     s->pack = (int32_t*)(raw + a256(LQ_HIST_WORDS * 4));
     s->packs = (int32_t*)((uint8_t*)s->pack + a256(stride * 4));
     s->out_partial = (float*)((uint8_t*)s->packs + a256((size_t)ctx->world * stride * 4));
+    s->n_global = n_features_global;
+    rc = try_xfused(ctx, s);
+    if (!rc && s->xfused) {
+        // one pass on a harmless input: kernel attributes, module load, and a check that the ranks meet
+        cudaMemsetAsync(s->h_in, 0x3f, hb, ctx->stream);
+        rc = stack_enqueue(ctx, s);
+        if (!rc) rc = lq_synchronize(ctx);
+    }
+    if (rc) {
+        lq_stack_destroy(ctx, s);
+        return rc;
+    }
     *out = s;
     return LQ_OK;
+}
+
+int lq_stack_path(const lq_stack* s) {
+    if (!s) return LQ_ERR_ARGUMENT;
+    if (s->xfused) return LQ_STACK_PATH_SHARDED_FUSED;
+    if (s->sharded) return LQ_STACK_PATH_SHARDED_NCCL;
+    return s->fused ? LQ_STACK_PATH_FUSED : LQ_STACK_PATH_GRAPH;
 }
 
 void lq_stack_destroy(lq_ctx* ctx, lq_stack* s) {
@@ -1785,6 +1935,18 @@ void lq_stack_destroy(lq_ctx* ctx, lq_stack* s) {
     if (s->h_in) cudaFree(s->h_in);
     if (s->layers_dev) cudaFree(s->layers_dev);
     if (s->hist_buf) cudaFree(s->hist_buf);
+    if (ctx && ctx->last_xstack == s) ctx->last_xstack = nullptr;
+    for (size_t r = 0; r < s->areas.size(); ++r)
+        if (s->areas[r] && s->areas[r] != s->xarea) cudaIpcCloseMemHandle(s->areas[r]);
+    if (s->xfused && ctx && ctx->comm && ctx->world > 1) {
+        // an area is freed only after every rank has unmapped it: the ranks destroy a stack together
+        if (NcclApi* nc = nccl_api()) {
+            nc->AllReduce(s->sync_word, s->sync_word, 1, ncclUint32, ncclSum, ctx->comm, ctx->stream);
+            cudaStreamSynchronize(ctx->stream);
+        }
+    }
+    if (s->xarea) cudaFree(s->xarea);
+    if (s->xhits) cudaFree(s->xhits);
     delete s;
 }
 

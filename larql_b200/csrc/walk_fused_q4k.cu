@@ -33,6 +33,7 @@
 // identical.  Every wait (mbarrier, grid barrier) is bounded and reports through the error
 // word instead of hanging.
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "../../include/larql_cuda.h"
@@ -44,16 +45,14 @@ namespace lq {
 namespace {
 
 // No separate producer warp: the last warp to release a ring stage refills it.
-// Tuning knobs (compile time).  16 warps at 128 registers per thread beat 12 warps at 168 with two rows
-// in flight per thread: every phase of this kernel is latency bound, so resident warps count most.
+// Tuning knobs (compile time).  16 warps at 128 registers per thread beat 12 warps at 168 registers, and
+// one row per thread and pass beats two interleaved: every phase of this kernel is latency bound, so
+// resident warps count most.
 #ifndef FW_CFG_THREADS
 #define FW_CFG_THREADS 512
 #endif
 #ifndef FW_CFG_UB
 #define FW_CFG_UB 2
-#endif
-#ifndef FW_CFG_ILP2
-#define FW_CFG_ILP2 0
 #endif
 constexpr int FW_CONSUMERS = FW_CFG_THREADS;
 constexpr int FW_THREADS = FW_CONSUMERS;
@@ -66,6 +65,7 @@ constexpr int FW_PICK_CAP = 8192;    // band entries the final pick can stage in
 constexpr int FW_RANK_CAP = 2048;    // up to this many band entries the pick ranks by counting
 constexpr int FW_STAMPS = 13;
 constexpr int FW_UB = FW_CFG_UB;             // up rows a thread fetches per batch in the gather
+constexpr int FW_MAX_WORLD = 8;              // ranks of one feature-sharded walk
 
 struct FusedGeom {
     int nsb, G, TS, P, Wt;      // super-blocks/row, cells/row, team size, teams, warps per team
@@ -81,6 +81,26 @@ struct FusedLayer {
     const uint8_t* gate;
     const uint8_t* up;
     const uint8_t* down;
+};
+
+// Feature-sharded walk over the GPUs of one box: every rank runs this kernel on its own row range and the
+// ranks meet in each other's memory.  area[r] is rank r's exchange area as mapped into this process
+// (area[rank]: this GPU's own), all laid out alike:
+//   flags [world] u32        arrival flag of every rank (values only ever grow, across launches too)
+//   meta  [world] {u32, u32} score bound bits and highest occupied histogram bin of every rank's rows
+//   cnt   [world] {u32, u32} certainly-in rows and band rows of every rank
+//   hist  [world][LQ_HIST_BINS] u32   every rank's histogram
+//   band_row / band_exact [n_rows_global]   band entries, rank r's from entry row_offset(r) on
+//   xsum  [world][hidden] f32          every rank's partial layer output
+// A rank writes its own slot of each array into EVERY rank's area with ordinary peer stores and then
+// raises its flag there (fence.sys, then the store); readers only ever read their own GPU's memory.
+struct FusedPeers {
+    int world, rank, row_offset, n_rows_global;
+    uint32_t xepoch0;  // value of the flags when this launch starts
+    uint32_t off_meta, off_cnt, off_hist, off_band_row, off_band_exact, off_xsum;
+    uint32_t pad;
+    int seg_off[FW_MAX_WORLD];  // row_offset of every rank
+    uint8_t* area[FW_MAX_WORLD];
 };
 
 struct FusedArgs {
@@ -109,10 +129,11 @@ struct FusedArgs {
     lq_walk_stats* stats;  // optional, last layer
     unsigned long long* phase_ns;  // optional [FW_STAMPS]: clock stamps of CTA 0 in the stamped layer
     int* err;
+    FusedPeers px;         // world == 1: unused
 };
 
 enum { CTR_SYNC = 0, CTR_BOUND0 = 1, CTR_BOUND1 = 2, CTR_IN = 3, CTR_BAND = 4, CTR_HITS = 5, CTR_MAXBIN0 = 6,
-       CTR_MAXBIN1 = 7, CTR_SYNCB = 8, CTR_WORDS = 16 };
+       CTR_MAXBIN1 = 7, CTR_WORDS = 16 };
 
 __host__ __device__ inline int fw_align(int v, int a) { return (v + a - 1) / a * a; }
 
@@ -167,19 +188,19 @@ __device__ __forceinline__ unsigned long long gtimer() {
 __device__ __forceinline__ void bar_sync(int id, int count) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
     uint32_t v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 // size a multiple of 16, address 16-byte aligned; this GPU's own memory
 __device__ __forceinline__ void l2_prefetch_bulk(const void* src, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
@@ -317,7 +338,6 @@ struct GatherArgs {
     const uint32_t* xb_s;
     const float* blk_s;
     int nsb, G, TS, P, Wt, row_bytes;
-    unsigned long long* stamp;  // optional extra clock stamps (thread 0 of the stamped CTA and layer)
 };
 
 __device__ __forceinline__ void gather_stage(const GatherArgs& ga, int base, int nn, uint32_t bar_parity, bool& failed) {
@@ -326,14 +346,12 @@ __device__ __forceinline__ void gather_stage(const GatherArgs& ga, int base, int
     const bool in_team = team < ga.P;
     const bool active = in_team && c < ga.G;
     const int s = c >> 2, g = c & 3, nblk = ga.nsb * 8, P = ga.P;
-    if (ga.stamp && tid == 0) ga.stamp[0] = gtimer();
     // 1. down rows -> ring
     if (tid == 0) mbar_expect_tx(ga.bar, (uint32_t)nn * (uint32_t)ga.row_bytes);
     bar_sync(FW_BAR_CONS, FW_CONSUMERS);  // the expectation is armed before any copy can complete
     for (int i = tid; i < nn; i += FW_CONSUMERS)
         tma_bulk_g2s(ga.ring + (size_t)i * ga.row_bytes, ga.down + (size_t)(uint32_t)ga.rows[base + i] * ga.row_bytes,
                      (uint32_t)ga.row_bytes, ga.bar);
-    if (ga.stamp && tid == 0) ga.stamp[1] = gtimer();
     // 2. up dots
     if (in_team) {
         CellX x;
@@ -365,7 +383,6 @@ __device__ __forceinline__ void gather_stage(const GatherArgs& ga, int base, int
             }
         }
     }
-    if (ga.stamp && tid == 0) ga.stamp[2] = gtimer();
     bar_sync(FW_BAR_CONS, FW_CONSUMERS);
     // 3. activations
     for (int i = tid; i < nn; i += FW_CONSUMERS) {
@@ -378,7 +395,6 @@ __device__ __forceinline__ void gather_stage(const GatherArgs& ga, int base, int
     }
     bar_sync(FW_BAR_CONS, FW_CONSUMERS);
     if (!failed && !mbar_wait(ga.bar, bar_parity)) failed = true;
-    if (ga.stamp && tid == 0) ga.stamp[3] = gtimer();
     // 4. down rows
     float acc_lo[32], acc_hi[32];
 #pragma unroll
@@ -415,7 +431,6 @@ __device__ __forceinline__ void gather_stage(const GatherArgs& ga, int base, int
             }
         }
     }
-    if (ga.stamp && tid == 0) ga.stamp[4] = gtimer();
     // 5. every team has finished reading the staged rows: the ring now takes the accumulators
     bar_sync(FW_BAR_CONS, FW_CONSUMERS);
     if (active) {
@@ -481,6 +496,49 @@ __device__ __forceinline__ int row_of_slot(const Ctx& cx, int m) {
     return (cx.first_tile + (m / cx.gm.R) * (int)gridDim.x) * cx.gm.R + (m % cx.gm.R);
 }
 
+// Barrier over the CTAs of ALL ranks of a sharded walk.  Every CTA arrives on its own GPU's counter; the
+// last one to arrive there knows that all of this rank's writes (to every rank's memory) are ordered before
+// its system-scope fence, optionally publishes the rank's selection counts, and raises the rank's flag in
+// every rank's area.  Everybody then waits, on its own GPU's memory only, until every rank's flag is up.
+// Bounded like the grid barrier: about a second per wait, then DEV_ERR_TMA_TIMEOUT and no further waiting.
+template <bool WITH_COUNTS>
+__device__ __forceinline__ void xgrid_sync(const Ctx& cx, uint32_t& epoch, uint32_t& xepoch, bool& failed, int* s_flag) {
+    const FusedArgs& a = cx.a;
+    const FusedPeers& px = a.px;
+    epoch += 1;
+    xepoch += 1;
+    bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+    if (threadIdx.x == 0 && !failed) {
+        __threadfence_system();
+        const uint32_t old = atomicAdd(&a.ctrs[CTR_SYNC], 1u);
+        if (old + 1u == epoch * gridDim.x) {
+            __threadfence();
+            if (WITH_COUNTS) {
+                const uint2 c = make_uint2(__ldcg(&a.ctrs[CTR_IN]), __ldcg(&a.ctrs[CTR_BAND]));
+                for (int p = 0; p < px.world; ++p) reinterpret_cast<uint2*>(px.area[p] + px.off_cnt)[px.rank] = c;
+                __threadfence_system();
+            }
+            for (int p = 0; p < px.world; ++p)
+                st_release_sys_u32(reinterpret_cast<uint32_t*>(px.area[p]) + px.rank, xepoch);
+        }
+        const uint32_t* fl = reinterpret_cast<const uint32_t*>(px.area[px.rank]);
+        const long long t0 = clock64();
+        uint32_t spins = 0;
+        for (int p = 0; p < px.world && !*s_flag; ++p) {
+            while ((int32_t)(ld_acquire_sys_u32(fl + p) - xepoch) < 0) {
+                if (clock64() - t0 > (1ll << 31) || ((++spins & 63u) == 0 && *(volatile int*)a.err != 0)) {
+                    set_err(a.err, DEV_ERR_TMA_TIMEOUT);
+                    *s_flag = 1;
+                    break;
+                }
+            }
+        }
+        __threadfence();
+    }
+    bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+    if (*s_flag) failed = true;
+}
+
 // One thread issues the TMA copy of a gate tile: tile `it` (counted over all layers) goes to stage
 // it % S.  The caller knows that every warp has finished with that stage's previous tile.
 __device__ __forceinline__ void issue_tile(const Smem& sm, const FusedLayer& lyr, int k, uint32_t it) {
@@ -515,7 +573,11 @@ __device__ __forceinline__ void prefetch_next_gate(const Smem& sm, int l) {
 }
 
 // ---- 0. prepare the activation ----------------------------------------------------------------
-__device__ __noinline__ void phase_prepare(int l, const float* h_cur) {
+// X (sharded walk): the residual of layer l > 0 is put together here, identically on every rank, from the
+// previous residual and every rank's partial output of layer l - 1 in rank order; the CTA that owns a
+// column slice keeps it in h_keep for the layer after.
+template <bool X>
+__device__ __noinline__ void phase_prepare(int l, const float* h_cur, float* h_keep) {
     extern __shared__ __align__(128) uint8_t smem[];  // the kernel's dynamic shared memory
     const Smem sm{smem};
     const Ctx& cx = sm.cx();
@@ -530,13 +592,22 @@ __device__ __noinline__ void phase_prepare(int l, const float* h_cur) {
     // pass 1: copy the residual into shared memory, sum of squares in f64
     double sq = 0.0;
     const float4* src = reinterpret_cast<const float4*>(h_cur);
+    const int per = (hidden / 4 + gridDim.x - 1) / gridDim.x, col0 = blockIdx.x * per;
     for (int i = tid; i < hidden / 4; i += FW_CONSUMERS) {
-        const float4 t = __ldcg(src + i);
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!X || l == 0 || (a.flags & LQ_WALK_RESIDUAL)) t = __ldcg(src + i);
+        if (X && l > 0) {
+            const float4* xsum = reinterpret_cast<const float4*>(a.px.area[a.px.rank] + a.px.off_xsum);
+            for (int r = 0; r < a.px.world; ++r) {
+                const float4 v = __ldcg(xsum + (size_t)r * (hidden / 4) + i);
+                t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+            }
+            if (i >= col0 && i < col0 + per) reinterpret_cast<float4*>(h_keep)[i] = t;
+        }
         *reinterpret_cast<float4*>(xs + ((4 * i) >> 6) * 68 + ((4 * i) & 63)) = t;
         sq += (double)t.x * (double)t.x + (double)t.y * (double)t.y;
         sq += (double)t.z * (double)t.z + (double)t.w * (double)t.w;
     }
-    FW_STAMP(19);
     float rms = 1.0f;
     if (a.flags & LQ_WALK_RMSNORM) {
         double* dred = reinterpret_cast<double*>(sm.red());
@@ -549,7 +620,6 @@ __device__ __noinline__ void phase_prepare(int l, const float* h_cur) {
     } else {
         bar_sync(FW_BAR_CONS, FW_CONSUMERS);
     }
-    FW_STAMP(20);
     // pass 2: four threads per 32-element block, 8 elements each.  With x_hat = step * q the
     // fixed-point copy, e = x - x_hat and a block's weights q_w in [0, 15]:
     //   |sum q_w e| = |sum (q_w - 7.5) e + 7.5 sum e| <= 7.5 (sum |e| + |sum e|),
@@ -630,7 +700,7 @@ __device__ __noinline__ void phase_scan(int l) {
     const bool in_team = team < P;
     const bool active = in_team && c < gm.G;
     const int s = c >> 2, g = c & 3;
-    const int my_count = cx.my_count, n_ahead = cx.n_ahead;
+    const int my_count = cx.my_count;
     const uint32_t scan_it = (uint32_t)l * (uint32_t)my_count;
     const FusedLayer ly = layer_of(a, l);
     uint32_t* hist = a.hist + (size_t)(l & 1) * LQ_HIST_BINS;
@@ -640,8 +710,6 @@ __device__ __noinline__ void phase_scan(int l) {
     const uint8_t* ring = sm.ring();
     bool failed = false;
 
-    long long t_issue = 0, t_wait = 0, t_bar = 0, t_rel = 0;
-    const bool timed = a.phase_ns && l == cx.stamp_layer && blockIdx.x == 0 && tid == 0;
     CellX x;
     float bmax = 0.0f;
     uint32_t kmax = 0;
@@ -656,38 +724,14 @@ __device__ __noinline__ void phase_scan(int l) {
     for (int k = 0; k < my_count; ++k) {
         const uint32_t it = scan_it + k;
         const int stg = it % gm.S;
-        const long long c1 = timed ? clock64() : 0;
         if (!failed && !mbar_wait(&full[stg], (it / gm.S) & 1)) failed = true;
-        const long long c2 = timed ? clock64() : 0;
-        t_wait += c2 - c1;
         const int row0 = (cx.first_tile + k * (int)gridDim.x) * R;
         const int rows_here = min(R, a.n_rows - row0);
         const uint8_t* tb = ring + (size_t)stg * gm.tile_bytes + (active ? s : 0) * 144;  // idle lanes stay inside the row
         float* wp = wpart + (size_t)k * R * gm.Wt;  // [row of the tile][warp of the team]
         if (in_team) {
-            // Two rows per pass, reduced together: lanes 0-15 sum row r0 and lanes 16-31 row r1, five shuffles
-            // for the pair instead of ten.  Rows past the end of a ragged last tile are computed on whatever
-            // the stage holds and discarded.
-            int j = 0;
-            for (; FW_CFG_ILP2 && j + 1 < gm.Rt; j += 2) {
-                const int r0 = team + j * P, r1 = r0 + P;
-                const bool ok0 = active && r0 < rows_here, ok1 = active && r1 < rows_here;
-                float b0, b1;
-                float v0 = cell_dot(tb + (size_t)(ok0 ? r0 : 0) * gm.row_bytes, g, x, b0);
-#if !FW_CFG_ILP2
-                asm volatile("" ::: "memory");  // one row after the other: interleaving them costs registers this build lacks
-#endif
-                float v1 = cell_dot(tb + (size_t)(ok1 ? r1 : 0) * gm.row_bytes, g, x, b1);
-                v0 = ok0 ? v0 : 0.0f;
-                v1 = ok1 ? v1 : 0.0f;
-                bmax = fmaxf(bmax, fmaxf(ok0 ? b0 : 0.0f, ok1 ? b1 : 0.0f));
-                const bool upper = (lane & 16) != 0;
-                float v = (upper ? v1 : v0) + __shfl_xor_sync(0xffffffffu, upper ? v0 : v1, 16);
-                for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == 0) wp[r0 * gm.Wt + wt] = v;
-                if (lane == 16) wp[r1 * gm.Wt + wt] = v;
-            }
-            for (; j < gm.Rt; ++j) {
+            // rows past the end of a ragged last tile are computed on whatever the stage holds and discarded
+            for (int j = 0; j < gm.Rt; ++j) {
                 const int r0 = team + j * P;
                 const bool ok0 = active && r0 < rows_here;
                 float b0;
@@ -698,8 +742,6 @@ __device__ __noinline__ void phase_scan(int l) {
                 if (lane == 0) wp[r0 * gm.Wt + wt] = v0;
             }
         }
-        const long long c2b = timed ? clock64() : 0;
-        t_issue += c2b - c2;  // (rows)
         // This warp has read the tile: the reduction above consumed every lane's loads.  The last warp to
         // say so refills the stage with the tile S further on (nobody waits for a stage to drain) and keeps
         // the L2 prefetch running ahead of the ring.
@@ -710,7 +752,6 @@ __device__ __noinline__ void phase_scan(int l) {
             const int t = k + gm.S + a.pf_dist;
             if (a.pf_dist > 0 && t >= covered) prefetch_tiles(sm, ly, t, t + 1);
         }
-        if (timed) t_rel += clock64() - c2b;
     }
     // every warp's partials are in place: scores of this CTA's rows, histogram, largest occupied bin
     bar_sync(FW_BAR_CONS, FW_CONSUMERS);
@@ -727,12 +768,6 @@ __device__ __noinline__ void phase_scan(int l) {
     }
     for (int o = 16; o > 0; o >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
     if (lane == 0 && kmax > 0u) atomicMax(&a.ctrs[CTR_MAXBIN0 + (l & 1)], kmax);
-    if (timed) {
-        a.phase_ns[21] = (unsigned long long)t_issue;
-        a.phase_ns[22] = (unsigned long long)t_wait;
-        a.phase_ns[23] = (unsigned long long)t_bar;
-        a.phase_ns[24] = (unsigned long long)t_rel;
-    }
     if (!a.pf_late) prefetch_next_gate(sm, l);
     // bound: sum over the team's cells of each thread's largest cell bound
     if (in_team) {
@@ -754,7 +789,29 @@ __device__ __noinline__ void phase_scan(int l) {
     if (failed) sm.ctl()[SC_FAILED] = 1;
 }
 
+// ---- 1b. sharded walk: this rank's histogram, bound and highest bin go to every rank -------------
+// After a barrier over this GPU's CTAs the local histogram is complete; every CTA copies a slice of it
+// into slot `rank` of every rank's area (all bins, so nothing stale is ever read).
+__device__ __noinline__ void phase_xhist(int l) {
+    extern __shared__ __align__(128) uint8_t smem[];  // the kernel's dynamic shared memory
+    const Smem sm{smem};
+    const FusedArgs& a = sm.cx().a;
+    const FusedPeers& px = a.px;
+    const int tid = threadIdx.x, par = l & 1;
+    const uint4* hist4 = reinterpret_cast<const uint4*>(a.hist + (size_t)par * LQ_HIST_BINS);
+    constexpr int N4 = LQ_HIST_BINS / 4;
+    const int per = (N4 + gridDim.x - 1) / gridDim.x, c0 = blockIdx.x * per, n = max(0, min(per, N4 - c0));
+    for (int i = tid; i < n * px.world; i += FW_CONSUMERS) {
+        const int p = i / n, j = i - p * n;
+        reinterpret_cast<uint4*>(px.area[p] + px.off_hist)[(size_t)px.rank * N4 + c0 + j] = __ldcg(hist4 + c0 + j);
+    }
+    if (blockIdx.x == 0 && tid < px.world)
+        reinterpret_cast<uint2*>(px.area[tid] + px.off_meta)[px.rank] =
+            make_uint2(__ldcg(&a.ctrs[CTR_BOUND0 + par]), __ldcg(&a.ctrs[CTR_MAXBIN0 + par]));
+}
+
 // ---- 2. threshold bucket, classification, exact re-score and publication of the band ------------
+template <bool X>
 __device__ __noinline__ void phase_select(int l) {
     extern __shared__ __align__(128) uint8_t smem[];  // the kernel's dynamic shared memory
     const Smem sm{smem};
@@ -763,7 +820,7 @@ __device__ __noinline__ void phase_select(int l) {
     const FusedArgs& a = cx.a;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int par = l & 1, R = gm.R;
-    const uint32_t* hist = a.hist + (size_t)par * LQ_HIST_BINS;
+    const uint32_t* hist = a.hist + (size_t)par * LQ_HIST_BINS;  // X: every rank's histogram, one after the other
     int* s_ctl = sm.ctl();
     float* red = sm.red();
     float* my_scores = sm.scores();
@@ -779,15 +836,37 @@ __device__ __noinline__ void phase_select(int l) {
         // Read the histogram from the highest occupied bin downwards, 1024 bins per round
         // (256 threads x 4 bins, thread 0 the highest), until the cumulative count reaches K.
         constexpr int HT = 256;
-        const uint32_t bbits = __ldcg(&a.ctrs[CTR_BOUND0 + par]);
-        const uint32_t maxbin = min(__ldcg(&a.ctrs[CTR_MAXBIN0 + par]), (uint32_t)LQ_HIST_BINS - 1u);
+        uint32_t bbits, maxbin;
+        if (X) {
+            // positive floats order like their bits: the largest bound of any rank, the highest bin of any rank
+            const uint2* meta = reinterpret_cast<const uint2*>(a.px.area[a.px.rank] + a.px.off_meta);
+            bbits = 0u;
+            maxbin = 0u;
+            for (int r = 0; r < a.px.world; ++r) {
+                const uint2 m = __ldcg(meta + r);
+                bbits = max(bbits, m.x);
+                maxbin = max(maxbin, m.y);
+            }
+            hist = reinterpret_cast<const uint32_t*>(a.px.area[a.px.rank] + a.px.off_hist);
+        } else {
+            bbits = __ldcg(&a.ctrs[CTR_BOUND0 + par]);
+            maxbin = __ldcg(&a.ctrs[CTR_MAXBIN0 + par]);
+        }
+        maxbin = min(maxbin, (uint32_t)LQ_HIST_BINS - 1u);
         const uint32_t K = (uint32_t)a.top_k;
         uint32_t* wsum = reinterpret_cast<uint32_t*>(red);
         uint32_t above_total = 0;
         for (int base_end = (int)(maxbin / 4u + 1u) * 4; base_end > 0; base_end -= 4 * HT) {
             const int b0 = base_end - 4 * (tid + 1);
             uint4 t4 = make_uint4(0u, 0u, 0u, 0u);
-            if (tid < HT && b0 >= 0) t4 = __ldcg(reinterpret_cast<const uint4*>(hist + b0));
+            if (tid < HT && b0 >= 0) {
+                t4 = __ldcg(reinterpret_cast<const uint4*>(hist + b0));
+                if (X)
+                    for (int r = 1; r < a.px.world; ++r) {
+                        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(hist + (size_t)r * LQ_HIST_BINS + b0));
+                        t4.x += v.x; t4.y += v.y; t4.z += v.z; t4.w += v.w;
+                    }
+            }
             const uint32_t own = t4.x + t4.y + t4.z + t4.w;
             uint32_t pre = own;  // inclusive prefix in thread order (higher bins first)
             for (int o = 1; o < 32; o <<= 1) {
@@ -869,7 +948,8 @@ __device__ __noinline__ void phase_select(int l) {
             ta += wcnt[w];
             tb2 += wcnt[32 + w];
         }
-        n_fair = max(0, (a.top_k + (int)gridDim.x - 1) / (int)gridDim.x + 1 - tb2);
+        const int n_ctas = (int)gridDim.x * (X ? a.px.world : 1);
+        n_fair = max(0, (a.top_k + n_ctas - 1) / n_ctas + 1 - tb2);
         for (int m0 = beg; m0 < end; m0 += 32) {
             const int m = m0 + lane;
             const int cc = m < end ? cls(m) : 0;
@@ -917,8 +997,18 @@ __device__ __noinline__ void phase_select(int l) {
         for (int i = tid; i < n_band_mine; i += FW_CONSUMERS) {
             const float v = band_ex[i];
             if (v != v) set_err(a.err, DEV_ERR_NAN_SCORE);
-            a.band_row[base + i] = (uint32_t)row_of_slot(cx, band_list[i]);
-            a.band_exact[base + i] = v;
+            if (X) {
+                // global row number; this rank's entries start at entry row_offset of every rank's arrays
+                const uint32_t row = (uint32_t)(row_of_slot(cx, band_list[i]) + a.px.row_offset);
+                const size_t at = (size_t)a.px.row_offset + base + i;
+                for (int p = 0; p < a.px.world; ++p) {
+                    reinterpret_cast<uint32_t*>(a.px.area[p] + a.px.off_band_row)[at] = row;
+                    reinterpret_cast<float*>(a.px.area[p] + a.px.off_band_exact)[at] = v;
+                }
+            } else {
+                a.band_row[base + i] = (uint32_t)row_of_slot(cx, band_list[i]);
+                a.band_exact[base + i] = v;
+            }
         }
     }
     const int n_keep = min(n_in_mine, n_fair), n_over = n_in_mine - n_keep;
@@ -938,6 +1028,7 @@ __device__ __noinline__ void phase_select(int l) {
 }
 
 // ---- 3. final pick among all band rows, identically in every CTA ---------------------------------
+template <bool X>
 __device__ __noinline__ void phase_pick(int l) {
     extern __shared__ __align__(128) uint8_t smem[];  // the kernel's dynamic shared memory
     const Smem sm{smem};
@@ -954,8 +1045,42 @@ __device__ __noinline__ void phase_pick(int l) {
     uint8_t* ring = sm.ring();
     const int n_band_mine = s_ctl[SC_N_BAND], n_keep = s_ctl[SC_N_KEEP];
 
-    const int n_in_tot = (int)__ldcg(&a.ctrs[CTR_IN]);
-    const int n_band_tot = min((int)__ldcg(&a.ctrs[CTR_BAND]), a.n_rows);
+    // X: the band entries of rank r sit at [seg_off[r], seg_off[r] + its count) of this GPU's copy of the
+    // band arrays; entry i of the concatenation is found through the running counts seg_pre[].
+    int n_in_tot, n_band_tot;
+    int seg_pre[FW_MAX_WORLD + 1];
+    const uint32_t* band_row_g = a.band_row;
+    const float* band_exact_g = a.band_exact;
+    if (X) {
+        const uint2* cnt = reinterpret_cast<const uint2*>(a.px.area[a.px.rank] + a.px.off_cnt);
+        n_in_tot = 0;
+        seg_pre[0] = 0;
+#pragma unroll
+        for (int r = 0; r < FW_MAX_WORLD; ++r) {
+            uint2 c = make_uint2(0u, 0u);
+            if (r < a.px.world) c = __ldcg(cnt + r);
+            n_in_tot += (int)c.x;
+            seg_pre[r + 1] = seg_pre[r] + (int)c.y;
+        }
+        n_band_tot = min(seg_pre[FW_MAX_WORLD], a.px.n_rows_global);
+        band_row_g = reinterpret_cast<const uint32_t*>(a.px.area[a.px.rank] + a.px.off_band_row);
+        band_exact_g = reinterpret_cast<const float*>(a.px.area[a.px.rank] + a.px.off_band_exact);
+    } else {
+        n_in_tot = (int)__ldcg(&a.ctrs[CTR_IN]);
+        n_band_tot = min((int)__ldcg(&a.ctrs[CTR_BAND]), a.n_rows);
+    }
+    auto band_at = [&](int i) -> int {  // where entry i of all band entries sits in the band arrays
+        if (!X) return i;
+        int pre = 0, off = a.px.seg_off[0];
+#pragma unroll
+        for (int q = 1; q < FW_MAX_WORLD; ++q) {
+            const bool in = q < a.px.world && i >= seg_pre[q];
+            pre = in ? seg_pre[q] : pre;
+            off = in ? a.px.seg_off[q] : off;
+        }
+        return off + (i - pre);
+    };
+    const int row_add = X ? a.px.row_offset : 0;  // own rows as global row numbers
     const int need = a.top_k - n_in_tot;
     uint32_t tau_key = 0, row_cut = 0xffffffffu;
     bool take_all = need >= n_band_tot;
@@ -1050,15 +1175,16 @@ __device__ __noinline__ void phase_pick(int l) {
         if (staged) {
             if (tid < STAGERS)
                 for (int i = tid; i < n_band_tot; i += STAGERS) {
-                    keys[i] = abs_key(__ldcg(&a.band_exact[i]));
-                    rows[i] = __ldcg(&a.band_row[i]);
+                    const int at = band_at(i);
+                    keys[i] = abs_key(__ldcg(&band_exact_g[at]));
+                    rows[i] = __ldcg(&band_row_g[at]);
                 }
             bar_sync(FW_BAR_CONS, FW_CONSUMERS);
         }
         if (by_rank) {
             for (int i = warp; i < n_band_mine; i += FW_NWARPS) {
                 const uint32_t key = abs_key(band_ex[i]);
-                const uint32_t row = (uint32_t)row_of_slot(cx, band_list[i]);
+                const uint32_t row = (uint32_t)(row_of_slot(cx, band_list[i]) + row_add);
                 int ahead = 0;  // entries that order before this one under (|v| desc, row asc)
                 for (int j = lane; j < n_band_tot; j += 32) {
                     const uint32_t kj = keys[j];
@@ -1071,12 +1197,12 @@ __device__ __noinline__ void phase_pick(int l) {
         } else {
             SelectSmem<FW_CONSUMERS>& ssm = *reinterpret_cast<SelectSmem<FW_CONSUMERS>*>(ring + FW_PICK_CAP * 8);
             int cnt_gt, need_eq;
-            auto keyf = [&](int i) -> uint32_t { return staged ? keys[i] : abs_key(__ldcg(&a.band_exact[i])); };
+            auto keyf = [&](int i) -> uint32_t { return staged ? keys[i] : abs_key(__ldcg(&band_exact_g[band_at(i)])); };
             block_kth_largest_keys<FW_CONSUMERS, FW_BAR_CONS>(keyf, n_band_tot, need, ssm, tau_key, cnt_gt, need_eq);
             // ties at the threshold: the need_eq lowest rows win
             auto rowf = [&](int i) -> uint32_t {
                 if (keyf(i) != tau_key) return 0u;
-                return ~(staged ? rows[i] : __ldcg(&a.band_row[i]));
+                return ~(staged ? rows[i] : __ldcg(&band_row_g[band_at(i)]));
             };
             uint32_t cut_key;
             int c2, n2;
@@ -1094,14 +1220,14 @@ __device__ __noinline__ void phase_pick(int l) {
             uint32_t row = 0;
             if (i < n_band_mine && need > 0) {
                 const uint32_t key = abs_key(band_ex[i]);
-                row = (uint32_t)row_of_slot(cx, band_list[i]);
+                row = (uint32_t)(row_of_slot(cx, band_list[i]) + row_add);
                 win = by_rank ? (win_s[i] != 0) : (take_all || key > tau_key || (key == tau_key && row <= row_cut));
             }
             const uint32_t bal = __ballot_sync(0xffffffffu, win);
             if (win) {
                 const int pos = n_keep + cnt + __popc(bal & ((1u << lane) - 1u));
-                g2_rows[pos] = (int)row;
-                g2_scores[pos] = band_ex[i];  // the gather uses the exact gate score
+                g2_rows[pos] = (int)row - row_add;  // the gather addresses this rank's own rows
+                g2_scores[pos] = band_ex[i];        // the gather uses the exact gate score
             }
             cnt += __popc(bal);
         }
@@ -1130,10 +1256,10 @@ __device__ __noinline__ void phase_pick(int l) {
     if (l + 1 == a.n_layers && a.stats && blockIdx.x == 0 && tid == 0) {
         a.stats->n_certain = n_in_tot;
         a.stats->n_band = n_band_tot;
-        a.stats->n_hits = min(a.top_k, a.n_rows);
+        a.stats->n_hits = min(a.top_k, X ? a.px.n_rows_global : a.n_rows);
         a.stats->need = need;
     }
-    if (l + 1 == a.n_layers && a.count_out && blockIdx.x == 0 && tid == 0)
+    if (!X && l + 1 == a.n_layers && a.count_out && blockIdx.x == 0 && tid == 0)
         *a.count_out = (uint32_t)min(a.top_k, a.n_rows);
     // the pick staged plain stores in the ring; order them before the TMA writes of the gather
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1162,8 +1288,6 @@ __device__ __noinline__ void phase_gather(int l) {
         ga.psum = sm.psum(); ga.act = sm.psum() + FW_MAX_GROWS * gm.Wt; ga.bar = sm.gbar();
         ga.xa_s = sm.xa(); ga.xb_s = sm.xb(); ga.blk_s = sm.blk();
         ga.nsb = gm.nsb; ga.G = gm.G; ga.TS = gm.TS; ga.P = P; ga.Wt = gm.Wt; ga.row_bytes = gm.row_bytes;
-        ga.stamp = (a.phase_ns && l == cx.stamp_layer && blockIdx.x == 0 && base == 0) ? a.phase_ns + 13 : nullptr;
-        if (ga.stamp && tid == 0) a.phase_ns[18] = (unsigned long long)n_g2;
         // leaves the accumulators staged in the ring
         gather_stage(ga, base, max(0, min(gm.D2, n_g2 - base)), gather_uses & 1u, failed);
         gather_uses += 1;
@@ -1194,7 +1318,7 @@ __device__ __noinline__ void phase_gather(int l) {
         const int base = s_ctl[SC_HIT_BASE];
         const int* g2_rows = sm.g_rows();
         for (int i = tid; i < n_g2; i += FW_CONSUMERS)
-            if (base + i < a.top_k) a.hit_out[base + i] = (uint32_t)g2_rows[i];
+            if (base + i < a.top_k) a.hit_out[base + i] = (uint32_t)g2_rows[i];  // (a sharded walk: this rank's own row numbers)
     }
     // the ring is free: the next layer's first tiles may land
     if (tid == 0 && l + 1 < a.n_layers) {
@@ -1212,6 +1336,9 @@ __device__ __noinline__ void phase_gather(int l) {
 }
 
 // ---- 4. finish: fixed-order sum of a column slice of the partials + residual --------------------
+// X: the slice sum goes, without the residual, into slot `rank` of every rank's xsum; the next prepare (or
+// the epilogue after the last layer) adds the slots up in rank order.
+template <bool X>
 __device__ __noinline__ void phase_finish(const float* h_cur, float* h_next) {
     extern __shared__ __align__(128) uint8_t smem[];  // the kernel's dynamic shared memory
     const Smem sm{smem};
@@ -1241,11 +1368,16 @@ __device__ __noinline__ void phase_finish(const float* h_cur, float* h_next) {
             const float4 v = red4[yy * per + tid];
             t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
         }
-        if (a.flags & LQ_WALK_RESIDUAL) {
-            const float4 hres = __ldcg(reinterpret_cast<const float4*>(h_cur) + col0 + tid);
-            t.x += hres.x; t.y += hres.y; t.z += hres.z; t.w += hres.w;
+        if (X) {
+            for (int p = 0; p < a.px.world; ++p)
+                reinterpret_cast<float4*>(a.px.area[p] + a.px.off_xsum)[(size_t)a.px.rank * ncol4 + col0 + tid] = t;
+        } else {
+            if (a.flags & LQ_WALK_RESIDUAL) {
+                const float4 hres = __ldcg(reinterpret_cast<const float4*>(h_cur) + col0 + tid);
+                t.x += hres.x; t.y += hres.y; t.z += hres.z; t.w += hres.w;
+            }
+            reinterpret_cast<float4*>(h_next)[col0 + tid] = t;
         }
-        reinterpret_cast<float4*>(h_next)[col0 + tid] = t;
     }
     if (blockIdx.x == 0 && tid == 0) {
         a.ctrs[CTR_IN] = 0;
@@ -1254,48 +1386,52 @@ __device__ __noinline__ void phase_finish(const float* h_cur, float* h_next) {
     bar_sync(FW_BAR_CONS, FW_CONSUMERS);  // red is reused by the next phase
 }
 
+// Parameters -> shared memory, barriers, the first tiles of layer 0.
+__device__ __forceinline__ void fused_setup(const FusedGeom& gm_in, const FusedArgs& a_in) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const Smem sm{smem};
+    const int tid = threadIdx.x;
+    Ctx& cxw = sm.cx();
+    const uint32_t* gsrc = reinterpret_cast<const uint32_t*>(&gm_in);
+    const uint32_t* asrc = reinterpret_cast<const uint32_t*>(&a_in);
+    uint32_t* gdst = reinterpret_cast<uint32_t*>(&cxw.gm);
+    uint32_t* adst = reinterpret_cast<uint32_t*>(&cxw.a);
+    for (int i = tid; i < (int)(sizeof(FusedGeom) / 4); i += FW_THREADS) gdst[i] = gsrc[i];
+    for (int i = tid; i < (int)(sizeof(FusedArgs) / 4); i += FW_THREADS) adst[i] = asrc[i];
+    if (tid == 0) {
+        const int R = gm_in.R;
+        cxw.n_tiles = (a_in.n_rows + R - 1) / R;
+        cxw.first_tile = blockIdx.x;
+        cxw.my_count =
+            (int)blockIdx.x < cxw.n_tiles ? (cxw.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+        cxw.n_slots = cxw.my_count * R;
+        cxw.n_ahead = min(gm_in.S, cxw.my_count);  // tiles issued before a layer's scan starts (a full ring)
+        cxw.stamp_layer = a_in.n_layers >= 2 ? a_in.n_layers - 2 : 0;
+        int* s_ctl = sm.ctl();
+        for (int i = 0; i < 16; ++i) s_ctl[i] = 0;
+        for (int i = 0; i < gm_in.S; ++i) {
+            mbar_init(&sm.full()[i], 1);
+            sm.released()[i] = 0;
+        }
+        mbar_init(sm.gbar(), 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (tid == 0) {
+        const Ctx& cx = sm.cx();
+        const FusedLayer l0 = layer_of(cx.a, 0);
+        for (int k = 0; k < cx.n_ahead; ++k) issue_tile(sm, l0, k, (uint32_t)k);
+    }
+}
+
 __global__ void __launch_bounds__(FW_THREADS, 1)
 walk_fused_q4k_kernel(const __grid_constant__ FusedGeom gm_in, const __grid_constant__ FusedArgs a_in) {
     extern __shared__ __align__(128) uint8_t smem[];
     const Smem sm{smem};
-    const int tid = threadIdx.x;
-    {
-        // parameters -> shared memory
-        Ctx& cxw = sm.cx();
-        const uint32_t* gsrc = reinterpret_cast<const uint32_t*>(&gm_in);
-        const uint32_t* asrc = reinterpret_cast<const uint32_t*>(&a_in);
-        uint32_t* gdst = reinterpret_cast<uint32_t*>(&cxw.gm);
-        uint32_t* adst = reinterpret_cast<uint32_t*>(&cxw.a);
-        for (int i = tid; i < (int)(sizeof(FusedGeom) / 4); i += FW_THREADS) gdst[i] = gsrc[i];
-        for (int i = tid; i < (int)(sizeof(FusedArgs) / 4); i += FW_THREADS) adst[i] = asrc[i];
-        if (tid == 0) {
-            const int R = gm_in.R;
-            cxw.n_tiles = (a_in.n_rows + R - 1) / R;
-            cxw.first_tile = blockIdx.x;
-            cxw.my_count =
-                (int)blockIdx.x < cxw.n_tiles ? (cxw.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-            cxw.n_slots = cxw.my_count * R;
-            cxw.n_ahead = min(gm_in.S, cxw.my_count);  // tiles issued before a layer's scan starts (a full ring)
-            cxw.stamp_layer = a_in.n_layers >= 2 ? a_in.n_layers - 2 : 0;
-            int* s_ctl = sm.ctl();
-            for (int i = 0; i < 16; ++i) s_ctl[i] = 0;
-            for (int i = 0; i < gm_in.S; ++i) {
-                mbar_init(&sm.full()[i], 1);
-                sm.released()[i] = 0;
-            }
-            mbar_init(sm.gbar(), 1);
-            fence_mbar_init();
-        }
-    }
-    __syncthreads();
+    fused_setup(gm_in, a_in);
     const Ctx& cx = sm.cx();
     const FusedArgs& a = cx.a;
     int* s_ctl = sm.ctl();
-    if (tid == 0) {
-        const FusedLayer l0 = layer_of(a, 0);
-        for (int k = 0; k < cx.n_ahead; ++k) issue_tile(sm, l0, k, (uint32_t)k);
-    }
-
     uint32_t epoch = 0;
     bool failed = false;
     const float* h_cur = a.h_in;
@@ -1303,42 +1439,92 @@ walk_fused_q4k_kernel(const __grid_constant__ FusedGeom gm_in, const __grid_cons
     for (int l = 0; l < n_layers; ++l) {
         float* h_next = (l + 1 == n_layers) ? a.h_out : ((l & 1) ? a.hbuf1 : a.hbuf0);
         FW_STAMP(0);
-        phase_prepare(l, h_cur);
+        phase_prepare<false>(l, h_cur, nullptr);
         FW_STAMP(1);
-        const long long dbg_s0 = clock64();
         phase_scan(l);
-        const long long dbg_scan = clock64() - dbg_s0;
         FW_STAMP(2);
         grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[SC_FAILED]);  // A: histogram complete
         FW_STAMP(3);
-        const long long dbg_e0 = clock64();
-        phase_select(l);
-        const long long dbg_sel = clock64() - dbg_e0;
+        phase_select<false>(l);
         FW_STAMP(5);
         grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[SC_FAILED]);  // B: band and pool rows published
         FW_STAMP(6);
-        const long long dbg_t0 = clock64();
-        phase_pick(l);
+        phase_pick<false>(l);
         FW_STAMP(7);
-        const long long dbg_t1 = clock64();
         phase_gather(l);
         FW_STAMP(9);
-        if (a.phase_ns && l == cx.stamp_layer && tid == 0) {
-            uint32_t* d = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.phase_ns) + 960) + blockIdx.x * 8;
-            d[0] = (uint32_t)(dbg_t1 - dbg_t0);
-            d[1] = (uint32_t)(clock64() - dbg_t1);
-            d[2] = (uint32_t)s_ctl[SC_N_G2];
-            d[3] = (uint32_t)s_ctl[SC_N_BAND];
-            d[4] = (uint32_t)dbg_scan;
-            d[5] = (uint32_t)dbg_sel;
-        }
         grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[SC_FAILED]);  // C: partials written
         FW_STAMP(10);
-        phase_finish(h_cur, h_next);
+        phase_finish<false>(h_cur, h_next);
         FW_STAMP(11);
         h_cur = h_next;
         if (l + 1 < n_layers) grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[SC_FAILED]);  // D: next residual
         FW_STAMP(12);
+    }
+    if (failed || s_ctl[SC_FAILED]) set_err(a.err, DEV_ERR_TMA_TIMEOUT);
+}
+
+// The same walk on one rank of a feature-sharded stack: this GPU's rows of every layer, the selection made
+// over all ranks' rows.  Per layer: barrier over this GPU's CTAs (its histogram is complete), histogram
+// slices to every rank, barrier over ALL ranks, threshold and classification, own band rows published to
+// every rank, barrier over all ranks (with the counts), final pick (the same on every CTA of every rank),
+// gather of own rows, local barrier, slice sums to every rank, barrier over all ranks.
+__global__ void __launch_bounds__(FW_THREADS, 1)
+walk_fused_q4k_sharded_kernel(const __grid_constant__ FusedGeom gm_in, const __grid_constant__ FusedArgs a_in) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const Smem sm{smem};
+    fused_setup(gm_in, a_in);
+    const Ctx& cx = sm.cx();
+    const FusedArgs& a = cx.a;
+    int* s_ctl = sm.ctl();
+    uint32_t epoch = 0, xepoch = a.px.xepoch0;
+    bool failed = false;
+    const int n_layers = a.n_layers;
+    // residual entering layer l: h_in for l == 0, else kept by the slice owners in hbuf[l & 1]
+    const float* h_cur = a.h_in;
+    for (int l = 0; l < n_layers; ++l) {
+        float* h_keep = (l & 1) ? a.hbuf1 : a.hbuf0;
+        FW_STAMP(0);
+        phase_prepare<true>(l, h_cur, h_keep);
+        if (l > 0) h_cur = h_keep;
+        FW_STAMP(1);
+        phase_scan(l);
+        FW_STAMP(2);
+        grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[SC_FAILED]);  // this GPU's histogram complete
+        phase_xhist(l);
+        xgrid_sync<false>(cx, epoch, xepoch, failed, &s_ctl[SC_FAILED]);       // A: every rank's histogram here
+        FW_STAMP(3);
+        phase_select<true>(l);
+        FW_STAMP(5);
+        xgrid_sync<true>(cx, epoch, xepoch, failed, &s_ctl[SC_FAILED]);        // B: band rows and counts here
+        FW_STAMP(6);
+        phase_pick<true>(l);
+        FW_STAMP(7);
+        phase_gather(l);
+        FW_STAMP(9);
+        grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[SC_FAILED]);  // C: partials written
+        FW_STAMP(10);
+        phase_finish<true>(nullptr, nullptr);
+        FW_STAMP(11);
+        xgrid_sync<false>(cx, epoch, xepoch, failed, &s_ctl[SC_FAILED]);       // D: every rank's slice sums here
+        FW_STAMP(12);
+    }
+    // epilogue: out = residual entering the last layer + every rank's partial output, own column slice
+    {
+        const int tid = threadIdx.x, ncol4 = cx.gm.nsb * 64;
+        const int per = (ncol4 + gridDim.x - 1) / gridDim.x, col0 = blockIdx.x * per;
+        if (tid < per && col0 + tid < ncol4) {
+            const int i = col0 + tid;
+            float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (a.flags & LQ_WALK_RESIDUAL) t = __ldcg(reinterpret_cast<const float4*>(h_cur) + i);
+            const float4* xsum = reinterpret_cast<const float4*>(a.px.area[a.px.rank] + a.px.off_xsum);
+            for (int r = 0; r < a.px.world; ++r) {
+                const float4 v = __ldcg(xsum + (size_t)r * ncol4 + i);
+                t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+            }
+            reinterpret_cast<float4*>(a.h_out)[i] = t;
+        }
+        if (a.count_out && blockIdx.x == 0 && tid == 0) *a.count_out = __ldcg(&a.ctrs[CTR_HITS]);
     }
     if (failed || s_ctl[SC_FAILED]) set_err(a.err, DEV_ERR_TMA_TIMEOUT);
 }
@@ -1364,20 +1550,30 @@ size_t fused_q4k_ws_bytes(int hidden, int n_rows, int sm_count) {
 
 int fused_q4k_stamp_count() { return FW_STAMPS; }
 
-// ws: fused_q4k_ws_bytes() of zero-initialised device memory, 256-byte aligned.  layers_dev:
-// n_layers x {gate, up, down} device pointers in device memory.
-cudaError_t launch_walk_fused_q4k(const void* layers_dev, const uint8_t* const* single, int n_layers, int n_rows,
-                                  int hidden, int top_k,
-                                  uint32_t flags, float c1, const float* h_in, float* h_out, uint8_t* ws,
-                                  uint32_t* hit_out, uint32_t* count_out, lq_walk_stats* stats_dev, int* err,
-                                  int sm_count, cudaStream_t st) {
-    FusedGeom g;
-    if (!fused_geom(hidden, n_rows, sm_count, g)) return cudaErrorInvalidValue;
-    const int n_tiles = (n_rows + g.R - 1) / g.R;
-    const int grid = sm_count < n_tiles ? sm_count : n_tiles;
-    cudaError_t e = set_max_dyn_smem((const void*)walk_fused_q4k_kernel, 227 * 1024);
-    if (e != cudaSuccess) return e;
-    FusedArgs a;
+namespace {
+
+struct XLayout {
+    uint32_t off_meta, off_cnt, off_hist, off_band_row, off_band_exact, off_xsum;
+    size_t bytes;
+};
+XLayout x_layout(int hidden, int n_rows_global, int world) {
+    XLayout x;
+    size_t o = 128;  // flags
+    x.off_meta = (uint32_t)o;        o += 128;
+    x.off_cnt = (uint32_t)o;         o += 128;
+    o = 1024;
+    x.off_hist = (uint32_t)o;        o += (size_t)world * LQ_HIST_BINS * 4;
+    x.off_band_row = (uint32_t)o;    o += ((size_t)n_rows_global * 4 + 255) / 256 * 256;
+    x.off_band_exact = (uint32_t)o;  o += ((size_t)n_rows_global * 4 + 255) / 256 * 256;
+    x.off_xsum = (uint32_t)o;        o += (size_t)world * hidden * 4;
+    x.bytes = (o + 255) / 256 * 256;
+    return x;
+}
+
+cudaError_t fill_args(FusedArgs& a, const FusedGeom& g, const void* layers_dev, const uint8_t* const* single,
+                      int n_layers, int n_rows, int hidden, int top_k, uint32_t flags, float c1, const float* h_in,
+                      float* h_out, uint8_t* ws, uint32_t* hit_out, uint32_t* count_out, lq_walk_stats* stats_dev,
+                      int* err, int sm_count, cudaStream_t st) {
     a.layers = reinterpret_cast<const FusedLayer*>(layers_dev);
     a.single = single ? FusedLayer{single[0], single[1], single[2]} : FusedLayer{nullptr, nullptr, nullptr};
     a.n_layers = n_layers;
@@ -1392,8 +1588,6 @@ cudaError_t launch_walk_fused_q4k(const void* layers_dev, const uint8_t* const* 
     static const int pf_late_env = [] { const char* v = getenv("LARQL_B200_FUSED_PF_LATE"); return v ? atoi(v) : 1; }();
     static const int pf_dist_env = [] { const char* v = getenv("LARQL_B200_FUSED_PFD"); return v ? atoi(v) : 0; }();
     a.pf_dist = pf_dist_env;
-    const int tiles_per_cta = (n_tiles + grid - 1) / grid;
-    (void)tiles_per_cta;
     a.pf_tiles = (a.layers && n_layers > 1 && pf_env > 0) ? pf_env : 0;
     a.pf_late = pf_late_env ? 1 : 0;
     a.h_in = h_in;
@@ -1415,14 +1609,89 @@ cudaError_t launch_walk_fused_q4k(const void* layers_dev, const uint8_t* const* 
     a.stats = stats_dev;
     a.phase_ns = stats_dev ? reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(stats_dev) + 64) : nullptr;
     a.err = err;
+    memset(&a.px, 0, sizeof a.px);
+    a.px.world = 1;
     // the barrier counters and the per-launch counters start from zero (the histogram is kept
     // zero by the kernel itself; a failed launch is followed by a full clear on the host side)
-    e = cudaMemsetAsync(a.ctrs, 0, 256, st);
+    return cudaMemsetAsync(a.ctrs, 0, 256, st);
+}
+
+}  // namespace
+
+size_t fused_q4k_xarea_bytes(int hidden, int n_rows_global, int world) {
+    return x_layout(hidden, n_rows_global, world).bytes;
+}
+
+bool fused_q4k_sharded_supported(int hidden, int n_rows_local, int n_rows_global, int top_k, int world, int sm_count) {
+    FusedGeom g;
+    if (world < 1 || world > FW_MAX_WORLD || n_rows_local <= 0 || top_k <= 0 || top_k >= n_rows_global) return false;
+    if (!fused_geom(hidden, n_rows_local, sm_count, g)) return false;
+    const int per = (hidden / 4 + sm_count - 1) / sm_count;
+    // every CTA of every rank takes part in every barrier: a rank needs at least one tile per CTA
+    const int n_tiles = (n_rows_local + g.R - 1) / g.R;
+    return per <= FW_CONSUMERS && g.max_slots <= 16384 && n_tiles >= sm_count;
+}
+
+// One rank's launch of a sharded walk.  areas[r]: rank r's exchange area (fused_q4k_xarea_bytes(), zeroed
+// once when it was created) as mapped into this process; row_offsets[r]: first global row of rank r;
+// xepoch0: how many all-rank barriers earlier launches on these areas have passed (3 per layer).
+cudaError_t launch_walk_fused_q4k_sharded(const void* layers_dev, int n_layers, int n_rows_local, int n_rows_global,
+                                          int hidden, int top_k, uint32_t flags, float c1, const float* h_in,
+                                          float* h_out, uint8_t* ws, uint32_t* hit_out, uint32_t* count_out,
+                                          lq_walk_stats* stats_dev, int* err, int sm_count, int world, int rank,
+                                          uint8_t* const* areas, const int* row_offsets, uint32_t xepoch0,
+                                          cudaStream_t st) {
+    FusedGeom g;
+    if (!fused_q4k_sharded_supported(hidden, n_rows_local, n_rows_global, top_k, world, sm_count))
+        return cudaErrorInvalidValue;
+    fused_geom(hidden, n_rows_local, sm_count, g);
+    cudaError_t e = set_max_dyn_smem((const void*)walk_fused_q4k_sharded_kernel, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    FusedArgs a;
+    e = fill_args(a, g, layers_dev, nullptr, n_layers, n_rows_local, hidden, top_k, flags, c1, h_in, h_out, ws, hit_out,
+                  count_out, stats_dev, err, sm_count, st);
+    if (e != cudaSuccess) return e;
+    const XLayout x = x_layout(hidden, n_rows_global, world);
+    a.px.world = world;
+    a.px.rank = rank;
+    a.px.row_offset = row_offsets[rank];
+    a.px.n_rows_global = n_rows_global;
+    a.px.xepoch0 = xepoch0;
+    a.px.off_meta = x.off_meta;
+    a.px.off_cnt = x.off_cnt;
+    a.px.off_hist = x.off_hist;
+    a.px.off_band_row = x.off_band_row;
+    a.px.off_band_exact = x.off_band_exact;
+    a.px.off_xsum = x.off_xsum;
+    for (int r = 0; r < world; ++r) {
+        a.px.seg_off[r] = row_offsets[r];
+        a.px.area[r] = areas[r];
+    }
+    void* args[] = {&g, &a};
+    return cudaLaunchCooperativeKernel((const void*)walk_fused_q4k_sharded_kernel, dim3(sm_count), dim3(FW_THREADS), args,
+                                       (size_t)g.smem_bytes, st);
+}
+
+// ws: fused_q4k_ws_bytes() of zero-initialised device memory, 256-byte aligned.  layers_dev:
+// n_layers x {gate, up, down} device pointers in device memory.
+cudaError_t launch_walk_fused_q4k(const void* layers_dev, const uint8_t* const* single, int n_layers, int n_rows,
+                                  int hidden, int top_k,
+                                  uint32_t flags, float c1, const float* h_in, float* h_out, uint8_t* ws,
+                                  uint32_t* hit_out, uint32_t* count_out, lq_walk_stats* stats_dev, int* err,
+                                  int sm_count, cudaStream_t st) {
+    FusedGeom g;
+    if (!fused_geom(hidden, n_rows, sm_count, g)) return cudaErrorInvalidValue;
+    const int n_tiles = (n_rows + g.R - 1) / g.R;
+    const int grid = sm_count < n_tiles ? sm_count : n_tiles;
+    cudaError_t e = set_max_dyn_smem((const void*)walk_fused_q4k_kernel, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    FusedArgs a;
+    e = fill_args(a, g, layers_dev, single, n_layers, n_rows, hidden, top_k, flags, c1, h_in, h_out, ws, hit_out,
+                  count_out, stats_dev, err, sm_count, st);
     if (e != cudaSuccess) return e;
     void* args[] = {&g, &a};
-    e = cudaLaunchCooperativeKernel((const void*)walk_fused_q4k_kernel, dim3(grid), dim3(FW_THREADS), args,
-                                    (size_t)g.smem_bytes, st);
-    return e;
+    return cudaLaunchCooperativeKernel((const void*)walk_fused_q4k_kernel, dim3(grid), dim3(FW_THREADS), args,
+                                       (size_t)g.smem_bytes, st);
 }
 
 }  // namespace lq
