@@ -133,6 +133,12 @@ def physical_gpu_index(local_rank: int) -> int:
     return local_rank
 
 
+# phases of the persistent walk kernel between its clock stamps (CTA 0, last layer but one); in a sharded walk
+# barrier_a also covers the barrier over this GPU's CTAs and the copy of its histogram to the other ranks
+PHASE_NAMES = ["prepare", "scan", "barrier_a", "select", "rescore", "barrier_b", "pick", "gather", "merge",
+               "barrier_c", "finish", "barrier_d"]
+
+
 def config_of(args, wl):
     moe = f", {wl['experts']} experts top-{wl['top_e']}" if "experts" in wl else ""
     return {"workload": f"{args.workload}: hidden {wl['hidden']}, features {wl['features']}{moe}, top_k {wl['top_k']}, "
@@ -394,17 +400,34 @@ def run_sharded(args, wl, be, ext, dev, rank, world, local):
     alg_bytes = algorithmic_bytes_per_token_layer(H, N, K) * L * B
     peak, peak_kind = measured_peaks()
     achieved = alg_bytes / world / (ms_step * 1e-3) / 1e9   # per GPU
+    fused = be.stack_path(stack) == 3
+    if fused:
+        kernel = "walk_fused_q4k_sharded_kernel (one persistent launch per token and rank)"
+        how = ("features sharded over %d GPU(s); every rank walks all layers in one persistent kernel and the ranks "
+               "exchange histogram, band rows and partial outputs through peer memory (three all-rank barriers per layer)"
+               % world)
+        note = ("per GPU: algorithmic bytes / n_gpus / step time; at batch 1 a layer is bound by its five barriers and "
+                "the serial selection steps between them, not by HBM")
+        us = be.fused_phase_us()
+        phases = dict(zip(PHASE_NAMES, [float(v) for v in us])) if us is not None else None
+    else:
+        kernel = "scan_q4k_kernel + gather_q4k_kernel per rank"
+        how = "features sharded over %d GPU(s), three NCCL exchanges per layer issued by the library" % world
+        note = ("per GPU: algorithmic bytes / n_gpus / step time; batch-1 sharding is bound by the latency "
+                "of three exchanges and a dozen small launches per layer, not by HBM")
+        phases = None
+    cfg = config_of(args, wl)
+    cfg["parallelism"] = how
     line = {
         "metric": "walk_ffn_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": config_of(args, wl),
+        "config": cfg,
         "walk_gbs": alg_bytes / (ms_step * 1e-3) / 1e9, "algorithmic_bytes_per_step": alg_bytes,
-        "collectives_per_layer": 3, "parity": parity,
-        "roofline": {"kernel": "scan_q4k_kernel + gather_q4k_kernel per rank", "bound": "hbm", "achieved": achieved,
+        "exchanges_per_layer": 3, "parity": parity, "phase_us_cta0": phases,
+        "roofline": {"kernel": kernel, "bound": "hbm", "achieved": achieved,
                      "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                     "note": "per GPU: algorithmic bytes / n_gpus / step time; batch-1 sharding is bound by the latency "
-                             "of three exchanges and a dozen small launches per layer, not by HBM"},
+                     "note": note},
         "cpu_baseline": None,
         "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": B * H * 4, "d2h_bytes_per_step": B * H * 4,
@@ -620,9 +643,7 @@ def run_ours(args, wl):
 
     fused = fmt == FMT_Q4_K and B == 1
     phase_us = be.fused_phase_us() if fused else None
-    names = ["prepare", "scan", "barrier_a", "select", "rescore", "barrier_b", "pick", "gather", "merge",
-             "barrier_c", "finish", "barrier_d"]
-    phase = dict(zip(names, [float(v) for v in phase_us])) if phase_us else {}
+    phase = dict(zip(PHASE_NAMES, [float(v) for v in phase_us])) if phase_us else {}
     peak, peak_kind = measured_peaks()
     achieved = step_bytes / (ms_step * 1e-3) / 1e9
 

@@ -66,7 +66,7 @@ struct lq_stack {
     uint8_t* xarea = nullptr;             // this rank's exchange area
     std::vector<uint8_t*> areas;          // every rank's area as mapped here (areas[rank] == xarea)
     std::vector<int> row_offs;            // first global row of every rank
-    uint32_t xepoch = 0;                  // all-rank barriers passed so far on these areas
+    uint32_t xepoch = 0;                  // layers walked so far on these areas (epoch of the exchange lines)
     uint32_t* xhits = nullptr;            // [top_k] rows of the last layer's selection + [1] their count
     uint32_t* sync_word = nullptr;        // one word for the launch rendezvous
 };
@@ -1538,7 +1538,7 @@ static int stack_enqueue(lq_ctx* ctx, lq_stack* s) {
                                              last ? s->xhits : nullptr, last ? s->xhits + s->top_k : nullptr,
                                              t == 0 ? ctx->stats_dev : nullptr, ctx->d_err, ctx->sm_count, ctx->world,
                                              ctx->rank, s->areas.data(), s->row_offs.data(), s->xepoch, ctx->stream));
-            s->xepoch += 3u * (uint32_t)L;
+            s->xepoch += (uint32_t)L;
             ctx->launches += 1;
         }
         ctx->last_xstack = s;

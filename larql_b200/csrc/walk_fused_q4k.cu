@@ -85,20 +85,23 @@ struct FusedLayer {
 
 // Feature-sharded walk over the GPUs of one box: every rank runs this kernel on its own row range and the
 // ranks meet in each other's memory.  area[r] is rank r's exchange area as mapped into this process
-// (area[rank]: this GPU's own), all laid out alike:
-//   flags [world] u32        arrival flag of every rank (values only ever grow, across launches too)
-//   meta  [world] {u32, u32} score bound bits and highest occupied histogram bin of every rank's rows
-//   cnt   [world] {u32, u32} certainly-in rows and band rows of every rank
-//   hist  [world][LQ_HIST_BINS] u32   every rank's histogram
-//   band_row / band_exact [n_rows_global]   band entries, rank r's from entry row_offset(r) on
-//   xsum  [world][hidden] f32          every rank's partial layer output
-// A rank writes its own slot of each array into EVERY rank's area with ordinary peer stores and then
-// raises its flag there (fence.sys, then the store); readers only ever read their own GPU's memory.
+// (area[rank]: this GPU's own), all laid out alike, in 16-byte LINES {word0, epoch, word1, epoch}:
+//   meta  [world]                      score bound bits | highest occupied histogram bin of a rank's rows
+//   cnt   [world]                      certainly-in rows | band rows of a rank
+//   hist  [world][LQ_HIST_BINS / 2]    a rank's histogram, two bins per line
+//   band  [n_rows_global]              band entries {global row | exact score}, rank r's from line row_offset(r) on
+//   xsum  [world][hidden / 2]          a rank's partial layer output, two floats per line
+// A rank writes its own slot of each array into EVERY rank's area with one 16-byte store per line; a reader
+// (always reading its own GPU's memory) takes a line once both epoch words carry the layer's epoch, which only
+// ever grows, across launches too.  Each 8-byte half of such a store arrives whole, so data and epoch cannot be
+// torn apart and no fence or separate flag is needed: an exchange costs one trip over NVLink.  A slot is
+// rewritten only after every reader is done with it, because a rank cannot get a layer ahead without the
+// others' lines of the layer in between.
 struct FusedPeers {
     int world, rank, row_offset, n_rows_global;
-    uint32_t xepoch0;  // value of the flags when this launch starts
-    uint32_t off_meta, off_cnt, off_hist, off_band_row, off_band_exact, off_xsum;
-    uint32_t pad;
+    uint32_t xepoch0;  // epoch of the last layer of the previous launch on these areas
+    uint32_t off_meta, off_cnt, off_hist, off_band, off_xsum;
+    uint32_t pad[2];
     int seg_off[FW_MAX_WORLD];  // row_offset of every rank
     uint8_t* area[FW_MAX_WORLD];
 };
@@ -133,7 +136,7 @@ struct FusedArgs {
 };
 
 enum { CTR_SYNC = 0, CTR_BOUND0 = 1, CTR_BOUND1 = 2, CTR_IN = 3, CTR_BAND = 4, CTR_HITS = 5, CTR_MAXBIN0 = 6,
-       CTR_MAXBIN1 = 7, CTR_WORDS = 16 };
+       CTR_MAXBIN1 = 7, CTR_BDONE = 8, CTR_WORDS = 16 };
 
 __host__ __device__ inline int fw_align(int v, int a) { return (v + a - 1) / a * a; }
 
@@ -193,13 +196,30 @@ __device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
+// One exchange line: two data words, each beside the epoch it belongs to.
+__device__ __forceinline__ void line_store(void* p, uint32_t w0, uint32_t w1, uint32_t epoch) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(w0), "r"(epoch), "r"(w1), "r"(epoch)
+                 : "memory");
 }
-__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ bool line_load(const void* p, uint32_t epoch, uint32_t& w0, uint32_t& w1) {
+    uint32_t e0, e1;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(e0), "=r"(w1), "=r"(e1) : "l"(p)
+                 : "memory");
+    return e0 == epoch && e1 == epoch;
+}
+// Waits (bounded: about a second, or until another CTA has recorded an error) for a line of this epoch.
+// On failure the words read as zero and DEV_ERR_TMA_TIMEOUT is recorded.
+__device__ __forceinline__ void line_wait(const void* p, uint32_t epoch, uint32_t& w0, uint32_t& w1, int* err) {
+    if (line_load(p, epoch, w0, w1)) return;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!line_load(p, epoch, w0, w1)) {
+        if (((++spins & 63u) == 0) && (clock64() - t0 > (1ll << 31) || *(volatile int*)err != 0)) {
+            set_err(err, DEV_ERR_TMA_TIMEOUT);
+            w0 = w1 = 0u;
+            return;
+        }
+    }
 }
 // size a multiple of 16, address 16-byte aligned; this GPU's own memory
 __device__ __forceinline__ void l2_prefetch_bulk(const void* src, uint32_t bytes) {
@@ -492,51 +512,10 @@ static_assert(192 + sizeof(Ctx) <= 1024 - 128, "context does not fit the barrier
     } while (0)
 
 __device__ __forceinline__ FusedLayer layer_of(const FusedArgs& a, int l) { return a.layers ? a.layers[l] : a.single; }
+// epoch of the exchange lines of layer l of this launch
+__device__ __forceinline__ uint32_t x_epoch(const FusedArgs& a, int l) { return a.px.xepoch0 + (uint32_t)l + 1u; }
 __device__ __forceinline__ int row_of_slot(const Ctx& cx, int m) {
     return (cx.first_tile + (m / cx.gm.R) * (int)gridDim.x) * cx.gm.R + (m % cx.gm.R);
-}
-
-// Barrier over the CTAs of ALL ranks of a sharded walk.  Every CTA arrives on its own GPU's counter; the
-// last one to arrive there knows that all of this rank's writes (to every rank's memory) are ordered before
-// its system-scope fence, optionally publishes the rank's selection counts, and raises the rank's flag in
-// every rank's area.  Everybody then waits, on its own GPU's memory only, until every rank's flag is up.
-// Bounded like the grid barrier: about a second per wait, then DEV_ERR_TMA_TIMEOUT and no further waiting.
-template <bool WITH_COUNTS>
-__device__ __forceinline__ void xgrid_sync(const Ctx& cx, uint32_t& epoch, uint32_t& xepoch, bool& failed, int* s_flag) {
-    const FusedArgs& a = cx.a;
-    const FusedPeers& px = a.px;
-    epoch += 1;
-    xepoch += 1;
-    bar_sync(FW_BAR_CONS, FW_CONSUMERS);
-    if (threadIdx.x == 0 && !failed) {
-        __threadfence_system();
-        const uint32_t old = atomicAdd(&a.ctrs[CTR_SYNC], 1u);
-        if (old + 1u == epoch * gridDim.x) {
-            __threadfence();
-            if (WITH_COUNTS) {
-                const uint2 c = make_uint2(__ldcg(&a.ctrs[CTR_IN]), __ldcg(&a.ctrs[CTR_BAND]));
-                for (int p = 0; p < px.world; ++p) reinterpret_cast<uint2*>(px.area[p] + px.off_cnt)[px.rank] = c;
-                __threadfence_system();
-            }
-            for (int p = 0; p < px.world; ++p)
-                st_release_sys_u32(reinterpret_cast<uint32_t*>(px.area[p]) + px.rank, xepoch);
-        }
-        const uint32_t* fl = reinterpret_cast<const uint32_t*>(px.area[px.rank]);
-        const long long t0 = clock64();
-        uint32_t spins = 0;
-        for (int p = 0; p < px.world && !*s_flag; ++p) {
-            while ((int32_t)(ld_acquire_sys_u32(fl + p) - xepoch) < 0) {
-                if (clock64() - t0 > (1ll << 31) || ((++spins & 63u) == 0 && *(volatile int*)a.err != 0)) {
-                    set_err(a.err, DEV_ERR_TMA_TIMEOUT);
-                    *s_flag = 1;
-                    break;
-                }
-            }
-        }
-        __threadfence();
-    }
-    bar_sync(FW_BAR_CONS, FW_CONSUMERS);
-    if (*s_flag) failed = true;
 }
 
 // One thread issues the TMA copy of a gate tile: tile `it` (counted over all layers) goes to stage
@@ -597,10 +576,15 @@ __device__ __noinline__ void phase_prepare(int l, const float* h_cur, float* h_k
         float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
         if (!X || l == 0 || (a.flags & LQ_WALK_RESIDUAL)) t = __ldcg(src + i);
         if (X && l > 0) {
-            const float4* xsum = reinterpret_cast<const float4*>(a.px.area[a.px.rank] + a.px.off_xsum);
+            // layer l - 1's partial outputs: two lines per float4 and rank, taken as they arrive
+            const uint4* xsum = reinterpret_cast<const uint4*>(a.px.area[a.px.rank] + a.px.off_xsum);
+            const uint32_t ep = x_epoch(a, l - 1);
             for (int r = 0; r < a.px.world; ++r) {
-                const float4 v = __ldcg(xsum + (size_t)r * (hidden / 4) + i);
-                t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+                uint32_t w0, w1, w2, w3;
+                line_wait(xsum + (size_t)r * (hidden / 2) + 2 * i, ep, w0, w1, a.err);
+                line_wait(xsum + (size_t)r * (hidden / 2) + 2 * i + 1, ep, w2, w3, a.err);
+                t.x += __uint_as_float(w0); t.y += __uint_as_float(w1);
+                t.z += __uint_as_float(w2); t.w += __uint_as_float(w3);
             }
             if (i >= col0 && i < col0 + per) reinterpret_cast<float4*>(h_keep)[i] = t;
         }
@@ -790,24 +774,26 @@ __device__ __noinline__ void phase_scan(int l) {
 }
 
 // ---- 1b. sharded walk: this rank's histogram, bound and highest bin go to every rank -------------
-// After a barrier over this GPU's CTAs the local histogram is complete; every CTA copies a slice of it
-// into slot `rank` of every rank's area (all bins, so nothing stale is ever read).
+// After a barrier over this GPU's CTAs the local histogram is complete; every CTA sends a slice of it,
+// as lines, into slot `rank` of every rank's area (all bins, so a reader never meets a stale line).
 __device__ __noinline__ void phase_xhist(int l) {
     extern __shared__ __align__(128) uint8_t smem[];  // the kernel's dynamic shared memory
     const Smem sm{smem};
     const FusedArgs& a = sm.cx().a;
     const FusedPeers& px = a.px;
     const int tid = threadIdx.x, par = l & 1;
-    const uint4* hist4 = reinterpret_cast<const uint4*>(a.hist + (size_t)par * LQ_HIST_BINS);
-    constexpr int N4 = LQ_HIST_BINS / 4;
-    const int per = (N4 + gridDim.x - 1) / gridDim.x, c0 = blockIdx.x * per, n = max(0, min(per, N4 - c0));
+    const uint32_t ep = x_epoch(a, l);
+    const uint2* hist2 = reinterpret_cast<const uint2*>(a.hist + (size_t)par * LQ_HIST_BINS);
+    constexpr int N2 = LQ_HIST_BINS / 2;
+    const int per = (N2 + gridDim.x - 1) / gridDim.x, c0 = blockIdx.x * per, n = max(0, min(per, N2 - c0));
     for (int i = tid; i < n * px.world; i += FW_CONSUMERS) {
         const int p = i / n, j = i - p * n;
-        reinterpret_cast<uint4*>(px.area[p] + px.off_hist)[(size_t)px.rank * N4 + c0 + j] = __ldcg(hist4 + c0 + j);
+        const uint2 v = __ldcg(hist2 + c0 + j);
+        line_store(reinterpret_cast<uint4*>(px.area[p] + px.off_hist) + (size_t)px.rank * N2 + c0 + j, v.x, v.y, ep);
     }
     if (blockIdx.x == 0 && tid < px.world)
-        reinterpret_cast<uint2*>(px.area[tid] + px.off_meta)[px.rank] =
-            make_uint2(__ldcg(&a.ctrs[CTR_BOUND0 + par]), __ldcg(&a.ctrs[CTR_MAXBIN0 + par]));
+        line_store(reinterpret_cast<uint4*>(px.area[tid] + px.off_meta) + px.rank, __ldcg(&a.ctrs[CTR_BOUND0 + par]),
+                   __ldcg(&a.ctrs[CTR_MAXBIN0 + par]), ep);
 }
 
 // ---- 2. threshold bucket, classification, exact re-score and publication of the band ------------
@@ -819,8 +805,8 @@ __device__ __noinline__ void phase_select(int l) {
     const FusedGeom& gm = cx.gm;
     const FusedArgs& a = cx.a;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int par = l & 1, R = gm.R;
-    const uint32_t* hist = a.hist + (size_t)par * LQ_HIST_BINS;  // X: every rank's histogram, one after the other
+    const int par = l & 1;
+    const uint32_t* hist = a.hist + (size_t)par * LQ_HIST_BINS;
     int* s_ctl = sm.ctl();
     float* red = sm.red();
     float* my_scores = sm.scores();
@@ -839,15 +825,15 @@ __device__ __noinline__ void phase_select(int l) {
         uint32_t bbits, maxbin;
         if (X) {
             // positive floats order like their bits: the largest bound of any rank, the highest bin of any rank
-            const uint2* meta = reinterpret_cast<const uint2*>(a.px.area[a.px.rank] + a.px.off_meta);
+            const uint4* meta = reinterpret_cast<const uint4*>(a.px.area[a.px.rank] + a.px.off_meta);
             bbits = 0u;
             maxbin = 0u;
             for (int r = 0; r < a.px.world; ++r) {
-                const uint2 m = __ldcg(meta + r);
-                bbits = max(bbits, m.x);
-                maxbin = max(maxbin, m.y);
+                uint32_t b, m;
+                line_wait(meta + r, x_epoch(a, l), b, m, a.err);
+                bbits = max(bbits, b);
+                maxbin = max(maxbin, m);
             }
-            hist = reinterpret_cast<const uint32_t*>(a.px.area[a.px.rank] + a.px.off_hist);
         } else {
             bbits = __ldcg(&a.ctrs[CTR_BOUND0 + par]);
             maxbin = __ldcg(&a.ctrs[CTR_MAXBIN0 + par]);
@@ -860,12 +846,19 @@ __device__ __noinline__ void phase_select(int l) {
             const int b0 = base_end - 4 * (tid + 1);
             uint4 t4 = make_uint4(0u, 0u, 0u, 0u);
             if (tid < HT && b0 >= 0) {
-                t4 = __ldcg(reinterpret_cast<const uint4*>(hist + b0));
-                if (X)
-                    for (int r = 1; r < a.px.world; ++r) {
-                        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(hist + (size_t)r * LQ_HIST_BINS + b0));
-                        t4.x += v.x; t4.y += v.y; t4.z += v.z; t4.w += v.w;
+                if (X) {
+                    // every rank's four bins: two lines each, taken as they arrive
+                    const uint4* hl = reinterpret_cast<const uint4*>(a.px.area[a.px.rank] + a.px.off_hist);
+                    const uint32_t ep = x_epoch(a, l);
+                    for (int r = 0; r < a.px.world; ++r) {
+                        uint32_t w0, w1, w2, w3;
+                        line_wait(hl + (size_t)r * (LQ_HIST_BINS / 2) + b0 / 2, ep, w0, w1, a.err);
+                        line_wait(hl + (size_t)r * (LQ_HIST_BINS / 2) + b0 / 2 + 1, ep, w2, w3, a.err);
+                        t4.x += w0; t4.y += w1; t4.z += w2; t4.w += w3;
                     }
+                } else {
+                    t4 = __ldcg(reinterpret_cast<const uint4*>(hist + b0));
+                }
             }
             const uint32_t own = t4.x + t4.y + t4.z + t4.w;
             uint32_t pre = own;  // inclusive prefix in thread order (higher bins first)
@@ -1001,10 +994,9 @@ __device__ __noinline__ void phase_select(int l) {
                 // global row number; this rank's entries start at entry row_offset of every rank's arrays
                 const uint32_t row = (uint32_t)(row_of_slot(cx, band_list[i]) + a.px.row_offset);
                 const size_t at = (size_t)a.px.row_offset + base + i;
-                for (int p = 0; p < a.px.world; ++p) {
-                    reinterpret_cast<uint32_t*>(a.px.area[p] + a.px.off_band_row)[at] = row;
-                    reinterpret_cast<float*>(a.px.area[p] + a.px.off_band_exact)[at] = v;
-                }
+                for (int p = 0; p < a.px.world; ++p)
+                    line_store(reinterpret_cast<uint4*>(a.px.area[p] + a.px.off_band) + at, row, __float_as_uint(v),
+                               x_epoch(a, l));
             } else {
                 a.band_row[base + i] = (uint32_t)row_of_slot(cx, band_list[i]);
                 a.band_exact[base + i] = v;
@@ -1023,6 +1015,22 @@ __device__ __noinline__ void phase_select(int l) {
         if (tid == 0) {
             a.pool_cnt[blockIdx.x] = (uint32_t)n_over;
             a.pool_cnt[512 + blockIdx.x] = (uint32_t)(n_keep + n_band_mine);  // upper bound of this CTA's load so far
+        }
+    }
+    if (X) {
+        // The last CTA of this rank to get here sends the rank's counts to every rank (its own too): whoever
+        // holds a rank's counts knows that all of that rank's CTAs have published their band and pool rows.
+        bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+        if (tid == 0) {
+            __threadfence();
+            const uint32_t done = atomicAdd(&a.ctrs[CTR_BDONE], 1u) + 1u;
+            if (done == (uint32_t)(l + 1) * gridDim.x) {
+                __threadfence();
+                const uint32_t n_in = __ldcg(&a.ctrs[CTR_IN]), n_band = __ldcg(&a.ctrs[CTR_BAND]);
+                for (int p = 0; p < a.px.world; ++p)
+                    line_store(reinterpret_cast<uint4*>(a.px.area[p] + a.px.off_cnt) + a.px.rank, n_in, n_band,
+                               x_epoch(a, l));
+            }
         }
     }
 }
@@ -1051,20 +1059,22 @@ __device__ __noinline__ void phase_pick(int l) {
     int seg_pre[FW_MAX_WORLD + 1];
     const uint32_t* band_row_g = a.band_row;
     const float* band_exact_g = a.band_exact;
+    const uint4* band_lines = nullptr;
     if (X) {
-        const uint2* cnt = reinterpret_cast<const uint2*>(a.px.area[a.px.rank] + a.px.off_cnt);
+        // every rank's counts, as they arrive; this GPU's own say that its band and pool rows are all published
+        const uint4* cnt = reinterpret_cast<const uint4*>(a.px.area[a.px.rank] + a.px.off_cnt);
         n_in_tot = 0;
         seg_pre[0] = 0;
 #pragma unroll
         for (int r = 0; r < FW_MAX_WORLD; ++r) {
-            uint2 c = make_uint2(0u, 0u);
-            if (r < a.px.world) c = __ldcg(cnt + r);
-            n_in_tot += (int)c.x;
-            seg_pre[r + 1] = seg_pre[r] + (int)c.y;
+            uint32_t c_in = 0u, c_band = 0u;
+            if (r < a.px.world) line_wait(cnt + r, x_epoch(a, l), c_in, c_band, a.err);
+            n_in_tot += (int)c_in;
+            seg_pre[r + 1] = seg_pre[r] + (int)c_band;
         }
+        __threadfence();  // the pool rows and counts below were written before the counts were sent
         n_band_tot = min(seg_pre[FW_MAX_WORLD], a.px.n_rows_global);
-        band_row_g = reinterpret_cast<const uint32_t*>(a.px.area[a.px.rank] + a.px.off_band_row);
-        band_exact_g = reinterpret_cast<const float*>(a.px.area[a.px.rank] + a.px.off_band_exact);
+        band_lines = reinterpret_cast<const uint4*>(a.px.area[a.px.rank] + a.px.off_band);
     } else {
         n_in_tot = (int)__ldcg(&a.ctrs[CTR_IN]);
         n_band_tot = min((int)__ldcg(&a.ctrs[CTR_BAND]), a.n_rows);
@@ -1175,9 +1185,15 @@ __device__ __noinline__ void phase_pick(int l) {
         if (staged) {
             if (tid < STAGERS)
                 for (int i = tid; i < n_band_tot; i += STAGERS) {
-                    const int at = band_at(i);
-                    keys[i] = abs_key(__ldcg(&band_exact_g[at]));
-                    rows[i] = __ldcg(&band_row_g[at]);
+                    if (X) {
+                        uint32_t row, ex;
+                        line_wait(band_lines + band_at(i), x_epoch(a, l), row, ex, a.err);
+                        keys[i] = abs_key(__uint_as_float(ex));
+                        rows[i] = row;
+                    } else {
+                        keys[i] = abs_key(__ldcg(&band_exact_g[i]));
+                        rows[i] = __ldcg(&band_row_g[i]);
+                    }
                 }
             bar_sync(FW_BAR_CONS, FW_CONSUMERS);
         }
@@ -1197,12 +1213,27 @@ __device__ __noinline__ void phase_pick(int l) {
         } else {
             SelectSmem<FW_CONSUMERS>& ssm = *reinterpret_cast<SelectSmem<FW_CONSUMERS>*>(ring + FW_PICK_CAP * 8);
             int cnt_gt, need_eq;
-            auto keyf = [&](int i) -> uint32_t { return staged ? keys[i] : abs_key(__ldcg(&band_exact_g[band_at(i)])); };
+            // (a band too large to stage: every read waits for its line again, which costs nothing once it is there)
+            auto entry = [&](int i, uint32_t& row) -> uint32_t {
+                if (X) {
+                    uint32_t ex;
+                    line_wait(band_lines + band_at(i), x_epoch(a, l), row, ex, a.err);
+                    return abs_key(__uint_as_float(ex));
+                }
+                row = __ldcg(&band_row_g[i]);
+                return abs_key(__ldcg(&band_exact_g[i]));
+            };
+            auto keyf = [&](int i) -> uint32_t {
+                uint32_t row;
+                return staged ? keys[i] : entry(i, row);
+            };
             block_kth_largest_keys<FW_CONSUMERS, FW_BAR_CONS>(keyf, n_band_tot, need, ssm, tau_key, cnt_gt, need_eq);
             // ties at the threshold: the need_eq lowest rows win
             auto rowf = [&](int i) -> uint32_t {
-                if (keyf(i) != tau_key) return 0u;
-                return ~(staged ? rows[i] : __ldcg(&band_row_g[band_at(i)]));
+                uint32_t row = 0u;
+                const uint32_t key = staged ? keys[i] : entry(i, row);
+                if (key != tau_key) return 0u;
+                return ~(staged ? rows[i] : row);
             };
             uint32_t cut_key;
             int c2, n2;
@@ -1339,7 +1370,7 @@ __device__ __noinline__ void phase_gather(int l) {
 // X: the slice sum goes, without the residual, into slot `rank` of every rank's xsum; the next prepare (or
 // the epilogue after the last layer) adds the slots up in rank order.
 template <bool X>
-__device__ __noinline__ void phase_finish(const float* h_cur, float* h_next) {
+__device__ __noinline__ void phase_finish(const float* h_cur, float* h_next, uint32_t ep) {
     extern __shared__ __align__(128) uint8_t smem[];  // the kernel's dynamic shared memory
     const Smem sm{smem};
     const Ctx& cx = sm.cx();
@@ -1369,8 +1400,12 @@ __device__ __noinline__ void phase_finish(const float* h_cur, float* h_next) {
             t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
         }
         if (X) {
-            for (int p = 0; p < a.px.world; ++p)
-                reinterpret_cast<float4*>(a.px.area[p] + a.px.off_xsum)[(size_t)a.px.rank * ncol4 + col0 + tid] = t;
+            const size_t at = (size_t)a.px.rank * (hidden / 2) + 2 * (size_t)(col0 + tid);
+            for (int p = 0; p < a.px.world; ++p) {
+                uint4* xl = reinterpret_cast<uint4*>(a.px.area[p] + a.px.off_xsum) + at;
+                line_store(xl, __float_as_uint(t.x), __float_as_uint(t.y), ep);
+                line_store(xl + 1, __float_as_uint(t.z), __float_as_uint(t.w), ep);
+            }
         } else {
             if (a.flags & LQ_WALK_RESIDUAL) {
                 const float4 hres = __ldcg(reinterpret_cast<const float4*>(h_cur) + col0 + tid);
@@ -1455,7 +1490,7 @@ walk_fused_q4k_kernel(const __grid_constant__ FusedGeom gm_in, const __grid_cons
         FW_STAMP(9);
         grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[SC_FAILED]);  // C: partials written
         FW_STAMP(10);
-        phase_finish<false>(h_cur, h_next);
+        phase_finish<false>(h_cur, h_next, 0u);
         FW_STAMP(11);
         h_cur = h_next;
         if (l + 1 < n_layers) grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[SC_FAILED]);  // D: next residual
@@ -1465,10 +1500,14 @@ walk_fused_q4k_kernel(const __grid_constant__ FusedGeom gm_in, const __grid_cons
 }
 
 // The same walk on one rank of a feature-sharded stack: this GPU's rows of every layer, the selection made
-// over all ranks' rows.  Per layer: barrier over this GPU's CTAs (its histogram is complete), histogram
-// slices to every rank, barrier over ALL ranks, threshold and classification, own band rows published to
-// every rank, barrier over all ranks (with the counts), final pick (the same on every CTA of every rank),
-// gather of own rows, local barrier, slice sums to every rank, barrier over all ranks.
+// over all ranks' rows.  Per layer:
+//   scan own rows; barrier over this GPU's CTAs (its histogram is complete); histogram slices to every rank;
+//   threshold from every rank's histogram (lines taken as they arrive) and classification; own band rows to
+//   every rank, and once all of this GPU's CTAs have done so, its counts;
+//   final pick over every rank's band rows (the same on every CTA of every rank), gather of own rows;
+//   barrier over this GPU's CTAs; slice sums of the partials to every rank;
+//   the next layer's prepare (or the epilogue) adds up every rank's sums as they arrive.
+// Two barriers per layer, both local; the ranks wait for each other only where they read each other's lines.
 __global__ void __launch_bounds__(FW_THREADS, 1)
 walk_fused_q4k_sharded_kernel(const __grid_constant__ FusedGeom gm_in, const __grid_constant__ FusedArgs a_in) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -1477,7 +1516,7 @@ walk_fused_q4k_sharded_kernel(const __grid_constant__ FusedGeom gm_in, const __g
     const Ctx& cx = sm.cx();
     const FusedArgs& a = cx.a;
     int* s_ctl = sm.ctl();
-    uint32_t epoch = 0, xepoch = a.px.xepoch0;
+    uint32_t epoch = 0;
     bool failed = false;
     const int n_layers = a.n_layers;
     // residual entering layer l: h_in for l == 0, else kept by the slice owners in hbuf[l & 1]
@@ -1492,35 +1531,36 @@ walk_fused_q4k_sharded_kernel(const __grid_constant__ FusedGeom gm_in, const __g
         FW_STAMP(2);
         grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[SC_FAILED]);  // this GPU's histogram complete
         phase_xhist(l);
-        xgrid_sync<false>(cx, epoch, xepoch, failed, &s_ctl[SC_FAILED]);       // A: every rank's histogram here
         FW_STAMP(3);
         phase_select<true>(l);
         FW_STAMP(5);
-        xgrid_sync<true>(cx, epoch, xepoch, failed, &s_ctl[SC_FAILED]);        // B: band rows and counts here
         FW_STAMP(6);
         phase_pick<true>(l);
         FW_STAMP(7);
         phase_gather(l);
         FW_STAMP(9);
-        grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[SC_FAILED]);  // C: partials written
+        grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[SC_FAILED]);  // this GPU's partials written
         FW_STAMP(10);
-        phase_finish<true>(nullptr, nullptr);
+        phase_finish<true>(nullptr, nullptr, x_epoch(a, l));
         FW_STAMP(11);
-        xgrid_sync<false>(cx, epoch, xepoch, failed, &s_ctl[SC_FAILED]);       // D: every rank's slice sums here
         FW_STAMP(12);
     }
     // epilogue: out = residual entering the last layer + every rank's partial output, own column slice
     {
-        const int tid = threadIdx.x, ncol4 = cx.gm.nsb * 64;
+        const int tid = threadIdx.x, hidden = cx.gm.nsb * 256, ncol4 = hidden / 4;
         const int per = (ncol4 + gridDim.x - 1) / gridDim.x, col0 = blockIdx.x * per;
         if (tid < per && col0 + tid < ncol4) {
             const int i = col0 + tid;
             float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
             if (a.flags & LQ_WALK_RESIDUAL) t = __ldcg(reinterpret_cast<const float4*>(h_cur) + i);
-            const float4* xsum = reinterpret_cast<const float4*>(a.px.area[a.px.rank] + a.px.off_xsum);
+            const uint4* xsum = reinterpret_cast<const uint4*>(a.px.area[a.px.rank] + a.px.off_xsum);
+            const uint32_t ep = x_epoch(a, n_layers - 1);
             for (int r = 0; r < a.px.world; ++r) {
-                const float4 v = __ldcg(xsum + (size_t)r * ncol4 + i);
-                t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+                uint32_t w0, w1, w2, w3;
+                line_wait(xsum + (size_t)r * (hidden / 2) + 2 * i, ep, w0, w1, a.err);
+                line_wait(xsum + (size_t)r * (hidden / 2) + 2 * i + 1, ep, w2, w3, a.err);
+                t.x += __uint_as_float(w0); t.y += __uint_as_float(w1);
+                t.z += __uint_as_float(w2); t.w += __uint_as_float(w3);
             }
             reinterpret_cast<float4*>(a.h_out)[i] = t;
         }
@@ -1553,19 +1593,18 @@ int fused_q4k_stamp_count() { return FW_STAMPS; }
 namespace {
 
 struct XLayout {
-    uint32_t off_meta, off_cnt, off_hist, off_band_row, off_band_exact, off_xsum;
+    uint32_t off_meta, off_cnt, off_hist, off_band, off_xsum;
     size_t bytes;
 };
-XLayout x_layout(int hidden, int n_rows_global, int world) {
+XLayout x_layout(int hidden, int n_rows_global, int world) {  // everything in 16-byte lines
     XLayout x;
-    size_t o = 128;  // flags
-    x.off_meta = (uint32_t)o;        o += 128;
-    x.off_cnt = (uint32_t)o;         o += 128;
+    size_t o = 0;
+    x.off_meta = (uint32_t)o;  o += 256;
+    x.off_cnt = (uint32_t)o;   o += 256;
     o = 1024;
-    x.off_hist = (uint32_t)o;        o += (size_t)world * LQ_HIST_BINS * 4;
-    x.off_band_row = (uint32_t)o;    o += ((size_t)n_rows_global * 4 + 255) / 256 * 256;
-    x.off_band_exact = (uint32_t)o;  o += ((size_t)n_rows_global * 4 + 255) / 256 * 256;
-    x.off_xsum = (uint32_t)o;        o += (size_t)world * hidden * 4;
+    x.off_hist = (uint32_t)o;  o += (size_t)world * (LQ_HIST_BINS / 2) * 16;
+    x.off_band = (uint32_t)o;  o += ((size_t)n_rows_global * 16 + 255) / 256 * 256;
+    x.off_xsum = (uint32_t)o;  o += (size_t)world * (hidden / 2) * 16;
     x.bytes = (o + 255) / 256 * 256;
     return x;
 }
@@ -1634,7 +1673,7 @@ bool fused_q4k_sharded_supported(int hidden, int n_rows_local, int n_rows_global
 
 // One rank's launch of a sharded walk.  areas[r]: rank r's exchange area (fused_q4k_xarea_bytes(), zeroed
 // once when it was created) as mapped into this process; row_offsets[r]: first global row of rank r;
-// xepoch0: how many all-rank barriers earlier launches on these areas have passed (3 per layer).
+// xepoch0: how many layers earlier launches on these areas have walked (the exchange lines' epoch).
 cudaError_t launch_walk_fused_q4k_sharded(const void* layers_dev, int n_layers, int n_rows_local, int n_rows_global,
                                           int hidden, int top_k, uint32_t flags, float c1, const float* h_in,
                                           float* h_out, uint8_t* ws, uint32_t* hit_out, uint32_t* count_out,
@@ -1660,8 +1699,7 @@ cudaError_t launch_walk_fused_q4k_sharded(const void* layers_dev, int n_layers, 
     a.px.off_meta = x.off_meta;
     a.px.off_cnt = x.off_cnt;
     a.px.off_hist = x.off_hist;
-    a.px.off_band_row = x.off_band_row;
-    a.px.off_band_exact = x.off_band_exact;
+    a.px.off_band = x.off_band;
     a.px.off_xsum = x.off_xsum;
     for (int r = 0; r < world; ++r) {
         a.px.seg_off[r] = row_offsets[r];
