@@ -221,6 +221,21 @@ __device__ __forceinline__ void line_wait(const void* p, uint32_t epoch, uint32_
         }
     }
 }
+// The same line of every rank's slot (rank r's at base + r * rank_stride): all loads are issued before any
+// is looked at, so the usual case costs one round trip to L2 whatever the number of ranks.
+__device__ __forceinline__ void lines_wait_ranks(const uint4* base, size_t rank_stride, int world, uint32_t epoch,
+                                                 uint32_t (&w0)[FW_MAX_WORLD], uint32_t (&w1)[FW_MAX_WORLD], int* err) {
+    bool ok = true;
+#pragma unroll
+    for (int r = 0; r < FW_MAX_WORLD; ++r) {
+        w0[r] = w1[r] = 0u;
+        if (r < world) ok &= line_load(base + (size_t)r * rank_stride, epoch, w0[r], w1[r]);
+    }
+    if (ok) return;
+#pragma unroll
+    for (int r = 0; r < FW_MAX_WORLD; ++r)
+        if (r < world) line_wait(base + (size_t)r * rank_stride, epoch, w0[r], w1[r], err);
+}
 // size a multiple of 16, address 16-byte aligned; this GPU's own memory
 __device__ __forceinline__ void l2_prefetch_bulk(const void* src, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
@@ -552,11 +567,7 @@ __device__ __forceinline__ void prefetch_next_gate(const Smem& sm, int l) {
 }
 
 // ---- 0. prepare the activation ----------------------------------------------------------------
-// X (sharded walk): the residual of layer l > 0 is put together here, identically on every rank, from the
-// previous residual and every rank's partial output of layer l - 1 in rank order; the CTA that owns a
-// column slice keeps it in h_keep for the layer after.
-template <bool X>
-__device__ __noinline__ void phase_prepare(int l, const float* h_cur, float* h_keep) {
+__device__ __noinline__ void phase_prepare(int l, const float* h_cur) {
     extern __shared__ __align__(128) uint8_t smem[];  // the kernel's dynamic shared memory
     const Smem sm{smem};
     const Ctx& cx = sm.cx();
@@ -571,23 +582,8 @@ __device__ __noinline__ void phase_prepare(int l, const float* h_cur, float* h_k
     // pass 1: copy the residual into shared memory, sum of squares in f64
     double sq = 0.0;
     const float4* src = reinterpret_cast<const float4*>(h_cur);
-    const int per = (hidden / 4 + gridDim.x - 1) / gridDim.x, col0 = blockIdx.x * per;
     for (int i = tid; i < hidden / 4; i += FW_CONSUMERS) {
-        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (!X || l == 0 || (a.flags & LQ_WALK_RESIDUAL)) t = __ldcg(src + i);
-        if (X && l > 0) {
-            // layer l - 1's partial outputs: two lines per float4 and rank, taken as they arrive
-            const uint4* xsum = reinterpret_cast<const uint4*>(a.px.area[a.px.rank] + a.px.off_xsum);
-            const uint32_t ep = x_epoch(a, l - 1);
-            for (int r = 0; r < a.px.world; ++r) {
-                uint32_t w0, w1, w2, w3;
-                line_wait(xsum + (size_t)r * (hidden / 2) + 2 * i, ep, w0, w1, a.err);
-                line_wait(xsum + (size_t)r * (hidden / 2) + 2 * i + 1, ep, w2, w3, a.err);
-                t.x += __uint_as_float(w0); t.y += __uint_as_float(w1);
-                t.z += __uint_as_float(w2); t.w += __uint_as_float(w3);
-            }
-            if (i >= col0 && i < col0 + per) reinterpret_cast<float4*>(h_keep)[i] = t;
-        }
+        const float4 t = __ldcg(src + i);
         *reinterpret_cast<float4*>(xs + ((4 * i) >> 6) * 68 + ((4 * i) & 63)) = t;
         sq += (double)t.x * (double)t.x + (double)t.y * (double)t.y;
         sq += (double)t.z * (double)t.z + (double)t.w * (double)t.w;
@@ -826,13 +822,14 @@ __device__ __noinline__ void phase_select(int l) {
         if (X) {
             // positive floats order like their bits: the largest bound of any rank, the highest bin of any rank
             const uint4* meta = reinterpret_cast<const uint4*>(a.px.area[a.px.rank] + a.px.off_meta);
+            uint32_t wb[FW_MAX_WORLD], wm[FW_MAX_WORLD];
+            lines_wait_ranks(meta, 1, a.px.world, x_epoch(a, l), wb, wm, a.err);
             bbits = 0u;
             maxbin = 0u;
-            for (int r = 0; r < a.px.world; ++r) {
-                uint32_t b, m;
-                line_wait(meta + r, x_epoch(a, l), b, m, a.err);
-                bbits = max(bbits, b);
-                maxbin = max(maxbin, m);
+#pragma unroll
+            for (int r = 0; r < FW_MAX_WORLD; ++r) {  // (absent ranks read as zero)
+                bbits = max(bbits, wb[r]);
+                maxbin = max(maxbin, wm[r]);
             }
         } else {
             bbits = __ldcg(&a.ctrs[CTR_BOUND0 + par]);
@@ -850,11 +847,12 @@ __device__ __noinline__ void phase_select(int l) {
                     // every rank's four bins: two lines each, taken as they arrive
                     const uint4* hl = reinterpret_cast<const uint4*>(a.px.area[a.px.rank] + a.px.off_hist);
                     const uint32_t ep = x_epoch(a, l);
-                    for (int r = 0; r < a.px.world; ++r) {
-                        uint32_t w0, w1, w2, w3;
-                        line_wait(hl + (size_t)r * (LQ_HIST_BINS / 2) + b0 / 2, ep, w0, w1, a.err);
-                        line_wait(hl + (size_t)r * (LQ_HIST_BINS / 2) + b0 / 2 + 1, ep, w2, w3, a.err);
-                        t4.x += w0; t4.y += w1; t4.z += w2; t4.w += w3;
+                    uint32_t w0[FW_MAX_WORLD], w1[FW_MAX_WORLD], w2[FW_MAX_WORLD], w3[FW_MAX_WORLD];
+                    lines_wait_ranks(hl + b0 / 2, LQ_HIST_BINS / 2, a.px.world, ep, w0, w1, a.err);
+                    lines_wait_ranks(hl + b0 / 2 + 1, LQ_HIST_BINS / 2, a.px.world, ep, w2, w3, a.err);
+#pragma unroll
+                    for (int r = 0; r < FW_MAX_WORLD; ++r) {
+                        t4.x += w0[r]; t4.y += w1[r]; t4.z += w2[r]; t4.w += w3[r];
                     }
                 } else {
                     t4 = __ldcg(reinterpret_cast<const uint4*>(hist + b0));
@@ -1063,14 +1061,14 @@ __device__ __noinline__ void phase_pick(int l) {
     if (X) {
         // every rank's counts, as they arrive; this GPU's own say that its band and pool rows are all published
         const uint4* cnt = reinterpret_cast<const uint4*>(a.px.area[a.px.rank] + a.px.off_cnt);
+        uint32_t c_in[FW_MAX_WORLD], c_band[FW_MAX_WORLD];
+        lines_wait_ranks(cnt, 1, a.px.world, x_epoch(a, l), c_in, c_band, a.err);
         n_in_tot = 0;
         seg_pre[0] = 0;
 #pragma unroll
         for (int r = 0; r < FW_MAX_WORLD; ++r) {
-            uint32_t c_in = 0u, c_band = 0u;
-            if (r < a.px.world) line_wait(cnt + r, x_epoch(a, l), c_in, c_band, a.err);
-            n_in_tot += (int)c_in;
-            seg_pre[r + 1] = seg_pre[r] + (int)c_band;
+            n_in_tot += (int)c_in[r];
+            seg_pre[r + 1] = seg_pre[r] + (int)c_band[r];
         }
         __threadfence();  // the pool rows and counts below were written before the counts were sent
         n_band_tot = min(seg_pre[FW_MAX_WORLD], a.px.n_rows_global);
@@ -1367,8 +1365,7 @@ __device__ __noinline__ void phase_gather(int l) {
 }
 
 // ---- 4. finish: fixed-order sum of a column slice of the partials + residual --------------------
-// X: the slice sum goes, without the residual, into slot `rank` of every rank's xsum; the next prepare (or
-// the epilogue after the last layer) adds the slots up in rank order.
+// X: the slice sum first goes into slot `rank` of every rank's xsum, and the slots are added up in rank order.
 template <bool X>
 __device__ __noinline__ void phase_finish(const float* h_cur, float* h_next, uint32_t ep) {
     extern __shared__ __align__(128) uint8_t smem[];  // the kernel's dynamic shared memory
@@ -1400,19 +1397,31 @@ __device__ __noinline__ void phase_finish(const float* h_cur, float* h_next, uin
             t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
         }
         if (X) {
-            const size_t at = (size_t)a.px.rank * (hidden / 2) + 2 * (size_t)(col0 + tid);
+            // this rank's sums of the slice go to every rank; the slice of the layer's output is every rank's
+            // sums added up in rank order (the same on every rank), taken as they arrive
+            const size_t at = 2 * (size_t)(col0 + tid);
             for (int p = 0; p < a.px.world; ++p) {
-                uint4* xl = reinterpret_cast<uint4*>(a.px.area[p] + a.px.off_xsum) + at;
+                uint4* xl = reinterpret_cast<uint4*>(a.px.area[p] + a.px.off_xsum) + (size_t)a.px.rank * (hidden / 2) + at;
                 line_store(xl, __float_as_uint(t.x), __float_as_uint(t.y), ep);
                 line_store(xl + 1, __float_as_uint(t.z), __float_as_uint(t.w), ep);
             }
-        } else {
-            if (a.flags & LQ_WALK_RESIDUAL) {
-                const float4 hres = __ldcg(reinterpret_cast<const float4*>(h_cur) + col0 + tid);
-                t.x += hres.x; t.y += hres.y; t.z += hres.z; t.w += hres.w;
-            }
-            reinterpret_cast<float4*>(h_next)[col0 + tid] = t;
+            const uint4* xsum = reinterpret_cast<const uint4*>(a.px.area[a.px.rank] + a.px.off_xsum) + at;
+            t = make_float4(0.f, 0.f, 0.f, 0.f);
+            uint32_t w0[FW_MAX_WORLD], w1[FW_MAX_WORLD], w2[FW_MAX_WORLD], w3[FW_MAX_WORLD];
+            lines_wait_ranks(xsum, (size_t)(hidden / 2), a.px.world, ep, w0, w1, a.err);
+            lines_wait_ranks(xsum + 1, (size_t)(hidden / 2), a.px.world, ep, w2, w3, a.err);
+#pragma unroll
+            for (int r = 0; r < FW_MAX_WORLD; ++r)
+                if (r < a.px.world) {
+                    t.x += __uint_as_float(w0[r]); t.y += __uint_as_float(w1[r]);
+                    t.z += __uint_as_float(w2[r]); t.w += __uint_as_float(w3[r]);
+                }
         }
+        if (a.flags & LQ_WALK_RESIDUAL) {
+            const float4 hres = __ldcg(reinterpret_cast<const float4*>(h_cur) + col0 + tid);
+            t.x += hres.x; t.y += hres.y; t.z += hres.z; t.w += hres.w;
+        }
+        reinterpret_cast<float4*>(h_next)[col0 + tid] = t;
     }
     if (blockIdx.x == 0 && tid == 0) {
         a.ctrs[CTR_IN] = 0;
@@ -1474,7 +1483,7 @@ walk_fused_q4k_kernel(const __grid_constant__ FusedGeom gm_in, const __grid_cons
     for (int l = 0; l < n_layers; ++l) {
         float* h_next = (l + 1 == n_layers) ? a.h_out : ((l & 1) ? a.hbuf1 : a.hbuf0);
         FW_STAMP(0);
-        phase_prepare<false>(l, h_cur, nullptr);
+        phase_prepare(l, h_cur);
         FW_STAMP(1);
         phase_scan(l);
         FW_STAMP(2);
@@ -1505,9 +1514,9 @@ walk_fused_q4k_kernel(const __grid_constant__ FusedGeom gm_in, const __grid_cons
 //   threshold from every rank's histogram (lines taken as they arrive) and classification; own band rows to
 //   every rank, and once all of this GPU's CTAs have done so, its counts;
 //   final pick over every rank's band rows (the same on every CTA of every rank), gather of own rows;
-//   barrier over this GPU's CTAs; slice sums of the partials to every rank;
-//   the next layer's prepare (or the epilogue) adds up every rank's sums as they arrive.
-// Two barriers per layer, both local; the ranks wait for each other only where they read each other's lines.
+//   barrier over this GPU's CTAs; slice sums of the partials to every rank; every rank's sums of the slice,
+//   as they arrive, plus the residual make the slice of the next residual; barrier over this GPU's CTAs.
+// Three barriers per layer, all local; the ranks wait for each other only where they read each other's lines.
 __global__ void __launch_bounds__(FW_THREADS, 1)
 walk_fused_q4k_sharded_kernel(const __grid_constant__ FusedGeom gm_in, const __grid_constant__ FusedArgs a_in) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -1518,18 +1527,16 @@ walk_fused_q4k_sharded_kernel(const __grid_constant__ FusedGeom gm_in, const __g
     int* s_ctl = sm.ctl();
     uint32_t epoch = 0;
     bool failed = false;
-    const int n_layers = a.n_layers;
-    // residual entering layer l: h_in for l == 0, else kept by the slice owners in hbuf[l & 1]
     const float* h_cur = a.h_in;
+    const int n_layers = a.n_layers;
     for (int l = 0; l < n_layers; ++l) {
-        float* h_keep = (l & 1) ? a.hbuf1 : a.hbuf0;
+        float* h_next = (l + 1 == n_layers) ? a.h_out : ((l & 1) ? a.hbuf1 : a.hbuf0);
         FW_STAMP(0);
-        phase_prepare<true>(l, h_cur, h_keep);
-        if (l > 0) h_cur = h_keep;
+        phase_prepare(l, h_cur);
         FW_STAMP(1);
         phase_scan(l);
         FW_STAMP(2);
-        grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[SC_FAILED]);  // this GPU's histogram complete
+        grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[SC_FAILED]);  // A: this GPU's histogram complete
         phase_xhist(l);
         FW_STAMP(3);
         phase_select<true>(l);
@@ -1539,33 +1546,15 @@ walk_fused_q4k_sharded_kernel(const __grid_constant__ FusedGeom gm_in, const __g
         FW_STAMP(7);
         phase_gather(l);
         FW_STAMP(9);
-        grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[SC_FAILED]);  // this GPU's partials written
+        grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[SC_FAILED]);  // C: this GPU's partials written
         FW_STAMP(10);
-        phase_finish<true>(nullptr, nullptr, x_epoch(a, l));
+        phase_finish<true>(h_cur, h_next, x_epoch(a, l));
         FW_STAMP(11);
+        h_cur = h_next;
+        if (l + 1 < n_layers) grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[SC_FAILED]);  // D: next residual
         FW_STAMP(12);
     }
-    // epilogue: out = residual entering the last layer + every rank's partial output, own column slice
-    {
-        const int tid = threadIdx.x, hidden = cx.gm.nsb * 256, ncol4 = hidden / 4;
-        const int per = (ncol4 + gridDim.x - 1) / gridDim.x, col0 = blockIdx.x * per;
-        if (tid < per && col0 + tid < ncol4) {
-            const int i = col0 + tid;
-            float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (a.flags & LQ_WALK_RESIDUAL) t = __ldcg(reinterpret_cast<const float4*>(h_cur) + i);
-            const uint4* xsum = reinterpret_cast<const uint4*>(a.px.area[a.px.rank] + a.px.off_xsum);
-            const uint32_t ep = x_epoch(a, n_layers - 1);
-            for (int r = 0; r < a.px.world; ++r) {
-                uint32_t w0, w1, w2, w3;
-                line_wait(xsum + (size_t)r * (hidden / 2) + 2 * i, ep, w0, w1, a.err);
-                line_wait(xsum + (size_t)r * (hidden / 2) + 2 * i + 1, ep, w2, w3, a.err);
-                t.x += __uint_as_float(w0); t.y += __uint_as_float(w1);
-                t.z += __uint_as_float(w2); t.w += __uint_as_float(w3);
-            }
-            reinterpret_cast<float4*>(a.h_out)[i] = t;
-        }
-        if (a.count_out && blockIdx.x == 0 && tid == 0) *a.count_out = __ldcg(&a.ctrs[CTR_HITS]);
-    }
+    if (a.count_out && blockIdx.x == 0 && threadIdx.x == 0) *a.count_out = __ldcg(&a.ctrs[CTR_HITS]);
     if (failed || s_ctl[SC_FAILED]) set_err(a.err, DEV_ERR_TMA_TIMEOUT);
 }
 
