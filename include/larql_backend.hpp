@@ -143,6 +143,23 @@ public:
         return ok(lq_gemv_multi(ctx_, cm.data(), cm.size(), x, x_len, ptrs.data(), exact ? 1 : 0)) ? std::optional(std::move(outs))
                                                                                                 : std::nullopt;
     }
+    // QuantMatVec::q6k_matvec
+    std::optional<std::vector<float>> q6k_matvec(const uint8_t* w, size_t w_len, const float* x, size_t x_len,
+                                                 size_t num_rows, size_t hidden) {
+        std::vector<float> out(num_rows);
+        if (!ok(lq_q6k_matvec(ctx_, w, w_len, x, x_len, num_rows, hidden, out.data()))) return std::nullopt;
+        return out;
+    }
+    // QuantMatVec::q4k_dual_matvec: gate and up against one activation
+    std::optional<std::pair<std::vector<float>, std::vector<float>>> q4k_dual_matvec(const uint8_t* w_a, size_t wa_len,
+                                                                                     const uint8_t* w_b, size_t wb_len,
+                                                                                     const float* x, size_t x_len,
+                                                                                     size_t num_rows, size_t hidden) {
+        std::vector<float> a(num_rows), b(num_rows);
+        if (!ok(lq_q4k_dual_matvec(ctx_, w_a, wa_len, w_b, wb_len, x, x_len, num_rows, hidden, a.data(), b.data())))
+            return std::nullopt;
+        return std::make_pair(std::move(a), std::move(b));
+    }
     // QuantMatVec::q4k_matvec_topk: (row, score) sorted by score descending, ties to the lower row
     std::optional<std::vector<std::pair<uint32_t, float>>> q4k_matvec_topk(const uint8_t* w, size_t w_len, const float* x,
                                                                            size_t x_len, size_t num_rows, size_t hidden,

@@ -58,7 +58,7 @@ enum lq_status {
  *   MXFP4 : packed [rows,K/32,16] + e8m0 scales [rows,K/32] (crates/larql-models/src/quant/mxfp4.rs:1-9)
  *   NVFP4 : packed [rows,K/16,8] + e4m3 scales [rows,K/16] + f32 tensor scale
  *           (crates/larql-models/src/quant/nvfp4.rs:24-36)                              */
-enum lq_format { LQ_FMT_Q4_K = 0, LQ_FMT_Q8_0 = 1, LQ_FMT_MXFP4 = 2, LQ_FMT_NVFP4 = 3 };
+enum lq_format { LQ_FMT_Q4_K = 0, LQ_FMT_Q8_0 = 1, LQ_FMT_MXFP4 = 2, LQ_FMT_NVFP4 = 3, LQ_FMT_Q6_K = 4 };
 /* OR-ed into lq_matrix.fmt: data/scales are DEVICE pointers already (resident weights handed to
  * a host-pointer entry point; activations and outputs stay host memory). */
 #define LQ_MAT_DEVICE 0x100
@@ -170,6 +170,22 @@ LQ_API int lq_f16_gemv(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float*
                        float* out);
 LQ_API int lq_bf16_gemv(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t n, size_t k,
                         float* out);
+
+/* Q6_K (210-byte super-blocks of 256; rows need 2-byte alignment).  A walk takes Q6_K for any of gate / up /
+ * down beside Q4_K (the Ollama convention keeps down as Q6_K): the gate is scanned in the backend matvec's
+ * order, up and down rows go through the per-format row functions (crates/larql-vindex/src/quant/registry.rs;
+ * q6k_row_dot / q6k_row_scaled_add, crates/larql-models/src/quant/ggml/q6_k.rs:44-168).
+ *   lq_q6k_matvec     QuantMatVec::q6k_matvec (backend/quant_matvec.rs:336-344); arithmetic and order of
+ *                     crates/larql-compute/src/cpu/ops/q6k_matvec.rs:45-96 (bit-identical)
+ *   lq_dequantize_q6k dequantize_q6_k (crates/larql-models/src/quant/ggml/q6_k.rs:171-195)
+ *   lq_q4k_dual_matvec QuantMatVec::q4k_dual_matvec (backend/quant_matvec.rs:287-296): gate and up against one
+ *                     activation in one launch; order of crates/larql-compute/src/cpu/ops/q4_common/dual.rs:22-167 (one
+ *                     running sum per row; bit-identical) */
+LQ_API int lq_q6k_matvec(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t num_rows,
+                         size_t hidden, float* out);
+LQ_API int lq_dequantize_q6k(lq_ctx* ctx, const uint8_t* data, size_t data_len, size_t n_elems, float* out);
+LQ_API int lq_q4k_dual_matvec(lq_ctx* ctx, const uint8_t* w_a, size_t wa_len, const uint8_t* w_b, size_t wb_len,
+                              const float* x, size_t x_len, size_t num_rows, size_t hidden, float* out_a, float* out_b);
 
 /* LM-head style scan + top-k: QuantMatVec::q4k_matvec_topk (backend/quant_matvec.rs:268-277) and
  * MatMul::f16_gemv_topk (backend/matmul.rs:100-109).  Up to top_k (row, score) pairs sorted by score

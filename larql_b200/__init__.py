@@ -20,7 +20,7 @@ import numpy as np
 _HERE = Path(__file__).resolve().parent
 LIB_PATH = _HERE / "liblarql_b200.so"
 
-FMT_Q4_K, FMT_Q8_0, FMT_MXFP4, FMT_NVFP4 = 0, 1, 2, 3
+FMT_Q4_K, FMT_Q8_0, FMT_MXFP4, FMT_NVFP4, FMT_Q6_K = 0, 1, 2, 3, 4
 MAT_DEVICE = 0x100  # OR-ed into a matrix format: data/scales are device pointers
 WALK_RMSNORM, WALK_RESIDUAL, WALK_FORCE_SPARSE = 1, 2, 4
 
@@ -40,7 +40,7 @@ EXPORTS = [
     "lq_moe_walk_ffn", "lq_stack_run_host", "lq_dev_shard_hits", "lq_gemv_multi", "lq_mxfp4_gemv_multi",
     "lq_nvfp4_gemv_multi", "lq_gemv16", "lq_gemv16_multi", "lq_f16_gemv", "lq_bf16_gemv", "lq_q4k_matvec_topk",
     "lq_gemv16_topk", "lq_f16_gemv_topk", "lq_comm_unique_id", "lq_comm_init", "lq_comm_destroy",
-    "lq_stack_create_sharded", "lq_stack_path",
+    "lq_stack_create_sharded", "lq_stack_path", "lq_q6k_matvec", "lq_dequantize_q6k", "lq_q4k_dual_matvec",
 ]
 
 
@@ -99,6 +99,9 @@ def load_library() -> C.CDLL:
         "lq_dev_shard_hits": (C.c_int, [vp, u32p, sz, C.POINTER(sz)]),
         "lq_stack_destroy": (None, [vp, vp]),
         "lq_stack_path": (C.c_int, [vp]),
+        "lq_q6k_matvec": (C.c_int, [vp, vp, sz, f32p, sz, sz, sz, f32p]),
+        "lq_dequantize_q6k": (C.c_int, [vp, vp, sz, sz, f32p]),
+        "lq_q4k_dual_matvec": (C.c_int, [vp, vp, sz, vp, sz, f32p, sz, sz, sz, f32p, f32p]),
         "lq_last_walk_stats": (C.c_int, [vp, C.POINTER(WalkStats)]),
         "lq_dev_quantize_q4k": (C.c_int, [vp, f32p, sz, vp]),
         "lq_profile_walk": (C.c_int, [vp, mp, mp, mp, f32p, sz, C.c_uint32, f32p, f32p]),
@@ -351,6 +354,27 @@ class CudaBackend:
         ok = self._status(self._lib.lq_gemv16_multi(self._h, 0 if kind == "f16" else 1, m, wp, wl, nn, x.size, _ptr(x),
                                                     x.size, op, int(exact)))
         return outs if ok else None
+
+    def q6k_matvec(self, q6k_data, x, num_rows: int, hidden: int):
+        """QuantMatVec::q6k_matvec; None on a shape refusal."""
+        w, x = _u8(q6k_data), _f32(x).reshape(-1)
+        out = np.empty(num_rows, np.float32)
+        ok = self._status(self._lib.lq_q6k_matvec(self._h, _ptr(w), w.size, _ptr(x), x.size, num_rows, hidden, _ptr(out)))
+        return out if ok else None
+
+    def dequantize_q6k(self, data, n_elems: int):
+        d = _u8(data)
+        out = np.empty(n_elems, np.float32)
+        ok = self._status(self._lib.lq_dequantize_q6k(self._h, _ptr(d), d.size, n_elems, _ptr(out)))
+        return out if ok else None
+
+    def q4k_dual_matvec(self, q4k_a, q4k_b, x, num_rows: int, hidden: int):
+        """QuantMatVec::q4k_dual_matvec: (out_a, out_b); None on a shape refusal."""
+        a, b, x = _u8(q4k_a), _u8(q4k_b), _f32(x).reshape(-1)
+        oa, ob = np.empty(num_rows, np.float32), np.empty(num_rows, np.float32)
+        ok = self._status(self._lib.lq_q4k_dual_matvec(self._h, _ptr(a), a.size, _ptr(b), b.size, _ptr(x), x.size,
+                                                       num_rows, hidden, _ptr(oa), _ptr(ob)))
+        return (oa, ob) if ok else None
 
     def q4k_matvec_topk(self, q4k_data, x, num_rows: int, hidden: int, top_k: int):
         """QuantMatVec::q4k_matvec_topk: [(row, score)] sorted by score descending, ties to the lower row."""

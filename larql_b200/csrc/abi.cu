@@ -190,6 +190,7 @@ size_t row_bytes_of(int fmt, int64_t cols) {
         case LQ_FMT_Q8_0: return (size_t)(cols / 32) * 34;
         case LQ_FMT_MXFP4: return (size_t)(cols / 32) * 16;
         case LQ_FMT_NVFP4: return (size_t)(cols / 16) * 8;
+        case LQ_FMT_Q6_K: return (size_t)(cols / 256) * 210;
     }
     return 0;
 }
@@ -203,6 +204,10 @@ int check_matrix(lq_ctx* ctx, const lq_matrix* m, const char* name) {
         case LQ_FMT_Q4_K:
             if (k % 256 != 0 || m->data_len < (size_t)r * row_bytes_of(LQ_FMT_Q4_K, k))
                 return fail(ctx, LQ_REFUSED_SHAPE, std::string(name) + ": Q4_K geometry");
+            break;
+        case LQ_FMT_Q6_K:
+            if (k % 256 != 0 || m->data_len < (size_t)r * row_bytes_of(LQ_FMT_Q6_K, k))
+                return fail(ctx, LQ_REFUSED_SHAPE, std::string(name) + ": Q6_K geometry");
             break;
         case LQ_FMT_Q8_0:
             if (k == 0 || k % 32 != 0 || m->data_len != (size_t)r * row_bytes_of(LQ_FMT_Q8_0, k))
@@ -418,6 +423,8 @@ bool fmt_aligned(const lq_matrix& m) {
     const uintptr_t a = (uintptr_t)m.data;
     switch (m.fmt & 0xff) {
         case LQ_FMT_Q8_0: return (a & 1) == 0;
+        case LQ_FMT_Q6_K: return (a & 1) == 0;
+        case LQ_FMT_Q4_K: return (a & 15) == 0;
         case LQ_FMT_MXFP4: return (a & 15) == 0;
         case LQ_FMT_NVFP4: return (a & 7) == 0;
     }
@@ -460,10 +467,56 @@ int enqueue_walk_token_fmt(lq_ctx* ctx, const lq_matrix& gate, const lq_matrix& 
 // Enqueue the walk of one prepared token.
 int enqueue_walk_token(lq_ctx* ctx, const lq_matrix& gate, const lq_matrix& up, const lq_matrix& down, size_t t,
                        size_t top_k, const float* residual, float* out) {
-    if (gate.fmt != up.fmt || gate.fmt != down.fmt)
-        return fail(ctx, LQ_REFUSED_UNSUPPORTED, "walk: gate/up/down formats differ");
+    auto kquant = [](int f) { return f == LQ_FMT_Q4_K || f == LQ_FMT_Q6_K; };
+    const bool mixed_kq = kquant(gate.fmt) && kquant(up.fmt) && kquant(down.fmt) &&
+                          !(gate.fmt == LQ_FMT_Q4_K && up.fmt == LQ_FMT_Q4_K && down.fmt == LQ_FMT_Q4_K);
+    if (!mixed_kq && (gate.fmt != up.fmt || gate.fmt != down.fmt))
+        return fail(ctx, LQ_REFUSED_UNSUPPORTED, "walk: gate/up/down formats differ (only Q4_K and Q6_K mix)");
     TokenWs& w = ctx->tok[t];
     const int N = (int)gate.rows, H = (int)gate.cols;
+    if (mixed_kq) {
+        // Q4_K / Q6_K in any mix: the gate by its own format's scan, the rows by the K-quant gather
+        if (H % 256 != 0) return fail(ctx, LQ_REFUSED_SHAPE, "walk: K-quant rows need hidden % 256 == 0");
+        if (!fmt_aligned(gate) || !fmt_aligned(up) || !fmt_aligned(down))
+            return fail(ctx, LQ_ERR_ARGUMENT, "walk: weight base address not block aligned");
+        const int k = (int)std::min<size_t>(top_k, (size_t)N);
+        cudaStream_t st = ctx->stream;
+        if (k == 0) {
+            CK(cudaMemsetAsync(w.sel, 0, sizeof(SelHeader), st));
+            if (residual) CK(cudaMemcpyAsync(out, residual, (size_t)H * 4, cudaMemcpyDeviceToDevice, st));
+            else CK(cudaMemsetAsync(out, 0, (size_t)H * 4, st));
+            return LQ_OK;
+        }
+        const bool sparse = k < N;
+        if (gate.fmt == LQ_FMT_Q4_K) {
+            const Q4kMat g{(const uint8_t*)gate.data, N, H};
+            CK(launch_scan_q4k(g, xprep_of(w), w.scores, sparse ? w.hist : nullptr, &w.sel->bound_bits, bound_c1(H),
+                               ctx->d_err, ctx->sm_count, st));
+            if (sparse) {
+                CK(launch_classify(w.scores, N, k, w, ctx->d_err, st));
+                CK(launch_rescore_q4k(g, w.xn, w.band_idx, &w.sel->n_band, 0, w.band_exact, w, k, 1, ctx->d_err,
+                                      ctx->sm_count, st));
+                ctx->launches += 1;
+            } else
+                CK(launch_select(w.scores, N, k, w, ctx->d_err, st));
+            ctx->launches += 2;
+        } else {
+            // the Q6_K matvec kernel runs in the reference's order: its scores are the reference's scores
+            CK(launch_q6k_matvec((const uint8_t*)gate.data, w.xn, nullptr, nullptr, N, H, w.scores, ctx->d_err,
+                                 ctx->sm_count, st));
+            CK(launch_select(w.scores, N, k, w, ctx->d_err, st));
+            ctx->launches += 2;
+            if (sparse) {
+                CK(launch_final_pick(w, ctx->d_err, st));
+                ctx->launches += 1;
+            }
+        }
+        CK(launch_gather_kquant(up.fmt, (const uint8_t*)up.data, down.fmt, (const uint8_t*)down.data, w.xn, H, w.hit_idx,
+                                w.hit_score, &w.sel->n_sel, k, ctx->partials, ctx->gather_grid, st));
+        CK(launch_finish(ctx->partials, ctx->gather_grid, H, residual, out, st));
+        ctx->launches += 2;
+        return LQ_OK;
+    }
     if (gate.fmt != LQ_FMT_Q4_K) {
         const int kk = (int)std::min<size_t>(top_k, (size_t)N);
         if (kk == 0) {
@@ -812,6 +865,11 @@ int lq_gemv(lq_ctx* ctx, const lq_matrix* m, const float* x, size_t x_len, float
     const size_t n = (size_t)m->rows, k = (size_t)m->cols;
     if (fmt == LQ_FMT_Q4_K)
         return q4k_host_common(ctx, (const uint8_t*)m->data, m->data_len, x, x_len, n, k, 1, out, out_len, exact);
+    if (fmt == LQ_FMT_Q6_K) {
+        if (out_len != n) return fail(ctx, LQ_REFUSED_SHAPE, "gemv: out_len != n");
+        if (m->fmt & LQ_MAT_DEVICE) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "gemv: Q6_K takes host weights here");
+        return lq_q6k_matvec(ctx, (const uint8_t*)m->data, m->data_len, x, x_len, n, k, out);
+    }
     if (x_len != k || out_len != n) return fail(ctx, LQ_REFUSED_SHAPE, "gemv: x_len != k or out_len != n");
     if (n == 0) return LQ_OK;
     if (k % 32 != 0 || k > 16384) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "gemv: k must be a multiple of 32, <= 16384");
@@ -838,6 +896,86 @@ int lq_gemv(lq_ctx* ctx, const lq_matrix* m, const float* x, size_t x_len, float
         ctx->launches += 2;
     }
     CK(cudaMemcpyAsync(out, dout, n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return lq_synchronize(ctx);
+}
+
+int lq_q6k_matvec(lq_ctx* ctx, const uint8_t* w, size_t w_len, const float* x, size_t x_len, size_t num_rows,
+                  size_t hidden, float* out) {
+    DevGuard dev_guard(ctx);
+    if (!ctx) return LQ_ERR_ARGUMENT;
+    // KernelShapeError-style refusal: the caller falls back to its CPU path
+    if (hidden % 256 != 0 || x_len != hidden || w_len < num_rows * (hidden / 256) * 210)
+        return fail(ctx, LQ_REFUSED_SHAPE, "q6k_matvec: shape");
+    if (num_rows == 0 || hidden == 0) return LQ_OK;
+    if (hidden > 16384) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "q6k_matvec: hidden > 16384");
+    if (!w || !x || !out) return LQ_ERR_ARGUMENT;
+    const lq_matrix hm{LQ_FMT_Q6_K, w, w_len, nullptr, 0, 1.0f, (int64_t)num_rows, (int64_t)hidden};
+    lq_matrix dm;
+    int rc = resolve_matrix(ctx, &hm, &dm);
+    if (rc) return rc;
+    if (!fmt_aligned(dm)) return fail(ctx, LQ_ERR_ARGUMENT, "q6k_matvec: weights not 2-byte aligned");
+    rc = ensure_stage(ctx, (hidden + num_rows) * 4 + 512);
+    if (rc) return rc;
+    float* dx = (float*)ctx->stage;
+    float* dout = (float*)(ctx->stage + a256(hidden * 4));
+    CK(cudaMemcpyAsync(dx, x, hidden * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CK(launch_q6k_matvec((const uint8_t*)dm.data, dx, nullptr, nullptr, (int)num_rows, (int)hidden, dout, nullptr,
+                         ctx->sm_count, ctx->stream));
+    ctx->launches += 1;
+    CK(cudaMemcpyAsync(out, dout, num_rows * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return lq_synchronize(ctx);
+}
+
+int lq_dequantize_q6k(lq_ctx* ctx, const uint8_t* data, size_t data_len, size_t n_elems, float* out) {
+    DevGuard dev_guard(ctx);
+    if (!ctx) return LQ_ERR_ARGUMENT;
+    if (n_elems % 256 != 0 || data_len < n_elems / 256 * 210) return fail(ctx, LQ_REFUSED_SHAPE, "dequantize_q6k: shape");
+    if (n_elems == 0) return LQ_OK;
+    if (!data || !out) return LQ_ERR_ARGUMENT;
+    const size_t bytes = n_elems / 256 * 210;
+    int rc = ensure_stage(ctx, a256(bytes) + n_elems * 4 + 512);
+    if (rc) return rc;
+    uint8_t* dsrc = ctx->stage;
+    float* dout = (float*)(ctx->stage + a256(bytes));
+    CK(cudaMemcpyAsync(dsrc, data, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    CK(launch_q6k_dequant(dsrc, n_elems, dout, ctx->stream));
+    ctx->launches += 1;
+    CK(cudaMemcpyAsync(out, dout, n_elems * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return lq_synchronize(ctx);
+}
+
+int lq_q4k_dual_matvec(lq_ctx* ctx, const uint8_t* w_a, size_t wa_len, const uint8_t* w_b, size_t wb_len, const float* x,
+                       size_t x_len, size_t num_rows, size_t hidden, float* out_a, float* out_b) {
+    DevGuard dev_guard(ctx);
+    if (!ctx) return LQ_ERR_ARGUMENT;
+    const size_t need = num_rows * (hidden / 256) * 144;
+    if (hidden % 256 != 0 || x_len != hidden || wa_len < need || wb_len < need)
+        return fail(ctx, LQ_REFUSED_SHAPE, "q4k_dual_matvec: shape");
+    if (!out_a || !out_b) return LQ_ERR_ARGUMENT;
+    if (num_rows == 0 || hidden == 0) {  // dual.rs:54-58
+        for (size_t i = 0; i < num_rows; ++i) out_a[i] = out_b[i] = 0.0f;
+        return LQ_OK;
+    }
+    if (hidden > 16384) return fail(ctx, LQ_REFUSED_UNSUPPORTED, "q4k_dual_matvec: hidden > 16384");
+    if (!w_a || !w_b || !x) return LQ_ERR_ARGUMENT;
+    const lq_matrix ha{LQ_FMT_Q4_K, w_a, wa_len, nullptr, 0, 1.0f, (int64_t)num_rows, (int64_t)hidden};
+    const lq_matrix hb{LQ_FMT_Q4_K, w_b, wb_len, nullptr, 0, 1.0f, (int64_t)num_rows, (int64_t)hidden};
+    lq_matrix da, db;
+    int rc;
+    if ((rc = resolve_matrix(ctx, &ha, &da)) || (rc = resolve_matrix(ctx, &hb, &db))) return rc;
+    if ((((uintptr_t)da.data | (uintptr_t)db.data) & 15) != 0)
+        return fail(ctx, LQ_ERR_ARGUMENT, "q4k_dual_matvec: weights not 16-byte aligned");
+    rc = ensure_stage(ctx, a256(hidden * 4) + 2 * a256(num_rows * 4) + 512);
+    if (rc) return rc;
+    float* dx = (float*)ctx->stage;
+    float* doa = (float*)(ctx->stage + a256(hidden * 4));
+    float* dob = (float*)((uint8_t*)doa + a256(num_rows * 4));
+    CK(cudaMemcpyAsync(dx, x, hidden * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CK(launch_q4k_dual_matvec((const uint8_t*)da.data, (const uint8_t*)db.data, dx, (int)num_rows, (int)hidden, doa, dob,
+                              ctx->sm_count, ctx->stream));
+    ctx->launches += 1;
+    CK(cudaMemcpyAsync(out_a, doa, num_rows * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CK(cudaMemcpyAsync(out_b, dob, num_rows * 4, cudaMemcpyDeviceToHost, ctx->stream));
     return lq_synchronize(ctx);
 }
 

@@ -139,6 +139,16 @@ cudaError_t launch_topk_value_sorted(const float* scores, int n, int top_k, uint
 // dense16.cu: gemv over f16 (kind 0) / bf16 (kind 1) weights [n, k]; exact = the reference loop's order
 cudaError_t launch_gemv16(const void* w, const float* x, int n, int k, int kind, int exact, float* out, cudaStream_t st);
 
+// kquant_rows.cu: Q6_K rows, the walk's gather with up / down each Q4_K or Q6_K, the fused gate+up matvec
+cudaError_t launch_q6k_matvec(const uint8_t* w, const float* x, const uint32_t* rows_idx, const int* n_rows_dev,
+                              int n_rows, int cols, float* out, int* err, int sm_count, cudaStream_t st);
+cudaError_t launch_q6k_dequant(const uint8_t* data, size_t n_elems, float* out, cudaStream_t st);
+cudaError_t launch_gather_kquant(int up_fmt, const uint8_t* up, int down_fmt, const uint8_t* down, const float* xn,
+                                 int cols, const uint32_t* hit_idx, const float* hit_score, const int* n_hits_dev,
+                                 int n_hits_host, float* partials, int grid, cudaStream_t st);
+cudaError_t launch_q4k_dual_matvec(const uint8_t* wa, const uint8_t* wb, const float* x, int rows, int cols,
+                                   float* out_a, float* out_b, int sm_count, cudaStream_t st);
+
 // gather_q4k.cu
 int gather_q4k_grid(int sm_count);
 cudaError_t launch_gather_q4k(const Q4kMat& up, const Q4kMat& down, const XPrep& xp, const uint32_t* hit_idx,

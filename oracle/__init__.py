@@ -21,8 +21,8 @@ _HERE = Path(__file__).resolve().parent
 _SRC = _HERE / "larql_oracle.c"
 _SO = _HERE / "_build" / "liblarql_oracle.so"
 
-FMT_Q4_K, FMT_Q8_0, FMT_MXFP4, FMT_NVFP4 = 0, 1, 2, 3
-FMT_NAMES = {FMT_Q4_K: "q4_k", FMT_Q8_0: "q8_0", FMT_MXFP4: "mxfp4", FMT_NVFP4: "nvfp4"}
+FMT_Q4_K, FMT_Q8_0, FMT_MXFP4, FMT_NVFP4, FMT_Q6_K = 0, 1, 2, 3, 4
+FMT_NAMES = {FMT_Q4_K: "q4_k", FMT_Q8_0: "q8_0", FMT_MXFP4: "mxfp4", FMT_NVFP4: "nvfp4", FMT_Q6_K: "q6_k"}
 
 
 def build(force: bool = False) -> Path:
@@ -68,6 +68,7 @@ def lib():
         f.orc_nearest_mxfp4_code.restype = C.c_uint8
         f.orc_nearest_mxfp4_code.argtypes = [C.c_float]
         f.orc_q4k_row_dot.restype = C.c_float
+        f.orc_q6k_row_dot.restype = C.c_float
         f.orc_nvfp4_tensor_scale_for.restype = C.c_float
         f.orc_sigmoid.restype = C.c_float
         f.orc_sigmoid.argtypes = [C.c_float]
@@ -155,6 +156,22 @@ def dequantize_q4_k(data, n: int) -> np.ndarray:
     return out
 
 
+def quantize_q6_k(data) -> np.ndarray:
+    d = _f32(data).reshape(-1)
+    assert d.size % 256 == 0, "data length must be a multiple of 256"
+    out = np.empty(d.size // 256 * 210, np.uint8)
+    lib().orc_quantize_q6_k(_p(d), _sz(d.size), _p(out))
+    return out
+
+
+def dequantize_q6_k(data, n: int) -> np.ndarray:
+    b = _u8(data)
+    assert n % 256 == 0 and b.size >= n // 256 * 210
+    out = np.empty(n, np.float32)
+    lib().orc_dequantize_q6_k(_p(b), _sz(n), _p(out))
+    return out
+
+
 def quantize_q8_0(data) -> np.ndarray:
     d = _f32(data).reshape(-1)
     assert d.size % 32 == 0
@@ -222,6 +239,36 @@ def q4k_matvec(w, x, rows: int, cols: int):
     out = np.empty(rows, np.float32)
     rc = lib().orc_q4k_matvec(_p(w), _sz(w.size), _p(x), _sz(x.size), _sz(rows), _sz(cols), _p(out), _sz(rows))
     return None if rc else out
+
+
+def q6k_matvec(w, x, rows: int, cols: int):
+    """Backend q6k_matvec (per sub-block sum, then acc += sc * sub). None on a shape refusal."""
+    w = _u8(w)
+    x = _f32(x)
+    out = np.empty(rows, np.float32)
+    rc = lib().orc_q6k_matvec(_p(w), _sz(w.size), _p(x), _sz(x.size), _sz(rows), _sz(cols), _p(out))
+    return None if rc else out
+
+
+def q6k_row_dot(row, x) -> np.float32:
+    row = _u8(row)
+    x = _f32(x)
+    return np.float32(lib().orc_q6k_row_dot(_p(row), _p(x), _sz(x.size)))
+
+
+def q6k_row_scaled_add(row, alpha: float, out: np.ndarray) -> None:
+    row = _u8(row)
+    assert out.dtype == np.float32 and out.flags.c_contiguous
+    lib().orc_q6k_row_scaled_add(_p(row), C.c_float(alpha), _p(out), _sz(out.size))
+
+
+def q4k_dual_matvec(w_a, w_b, x, rows: int, cols: int):
+    """Gate and up against one activation (q4k_dual_matvec_into): one running sum per row. None on a refusal."""
+    w_a, w_b, x = _u8(w_a), _u8(w_b), _f32(x)
+    out_a, out_b = np.empty(rows, np.float32), np.empty(rows, np.float32)
+    rc = lib().orc_q4k_dual_matvec(_p(w_a), _sz(w_a.size), _p(w_b), _sz(w_b.size), _p(x), _sz(x.size), _sz(rows),
+                                   _sz(cols), _p(out_a), _p(out_b))
+    return None if rc else (out_a, out_b)
 
 
 def q4k_row_dot(row, x) -> np.float32:
@@ -337,7 +384,7 @@ def moe_route(logits, top_k: int, renormalise: bool = True):
 
 # ----------------------------------------------------------------- walk
 class Matrix:
-    """A quantised [rows, cols] matrix in one of the four formats (host memory)."""
+    """A quantised [rows, cols] matrix in one of the block formats (host memory)."""
 
     def __init__(self, fmt: int, rows: int, cols: int, data, scales=None, tensor_scale: float = 1.0):
         self.fmt, self.rows, self.cols = fmt, rows, cols
@@ -355,13 +402,15 @@ class Matrix:
 
     def row_bytes(self) -> int:
         return {FMT_Q4_K: self.cols // 256 * 144, FMT_Q8_0: self.cols // 32 * 34, FMT_MXFP4: self.cols // 32 * 16,
-                FMT_NVFP4: self.cols // 16 * 8}[self.fmt]
+                FMT_NVFP4: self.cols // 16 * 8, FMT_Q6_K: self.cols // 256 * 210}[self.fmt]
 
     def gemv(self, x):
         if self.fmt == FMT_Q4_K:
             return q4k_matvec(self.data, x, self.rows, self.cols)
         if self.fmt == FMT_Q8_0:
             return q8_0_gemv(self.data, x, self.rows, self.cols)
+        if self.fmt == FMT_Q6_K:
+            return q6k_matvec(self.data, x, self.rows, self.cols)
         if self.fmt == FMT_MXFP4:
             return mxfp4_gemv(self.data, self.scales, x, self.rows, self.cols)
         return nvfp4_gemv(self.data, self.scales, self.tensor_scale, x, self.rows, self.cols)
@@ -372,6 +421,8 @@ class Matrix:
             return dequantize_q4_k(self.data, n).reshape(self.rows, self.cols)
         if self.fmt == FMT_Q8_0:
             return dequantize_q8_0(self.data, n).reshape(self.rows, self.cols)
+        if self.fmt == FMT_Q6_K:
+            return dequantize_q6_k(self.data, n).reshape(self.rows, self.cols)
         if self.fmt == FMT_MXFP4:
             return dequantize_mxfp4(self.data, self.scales, self.rows, self.cols // 32).reshape(self.rows, self.cols)
         return dequantize_nvfp4(self.data, self.scales, self.tensor_scale, self.rows, self.cols).reshape(
@@ -386,6 +437,8 @@ def quantize_matrix(fmt: int, w) -> Matrix:
         return Matrix(fmt, rows, cols, quantize_q4_k(w))
     if fmt == FMT_Q8_0:
         return Matrix(fmt, rows, cols, quantize_q8_0(w))
+    if fmt == FMT_Q6_K:
+        return Matrix(fmt, rows, cols, quantize_q6_k(w))
     if fmt == FMT_MXFP4:
         p, s = quantize_mxfp4(w, rows, cols)
         return Matrix(fmt, rows, cols, p, s)

@@ -448,6 +448,181 @@ ORC_API int orc_q4k_matmul(const uint8_t *w, size_t w_len, const float *x, size_
 
 /* ------------------------------------------------------------- Q8_0 ----- */
 
+/* ------------------------------------------------------------ Q6_K ----- */
+/* 256 values in 210 bytes: ql[128] low nibbles, qh[64] high bit pairs, 16 int8
+ * sub-block scales, f16 d.  The 16 signed values of scale sub-block j:
+ * q6k_subblock_vals, crates/larql-models/src/quant/ggml/q6_k.rs:19-42. */
+static void q6k_subblock_vals(const uint8_t *block, int j, int8_t *out) {
+    const uint8_t *ql = block, *qh = block + 128;
+    int half = j / 8, g = j % 8, plane = g / 2, lbase = (g % 2) * 16;
+    int ql_off = half * 64 + (plane & 1) * 32 + lbase, qh_off = half * 32 + lbase, shift = plane * 2;
+    for (int i = 0; i < 16; i++) {
+        int lo4 = plane < 2 ? (ql[ql_off + i] & 0x0F) : (ql[ql_off + i] >> 4);
+        int hi2 = (qh[qh_off + i] >> shift) & 0x03;
+        out[i] = (int8_t)((lo4 | (hi2 << 4)) - 32);
+    }
+}
+
+/* quantize_q6_k, crates/larql-compute/src/cpu/ops/q4_common/quantize.rs:198-277.
+ * roundf is round-half-away-from-zero like f32::round. */
+ORC_API void orc_quantize_q6_k(const float *data, size_t n, uint8_t *out) {
+    for (size_t sb = 0; sb < n / 256; sb++) {
+        const float *block = data + sb * 256;
+        uint8_t *o = out + sb * 210;
+        float amax = 0.0f;
+        for (int i = 0; i < 256; i++) { float a = fabsf(block[i]); if (a > amax) amax = a; }
+        float d = amax / (31.0f * 127.0f);
+        int8_t sub_scales[16];
+        for (int j = 0; j < 16; j++) {
+            float sub_max = 0.0f;
+            for (int i = 0; i < 16; i++) { float a = fabsf(block[j * 16 + i]); if (a > sub_max) sub_max = a; }
+            float sc = d > 0.0f ? sub_max / (31.0f * d) : 0.0f;
+            float r = roundf(sc);
+            if (r < -128.0f) r = -128.0f;
+            if (r > 127.0f) r = 127.0f;
+            sub_scales[j] = (int8_t)r;
+        }
+        uint8_t q6[256];
+        for (int j = 0; j < 16; j++) {
+            float sc = d * (float)sub_scales[j];
+            float inv_sc = fabsf(sc) > 1e-10f ? 1.0f / sc : 0.0f;
+            for (int i = 0; i < 16; i++) {
+                float r = roundf(block[j * 16 + i] * inv_sc);
+                if (r < -32.0f) r = -32.0f;
+                if (r > 31.0f) r = 31.0f;
+                q6[j * 16 + i] = (uint8_t)((int)r + 32);
+            }
+        }
+        uint8_t *ql = o, *qh = o + 128;
+        for (int half = 0; half < 2; half++) {
+            int e = half * 128;
+            for (int l = 0; l < 32; l++) {
+                uint8_t q1 = q6[e + l], q2 = q6[e + l + 32], q3 = q6[e + l + 64], q4 = q6[e + l + 96];
+                ql[half * 64 + l] = (uint8_t)((q1 & 0x0F) | ((q3 & 0x0F) << 4));
+                ql[half * 64 + l + 32] = (uint8_t)((q2 & 0x0F) | ((q4 & 0x0F) << 4));
+                qh[half * 32 + l] = (uint8_t)(((q1 >> 4) & 3) | (((q2 >> 4) & 3) << 2) | (((q3 >> 4) & 3) << 4) |
+                                              (((q4 >> 4) & 3) << 6));
+            }
+        }
+        for (int j = 0; j < 16; j++) o[192 + j] = (uint8_t)sub_scales[j];
+        uint16_t dh = orc_f32_to_f16_trunc(d);
+        o[208] = (uint8_t)(dh & 0xff);
+        o[209] = (uint8_t)(dh >> 8);
+    }
+}
+
+/* dequantize_q6_k, q6_k.rs:171-195: value = (d * scale_j) * q. */
+ORC_API void orc_dequantize_q6_k(const uint8_t *data, size_t n, float *out) {
+    for (size_t sb = 0; sb < n / 256; sb++) {
+        const uint8_t *block = data + sb * 210;
+        float d = orc_f16_to_f32((uint16_t)(block[208] | (block[209] << 8)));
+        for (int j = 0; j < 16; j++) {
+            float sc = d * (float)(int8_t)block[192 + j];
+            int8_t v[16];
+            q6k_subblock_vals(block, j, v);
+            for (int i = 0; i < 16; i++) out[sb * 256 + j * 16 + i] = sc * (float)v[i];
+        }
+    }
+}
+
+/* q6k_row_dot_scalar (the arm taken on x86), q6_k.rs:70-88: one running sum,
+ * acc += (sc * v) * x per element. */
+ORC_API float orc_q6k_row_dot(const uint8_t *data, const float *x, size_t n) {
+    float acc = 0.0f;
+    for (size_t sb = 0; sb < n / 256; sb++) {
+        const uint8_t *block = data + sb * 210;
+        float d = orc_f16_to_f32((uint16_t)(block[208] | (block[209] << 8)));
+        for (int j = 0; j < 16; j++) {
+            float sc = d * (float)(int8_t)block[192 + j];
+            int8_t v[16];
+            q6k_subblock_vals(block, j, v);
+            for (int i = 0; i < 16; i++) acc += sc * (float)v[i] * x[sb * 256 + j * 16 + i];
+        }
+    }
+    return acc;
+}
+
+/* q6k_row_scaled_add, q6_k.rs:142-168: out += (alpha * sc) * v. */
+ORC_API void orc_q6k_row_scaled_add(const uint8_t *data, float alpha, float *out, size_t n) {
+    for (size_t sb = 0; sb < n / 256; sb++) {
+        const uint8_t *block = data + sb * 210;
+        float d = orc_f16_to_f32((uint16_t)(block[208] | (block[209] << 8)));
+        for (int j = 0; j < 16; j++) {
+            float sc = d * (float)(int8_t)block[192 + j];
+            int8_t v[16];
+            q6k_subblock_vals(block, j, v);
+            for (int i = 0; i < 16; i++) out[sb * 256 + j * 16 + i] += alpha * sc * (float)v[i];
+        }
+    }
+}
+
+/* One row of the backend matvec, crates/larql-compute/src/cpu/ops/q6k_matvec.rs:45-96:
+ * per sub-block sub = sum v*x (sequential), acc += sc * sub. */
+static float q6k_matvec_row(const uint8_t *row, const float *x, size_t nsb) {
+    float acc = 0.0f;
+    for (size_t sb = 0; sb < nsb; sb++) {
+        const uint8_t *block = row + sb * 210;
+        float d = orc_f16_to_f32((uint16_t)(block[208] | (block[209] << 8)));
+        for (int j = 0; j < 16; j++) {
+            float sc = d * (float)(int8_t)block[192 + j];
+            int8_t v[16];
+            q6k_subblock_vals(block, j, v);
+            float sub = 0.0f;
+            for (int i = 0; i < 16; i++) sub += (float)v[i] * x[sb * 256 + j * 16 + i];
+            acc += sc * sub;
+        }
+    }
+    return acc;
+}
+
+ORC_API int orc_q6k_matvec(const uint8_t *w, size_t w_len, const float *x, size_t x_len, size_t rows, size_t cols,
+                           float *out) {
+    if (cols % 256 != 0 || x_len != cols || w_len < rows * (cols / 256) * 210) return 1;
+    for (size_t r = 0; r < rows; r++) out[r] = q6k_matvec_row(w + r * (cols / 256) * 210, x, cols / 256);
+    return 0;
+}
+
+/* q4k_dual_matvec_into, crates/larql-compute/src/cpu/ops/q4_common/dual.rs:22-167 with the scalar
+ * q4_dual_dot_32 (:186-198): both matrices against one x; unlike q4k_matvec_into each row keeps ONE
+ * running sum over all its super-blocks.  Returns 1 on a shape refusal. */
+ORC_API int orc_q4k_dual_matvec(const uint8_t *w_a, size_t wa_len, const uint8_t *w_b, size_t wb_len, const float *x,
+                                size_t x_len, size_t rows, size_t cols, float *out_a, float *out_b) {
+    size_t nb = cols / 256, row_bytes = nb * 144;
+    if (cols % 256 != 0 || x_len != cols || wa_len < rows * row_bytes || wb_len < rows * row_bytes) return 1;
+    float *sum_x = (float *)malloc(sizeof(float) * (cols / 32 + 1));
+    q4k_sum_x(x, cols, sum_x);
+    for (size_t r = 0; r < rows; r++) {
+        for (int which = 0; which < 2; which++) {
+            const uint8_t *w = which ? w_b : w_a;
+            float acc = 0.0f;
+            for (size_t sb = 0; sb < nb; sb++) {
+                const uint8_t *b = w + r * row_bytes + sb * 144;
+                float d = orc_f16_to_f32((uint16_t)(b[0] | (b[1] << 8)));
+                float dmin = orc_f16_to_f32((uint16_t)(b[2] | (b[3] << 8)));
+                uint8_t sc[8], mn[8];
+                unpack_q4k_scales(b + 4, sc, mn);
+                for (int g = 0; g < 4; g++) {
+                    int sb_lo = 2 * g, sb_hi = 2 * g + 1;
+                    float sc_lo = d * (float)sc[sb_lo], sc_hi = d * (float)sc[sb_hi];
+                    float mn_lo = dmin * (float)mn[sb_lo], mn_hi = dmin * (float)mn[sb_hi];
+                    const uint8_t *chunk = b + 16 + g * 32;
+                    const float *x_lo = x + sb * 256 + sb_lo * 32, *x_hi = x + sb * 256 + sb_hi * 32;
+                    float dot_lo = 0.0f, dot_hi = 0.0f;
+                    for (int l = 0; l < 32; l++) {
+                        dot_lo += (float)(chunk[l] & 0x0F) * x_lo[l];
+                        dot_hi += (float)((chunk[l] >> 4) & 0x0F) * x_hi[l];
+                    }
+                    acc += sc_lo * dot_lo - mn_lo * sum_x[sb * 8 + sb_lo];
+                    acc += sc_hi * dot_hi - mn_hi * sum_x[sb * 8 + sb_hi];
+                }
+            }
+            (which ? out_b : out_a)[r] = acc;
+        }
+    }
+    free(sum_x);
+    return 0;
+}
+
 /* crates/larql-models/src/quant/ggml/quantize.rs:50-77 (quantize_q8_0). */
 ORC_API void orc_quantize_q8_0(const float *data, size_t n, uint8_t *out) {
     for (size_t i = 0; i < n / 32; i++) {
@@ -841,7 +1016,7 @@ ORC_API size_t orc_moe_route(const float *logits, size_t n_experts, size_t top_k
 
 /* --------------------------------------------------------- the walk ----- */
 
-enum { ORC_FMT_Q4_K = 0, ORC_FMT_Q8_0 = 1, ORC_FMT_MXFP4 = 2, ORC_FMT_NVFP4 = 3 };
+enum { ORC_FMT_Q4_K = 0, ORC_FMT_Q8_0 = 1, ORC_FMT_MXFP4 = 2, ORC_FMT_NVFP4 = 3, ORC_FMT_Q6_K = 4 };
 
 typedef struct {
     int32_t fmt;
@@ -856,6 +1031,7 @@ static size_t mat_row_bytes(const orc_matrix *m) {
         case ORC_FMT_Q4_K: return m->cols / 256 * 144;
         case ORC_FMT_Q8_0: return m->cols / 32 * 34;
         case ORC_FMT_MXFP4: return m->cols / 32 * 16;
+        case ORC_FMT_Q6_K: return m->cols / 256 * 210;
         default: return m->cols / 16 * 8;
     }
 }
@@ -866,6 +1042,7 @@ static void mat_gemv_rows(const orc_matrix *m, const float *x, const float *sum_
         case ORC_FMT_Q4_K: q4k_matvec_rows(m->data, x, sum_x, r0, r1, m->cols, out); break;
         case ORC_FMT_Q8_0: for (size_t r = r0; r < r1; r++) out[r] = q8_0_row_dot(m->data, x, r, m->cols / 32); break;
         case ORC_FMT_MXFP4: for (size_t r = r0; r < r1; r++) out[r] = mxfp4_row_dot(m->data, m->scales, x, r, m->cols / 32); break;
+        case ORC_FMT_Q6_K: for (size_t r = r0; r < r1; r++) out[r] = q6k_matvec_row(m->data + r * mat_row_bytes(m), x, m->cols / 256); break;
         default: for (size_t r = r0; r < r1; r++) out[r] = nvfp4_row_dot(m->data, m->scales, m->tensor_scale, x, r, m->cols / 16); break;
     }
 }
@@ -878,6 +1055,7 @@ static float mat_row_dot(const orc_matrix *m, size_t row, const float *x) {
         case ORC_FMT_Q4_K: return orc_q4k_row_dot(m->data + row * mat_row_bytes(m), x, m->cols);
         case ORC_FMT_Q8_0: return q8_0_row_dot(m->data, x, row, m->cols / 32);
         case ORC_FMT_MXFP4: return mxfp4_row_dot(m->data, m->scales, x, row, m->cols / 32);
+        case ORC_FMT_Q6_K: return orc_q6k_row_dot(m->data + row * mat_row_bytes(m), x, m->cols);
         default: return nvfp4_row_dot(m->data, m->scales, m->tensor_scale, x, row, m->cols / 16);
     }
 }
@@ -886,6 +1064,7 @@ static void mat_dequant_row(const orc_matrix *m, size_t row, float *out) {
     switch (m->fmt) {
         case ORC_FMT_Q4_K: orc_dequantize_q4_k(m->data + row * mat_row_bytes(m), m->cols, out); break;
         case ORC_FMT_Q8_0: orc_dequantize_q8_0(m->data + row * mat_row_bytes(m), m->cols, out); break;
+        case ORC_FMT_Q6_K: orc_dequantize_q6_k(m->data + row * mat_row_bytes(m), m->cols, out); break;
         case ORC_FMT_MXFP4:
             orc_dequantize_mxfp4(m->data + row * mat_row_bytes(m), m->scales + row * (m->cols / 32), 1, m->cols / 32, out);
             break;
@@ -897,9 +1076,11 @@ static void mat_dequant_row(const orc_matrix *m, size_t row, float *out) {
 }
 
 /* One feature's down accumulate: ffn_row_scaled_add (ffn_row/mod.rs:106-179).
- * Q4_K: fused q4k_row_scaled_add; other formats: out += act * dequant(row). */
+ * Q4_K / Q6_K: the registry's fused row_scaled_add (crates/larql-vindex/src/quant/registry.rs);
+ * other formats: out += act * dequant(row). */
 static void mat_row_scaled_add(const orc_matrix *m, size_t row, float alpha, float *out, float *scratch) {
     if (m->fmt == ORC_FMT_Q4_K) { orc_q4k_row_scaled_add(m->data + row * mat_row_bytes(m), alpha, out, m->cols); return; }
+    if (m->fmt == ORC_FMT_Q6_K) { orc_q6k_row_scaled_add(m->data + row * mat_row_bytes(m), alpha, out, m->cols); return; }
     mat_dequant_row(m, row, scratch);
     for (size_t i = 0; i < m->cols; i++) out[i] += alpha * scratch[i];
 }

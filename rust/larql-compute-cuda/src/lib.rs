@@ -74,6 +74,10 @@ extern "C" {
                      hidden: usize, seq_len: usize, out: *mut f32, out_len: usize) -> c_int;
     fn lq_q4k_matvec_topk(ctx: *mut LqCtx, w: *const u8, w_len: usize, x: *const f32, x_len: usize, num_rows: usize,
                           hidden: usize, top_k: usize, idx: *mut u32, val: *mut f32, count: *mut usize) -> c_int;
+    fn lq_q6k_matvec(ctx: *mut LqCtx, w: *const u8, w_len: usize, x: *const f32, x_len: usize, num_rows: usize,
+                     hidden: usize, out: *mut f32) -> c_int;
+    fn lq_q4k_dual_matvec(ctx: *mut LqCtx, w_a: *const u8, wa_len: usize, w_b: *const u8, wb_len: usize, x: *const f32,
+                          x_len: usize, num_rows: usize, hidden: usize, out_a: *mut f32, out_b: *mut f32) -> c_int;
     fn lq_q8_0_gemv(ctx: *mut LqCtx, blocks: *const u8, blocks_len: usize, x: *const f32, x_len: usize, n: usize,
                     k: usize, out: *mut f32) -> c_int;
     fn lq_mxfp4_gemv(ctx: *mut LqCtx, packed: *const u8, packed_len: usize, scales: *const u8, scales_len: usize,
@@ -368,6 +372,29 @@ impl QuantMatVec for CudaBackend {
             (rc, ())
         })
         .map(|_| out)
+    }
+    fn q6k_matvec(&self, q6k_data: &[u8], x: &[f32], num_rows: usize, hidden: usize) -> Option<Vec<f32>> {
+        let mut out = vec![0f32; num_rows];
+        self.call(|c| {
+            let rc = unsafe {
+                lq_q6k_matvec(c, q6k_data.as_ptr(), q6k_data.len(), x.as_ptr(), x.len(), num_rows, hidden,
+                              out.as_mut_ptr())
+            };
+            (rc, ())
+        })
+        .map(|_| out)
+    }
+    fn q4k_dual_matvec(&self, q4k_a: &[u8], q4k_b: &[u8], x: &[f32], num_rows: usize, hidden: usize)
+                       -> Option<(Vec<f32>, Vec<f32>)> {
+        let (mut a, mut b) = (vec![0f32; num_rows], vec![0f32; num_rows]);
+        self.call(|c| {
+            let rc = unsafe {
+                lq_q4k_dual_matvec(c, q4k_a.as_ptr(), q4k_a.len(), q4k_b.as_ptr(), q4k_b.len(), x.as_ptr(), x.len(),
+                                   num_rows, hidden, a.as_mut_ptr(), b.as_mut_ptr())
+            };
+            (rc, ())
+        })
+        .map(|_| (a, b))
     }
     fn q4k_matvec_topk(&self, q4k_data: &[u8], x: &[f32], num_rows: usize, hidden: usize, top_k: usize)
                        -> Option<Vec<(u32, f32)>> {
