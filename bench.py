@@ -688,7 +688,7 @@ def run_ours(args, wl):
         kernel = "scan_q4k_mma_kernel + gather_q4k_kernel (batched path)"
     else:
         kernel = "scan_exact_staged_kernel + gather_fmt_kernel"
-    traffic_ratio = 1.066   # DRAM read + write over algorithmic bytes, ncu capture of the 2-layer case of this workload
+    traffic_ratio = 1.035   # DRAM read + write over algorithmic bytes, ncu capture of the 2-layer case of this workload
     line = {
         "metric": "walk_ffn_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -700,7 +700,7 @@ def run_ours(args, wl):
         "roofline": {"kernel": kernel, "bound": "hbm", "achieved": achieved, "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": (step_bytes * traffic_ratio) if (args.workload == "llama70b_q4k" and B == 1) else None,
-                     "traffic_note": "DRAM read + write per launch = 1.066 x algorithmic, measured by ncu on the 2-layer "
+                     "traffic_note": "DRAM read + write per launch = 1.035 x algorithmic, measured by ncu on the 2-layer "
                                      "case of this workload and scaled by layers (traffic grows with the layers)",
                      "algorithmic_bytes_per_launch": step_bytes if fused else None,
                      "avg_launch_ms": ms_step if fused else None, "launches_per_step": int(launches_per_step)},
