@@ -15,10 +15,12 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
+import os
+
 import numpy as np
 
 _HERE = Path(__file__).resolve().parent
-LIB_PATH = _HERE / "liblarql_b200.so"
+LIB_PATH = Path(os.environ.get("LARQL_B200_LIB") or (_HERE / "liblarql_b200.so"))  # override: a tuning build
 
 FMT_Q4_K, FMT_Q8_0, FMT_MXFP4, FMT_NVFP4, FMT_Q6_K = 0, 1, 2, 3, 4
 MAT_DEVICE = 0x100  # OR-ed into a matrix format: data/scales are device pointers

@@ -107,6 +107,10 @@ struct lq_ctx {
     lq_walk_stats* stats_dev = nullptr;
     bool use_fused = true;
     bool last_fused = false;
+    // batched gate scan: tcgen05 (default) or the mma.sync kernel (LARQL_B200_BATCH_SCAN=mma)
+    bool use_tc_scan = true;
+    uint8_t* tc_scratch = nullptr;
+    size_t tc_scratch_cap = 0;
     // multi-GPU: one NCCL communicator per context (lq_comm_init)
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1;
@@ -555,6 +559,32 @@ int enqueue_walk_token(lq_ctx* ctx, const lq_matrix& gate, const lq_matrix& up, 
     return LQ_OK;
 }
 
+// Fast scores (+ histogram and bound) of every row for nb <= 64 tokens: the tcgen05 scan, 32 tokens per launch,
+// or the mma.sync scan.  Never called inside a capture for the first time (the scratch is allocated here).
+int batched_scan(lq_ctx* ctx, const Q4kMat& g, const TokenWs& w, size_t ws_stride, int nb, int want_hist, float c1) {
+    if (!ctx->use_tc_scan) {
+        CK(launch_scan_q4k_mma(g, w, ws_stride, nb, want_hist, c1, ctx->d_err, ctx->sm_count, ctx->stream));
+        ctx->launches += 1;
+        return LQ_OK;
+    }
+    const size_t need = scan_q4k_tc_scratch_bytes(g.cols);
+    if (need > ctx->tc_scratch_cap) {
+        CK(cudaStreamSynchronize(ctx->stream));
+        if (ctx->tc_scratch) cudaFree(ctx->tc_scratch);
+        ctx->tc_scratch = nullptr;
+        ctx->tc_scratch_cap = 0;
+        CK(cudaMalloc(&ctx->tc_scratch, need));
+        ctx->tc_scratch_cap = need;
+    }
+    for (int o = 0; o < nb; o += 32) {
+        // one scratch for all launches: they run one after the other on the stream
+        CK(launch_scan_q4k_tc(g, ws_at(w, ws_stride * (size_t)o), ws_stride, std::min(32, nb - o), want_hist, c1,
+                              ctx->tc_scratch, ctx->d_err, ctx->stream));
+        ctx->launches += 2;  // the token planes, the scan
+    }
+    return LQ_OK;
+}
+
 size_t effective_k(size_t top_k, size_t n, uint32_t flags) {
     // K >= 80% of the features runs dense (all features) unless the walk is forced
     // (crates/larql-inference/src/vindex/walk_ffn/helpers.rs:18-30, thresholds.rs:29-31).
@@ -612,7 +642,7 @@ int dev_walk(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const lq_m
             const TokenWs& w = ctx->tok[c0];
             const int gb = batch_gather_grid(ctx, (size_t)nb);
             const TokStride ts{ws_stride, H, (size_t)gb * H};
-            CK(launch_scan_q4k_mma(g, w, ws_stride, nb, 1, bound_c1((int)H), ctx->d_err, ctx->sm_count, ctx->stream));
+            if ((rc = batched_scan(ctx, g, w, ws_stride, nb, 1, bound_c1((int)H)))) return rc;
             CK(launch_classify(w.scores, (int)N, (int)k, w, ctx->d_err, ctx->stream, nb, ws_stride));
             CK(launch_rescore_q4k(g, w.xn, w.band_idx, &w.sel->n_band, 0, w.band_exact, w, (int)k, 1, ctx->d_err,
                                   ctx->sm_count, ctx->stream, nb, ws_stride));
@@ -620,7 +650,7 @@ int dev_walk(lq_ctx* ctx, const lq_matrix* gate, const lq_matrix* up, const lq_m
                                  ctx->d_err, ctx->stream, nb, ts));
             CK(launch_finish(ctx->partials, gb, (int)H, (flags & LQ_WALK_RESIDUAL) ? x + c0 * H : nullptr, out + c0 * H,
                              ctx->stream, nb, ts));
-            ctx->launches += 5;
+            ctx->launches += 4;
             if (idx_out)
                 CK(cudaMemcpy2DAsync(idx_out + c0 * k, k * 4, w.hit_idx, ws_stride, k * 4, (size_t)nb,
                                      cudaMemcpyDeviceToDevice, ctx->stream));
@@ -676,6 +706,7 @@ int lq_create(int device, lq_ctx** out) {
         return LQ_ERR_CUDA;
     }
     if (const char* e = getenv("LARQL_B200_NO_FUSED")) ctx->use_fused = !(e[0] && e[0] != '0');
+    if (const char* e = getenv("LARQL_B200_BATCH_SCAN")) ctx->use_tc_scan = strcmp(e, "mma") != 0;
     if (const char* e = getenv("LARQL_B200_BATCH_MIN")) ctx->batch_min = (size_t)std::max(2, atoi(e));
     *out = ctx;
     return LQ_OK;
@@ -694,6 +725,7 @@ void lq_destroy(lq_ctx* ctx) {
     cudaFree(ctx->ws_raw);
     cudaFree(ctx->fws);
     cudaFree(ctx->stats_dev);
+    cudaFree(ctx->tc_scratch);
     cudaFree(ctx->stage);
     cudaFree(ctx->sort_buf);
     cudaFree(ctx->d_err);
@@ -814,10 +846,10 @@ static int q4k_host_common(lq_ctx* ctx, const uint8_t* w, size_t w_len, const fl
             launch_prep(dx + c0 * hidden, (int)nb, (int)hidden, 0, 0.0, t0.xn, t0.xa, t0.xb, t0.bscale, t0.bsum, t0.babs,
                         tstride / sizeof(float), nullptr, ctx->stream);
             CK(cudaGetLastError());
-            CK(launch_scan_q4k_mma(m, t0, tstride, (int)nb, 0, 0.0f, ctx->d_err, ctx->sm_count, ctx->stream));
+            if ((rc = batched_scan(ctx, m, t0, tstride, (int)nb, 0, 0.0f))) return rc;
             CK(cudaMemcpy2DAsync(dout + c0 * num_rows, num_rows * 4, t0.scores, tstride ? tstride : num_rows * 4,
                                  num_rows * 4, nb, cudaMemcpyDeviceToDevice, ctx->stream));
-            ctx->launches += 2;
+            ctx->launches += 1;
         }
         CK(cudaMemcpyAsync(out, dout, out_len * 4, cudaMemcpyDeviceToHost, ctx->stream));
         return lq_synchronize(ctx);

@@ -46,10 +46,10 @@ struct TokStride {
 };
 #ifdef __CUDACC__
 template <class T>
-__device__ __forceinline__ T* tok_off(T* p, size_t bytes) {
+__host__ __device__ __forceinline__ T* tok_off(T* p, size_t bytes) {
     return p ? reinterpret_cast<T*>(reinterpret_cast<uintptr_t>(p) + bytes) : p;
 }
-__device__ __forceinline__ TokenWs ws_at(TokenWs w, size_t b) {
+__host__ __device__ __forceinline__ TokenWs ws_at(TokenWs w, size_t b) {
     w.xn = tok_off(w.xn, b); w.xa = tok_off(w.xa, b); w.xb = tok_off(w.xb, b);
     w.bscale = tok_off(w.bscale, b); w.bsum = tok_off(w.bsum, b); w.babs = tok_off(w.babs, b);
     w.scores = tok_off(w.scores, b); w.hist = tok_off(w.hist, b); w.sel = tok_off(w.sel, b);
@@ -121,6 +121,10 @@ cudaError_t launch_rescore_q4k(const Q4kMat& m, const float* xn, const uint32_t*
 // scan_q4k_mma.cu: fast scores of every row for `batch` tokens at once on the tensor cores
 // (integer dots of the 4-bit weights against the tokens' fixed-point planes), with the histogram
 // and the bound of every token as launch_scan_q4k leaves them.
+// scan_q4k_tc.cu: the same contract on tcgen05 (kind::i8, accumulators in tensor memory); batch <= 32 per launch
+size_t scan_q4k_tc_scratch_bytes(int cols);
+cudaError_t launch_scan_q4k_tc(const Q4kMat& m, TokenWs ws0, size_t ws_stride, int batch, int want_hist, float c1,
+                               uint8_t* scratch, int* err, cudaStream_t st);
 cudaError_t launch_scan_q4k_mma(const Q4kMat& m, TokenWs ws0, size_t ws_stride, int batch, int want_hist, float c1,
                                 int* err, int sm_count, cudaStream_t st);
 
