@@ -187,6 +187,32 @@ LQ_API int lq_dequantize_q6k(lq_ctx* ctx, const uint8_t* data, size_t data_len, 
 LQ_API int lq_q4k_dual_matvec(lq_ctx* ctx, const uint8_t* w_a, size_t wa_len, const uint8_t* w_b, size_t wb_len,
                               const float* x, size_t x_len, size_t num_rows, size_t hidden, float* out_a, float* out_b);
 
+/* ---- on-disk K-quant FFN weights of a vindex directory (host only; needs no context) ----------------
+ * interleaved_kquant.bin + interleaved_kquant_manifest.json hold, per layer, gate [features, padded hidden],
+ * up [features, padded hidden] and down [hidden, padded features] as Q4_K / Q6_K
+ * (write_interleaved_ffn_kquant, crates/larql-vindex/src/format/weights/write_kquant/ffn.rs:25-117; read by
+ * load_interleaved_kquant, crates/larql-vindex/src/index/storage/ffn_store/interleaved_kquant.rs:64-106);
+ * down_features_kquant.bin + manifest hold the feature-major down [padded features, padded hidden] the walk
+ * wants (crates/larql-vindex/src/format/weights/write_kquant/feature_major_down.rs:48-104; read by
+ * load_down_features_q4k, crates/larql-vindex/src/index/storage/ffn_store/interleaved_kquant.rs:115-159).  The legacy
+ * file names (interleaved_q4k.bin, down_features_q4k.bin) are looked for second.  Rows are padded to whole
+ * 256-element super-blocks (k_quant_padded_cols, crates/larql-models/src/quant/ggml/mod.rs:105-114), so a
+ * matrix's `cols` is the padded width: a caller pads its activation with zeros to that width.
+ *   lq_vindex_open    maps the files read-only and checks every manifest entry (format known to the registry,
+ *                     shape, length, range); *out is NULL and err holds the reason on any refusal
+ *   lq_vindex_layer   the layer's matrices, pointing into the mappings (valid until lq_vindex_close);
+ *                     down_fm->fmt = -1 when the directory has no feature-major sidecar
+ *   lq_nvfp4_pack_split  the three regions {codes | scales | f32 tensor scale} of a stored NVFP4 tensor
+ *                     (PackLayout::derive and split, crates/larql-vindex/src/format/vindex3/represent/nvfp4_pack.rs:43-164) */
+typedef struct lq_vindex lq_vindex;
+LQ_API size_t lq_k_quant_padded_cols(size_t cols);
+LQ_API int lq_vindex_open(const char* dir, lq_vindex** out, char* err, size_t err_cap);
+LQ_API size_t lq_vindex_num_layers(const lq_vindex* v);
+LQ_API int lq_vindex_layer(const lq_vindex* v, size_t layer, lq_matrix* gate, lq_matrix* up, lq_matrix* down,
+                           lq_matrix* down_fm);
+LQ_API void lq_vindex_close(lq_vindex* v);
+LQ_API int lq_nvfp4_pack_split(const uint8_t* bytes, size_t len, size_t rows, size_t k, lq_matrix* out);
+
 /* LM-head style scan + top-k: QuantMatVec::q4k_matvec_topk (backend/quant_matvec.rs:268-277) and
  * MatMul::f16_gemv_topk (backend/matmul.rs:100-109).  Up to top_k (row, score) pairs sorted by score
  * descending, ties to the lower row; *count = min(top_k, rows).  Scores are computed in the reference

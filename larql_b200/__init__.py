@@ -43,6 +43,8 @@ EXPORTS = [
     "lq_nvfp4_gemv_multi", "lq_gemv16", "lq_gemv16_multi", "lq_f16_gemv", "lq_bf16_gemv", "lq_q4k_matvec_topk",
     "lq_gemv16_topk", "lq_f16_gemv_topk", "lq_comm_unique_id", "lq_comm_init", "lq_comm_destroy",
     "lq_stack_create_sharded", "lq_stack_path", "lq_q6k_matvec", "lq_dequantize_q6k", "lq_q4k_dual_matvec",
+    "lq_k_quant_padded_cols", "lq_vindex_open", "lq_vindex_num_layers", "lq_vindex_layer", "lq_vindex_close",
+    "lq_nvfp4_pack_split",
 ]
 
 
@@ -101,6 +103,12 @@ def load_library() -> C.CDLL:
         "lq_dev_shard_hits": (C.c_int, [vp, u32p, sz, C.POINTER(sz)]),
         "lq_stack_destroy": (None, [vp, vp]),
         "lq_stack_path": (C.c_int, [vp]),
+        "lq_k_quant_padded_cols": (sz, [sz]),
+        "lq_vindex_open": (C.c_int, [C.c_char_p, C.POINTER(vp), C.c_char_p, sz]),
+        "lq_vindex_num_layers": (sz, [vp]),
+        "lq_vindex_layer": (C.c_int, [vp, sz, mp, mp, mp, mp]),
+        "lq_vindex_close": (None, [vp]),
+        "lq_nvfp4_pack_split": (C.c_int, [vp, sz, sz, sz, mp]),
         "lq_q6k_matvec": (C.c_int, [vp, vp, sz, f32p, sz, sz, sz, f32p]),
         "lq_dequantize_q6k": (C.c_int, [vp, vp, sz, sz, f32p]),
         "lq_q4k_dual_matvec": (C.c_int, [vp, vp, sz, vp, sz, f32p, sz, sz, sz, f32p, f32p]),
@@ -166,6 +174,71 @@ class HostMatrix:
     def c(self) -> LqMatrix:
         return LqMatrix(self.fmt, _ptr(self.data), self.data.size, _ptr(self.scales) if self.scales is not None else None,
                         self.scales.size if self.scales is not None else 0, self.tensor_scale, self.rows, self.cols)
+
+
+def k_quant_padded_cols(cols: int) -> int:
+    """Row width of a K-quant matrix on disk: the next multiple of 256 (k_quant_padded_cols)."""
+    return int(load_library().lq_k_quant_padded_cols(int(cols)))
+
+
+def _host_matrix_of(m: "LqMatrix", keepalive=None) -> "HostMatrix":
+    def view(ptr, n):
+        if not ptr or not n:
+            return None
+        a = np.ctypeslib.as_array((C.c_ubyte * n).from_address(ptr))
+        a.flags.writeable = False
+        return a
+    hm = HostMatrix.__new__(HostMatrix)
+    hm.fmt, hm.rows, hm.cols = int(m.fmt), int(m.rows), int(m.cols)
+    hm.data, hm.scales = view(m.data, m.data_len), view(m.scales, m.scales_len)
+    hm.tensor_scale = float(m.tensor_scale)
+    hm.keepalive = keepalive
+    return hm
+
+
+class VindexFiles:
+    """The K-quant FFN weights of a vindex directory, mapped read-only (interleaved_kquant.bin and, when present,
+    the feature-major down sidecar).  ``layer(l)`` returns (gate, up, down, down_fm) as HostMatrix views into the
+    mappings; down_fm is None without the sidecar.  Raises BackendError with the reader's reason on a refusal."""
+
+    def __init__(self, directory):
+        self._lib = load_library()
+        self._h = C.c_void_p()
+        err = C.create_string_buffer(512)
+        rc = self._lib.lq_vindex_open(str(directory).encode(), C.byref(self._h), err, len(err))
+        if rc != LQ_OK:
+            raise BackendError(err.value.decode() or f"lq_vindex_open: status {rc}")
+
+    @property
+    def num_layers(self) -> int:
+        return int(self._lib.lq_vindex_num_layers(self._h))
+
+    def layer(self, l: int):
+        g, u, d, f = LqMatrix(), LqMatrix(), LqMatrix(), LqMatrix()
+        if self._lib.lq_vindex_layer(self._h, int(l), C.byref(g), C.byref(u), C.byref(d), C.byref(f)) != LQ_OK:
+            raise IndexError(f"layer {l} out of range")
+        return (_host_matrix_of(g, self), _host_matrix_of(u, self), _host_matrix_of(d, self),
+                _host_matrix_of(f, self) if f.fmt >= 0 else None)
+
+    def close(self):
+        if self._h:
+            self._lib.lq_vindex_close(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def nvfp4_pack_split(payload, rows: int, k: int):
+    """The stored form of an NVFP4 tensor {codes | scales | f32 tensor scale} as a HostMatrix view; None on a
+    shape refusal (k not a multiple of 16, or a length that does not match [rows, k])."""
+    b = _u8(payload)
+    m = LqMatrix()
+    rc = load_library().lq_nvfp4_pack_split(_ptr(b), b.size, int(rows), int(k), C.byref(m))
+    return _host_matrix_of(m, b) if rc == LQ_OK else None
 
 
 class DeviceMatrix:

@@ -16,9 +16,18 @@ histogram and the bound are global, the band is resolved with exact reference-or
 ties go to the lower GLOBAL row).  The reference itself has no feature sharding; it shards
 layers or experts over HTTP (docs/ffn/distributed.md:14-40).
 
-``ShardedWalk`` is the protocol; the per-rank arithmetic is a *compute* object with ``scan``,
-``classify`` and ``gather`` methods.  ``CudaShardCompute`` runs them through the C ABI; the CPU
-test-suite plugs in a numpy stand-in to exercise the protocol over the gloo backend.
+``ShardedWalk`` is the protocol for a host that brings its own collectives (torch.distributed
+here); the per-rank arithmetic is a *compute* object with ``scan``, ``classify`` and ``gather``
+methods.  ``CudaShardCompute`` runs them through the C ABI; the CPU test-suite plugs in a numpy
+stand-in to exercise the protocol over the gloo backend.  The library runs the same protocol by
+itself (``CudaBackend.comm_init`` / ``stack_create_sharded``: the exchanges are made from C++, on
+the persistent kernel through peer memory where it applies); that is the path the benchmark times.
+
+Ordering: the C-ABI steps are enqueued on the backend's own non-blocking stream.  When the compute
+object exposes that stream (``stream()``), ``ShardedWalk.layer`` issues the collectives and the
+residual add on the same stream, after making it wait for the caller's current stream, and makes
+the caller's stream wait for it before returning: steps and collectives are ordered whatever
+stream the caller is on.
 """
 from __future__ import annotations
 
@@ -48,9 +57,21 @@ class ShardedWalk:
         self.pack = torch.zeros(self.stride, dtype=torch.int32, device=device)
         self.packs = torch.zeros(world * self.stride, dtype=torch.int32, device=device)
         self.out = torch.zeros(hidden, dtype=torch.float32, device=device)
+        handle = compute.stream() if hasattr(compute, "stream") else None
+        self._stream = torch.cuda.ExternalStream(handle, device=device) if handle else None
 
     def layer(self, l: int, h: torch.Tensor) -> torch.Tensor:
         """h: [hidden] residual on the compute device. Returns h + walk_l(rmsnorm(h))."""
+        if self._stream is None:
+            return self._layer(l, h)
+        caller = torch.cuda.current_stream(self._stream.device)
+        self._stream.wait_stream(caller)          # h is ready before the first step reads it
+        with torch.cuda.stream(self._stream):
+            out = self._layer(l, h)
+        caller.wait_stream(self._stream)          # the result is ready for whatever the caller enqueues next
+        return out
+
+    def _layer(self, l: int, h: torch.Tensor) -> torch.Tensor:
         c = self.compute
         c.scan(l, h, self.hist)
         if self.world > 1:
@@ -78,6 +99,10 @@ class CudaShardCompute:
         # layers: list of (gate, up, down_fm) DeviceMatrix shards (rows = this rank's range)
         self.be, self.layers, self.rank, self.world = backend, layers, rank, world
         self.row_offset, self.top_k, self.cap, self.flags = row_offset, top_k, cap, flags
+
+    def stream(self) -> int:
+        """The CUDA stream the steps are enqueued on (a cudaStream_t as an integer)."""
+        return self.be.stream()
 
     def scan(self, l, h, hist):
         ok = self.be.dev_shard_scan(self.layers[l][0], h.data_ptr(), self.flags, self.rank, self.world, hist.data_ptr())

@@ -104,3 +104,24 @@ def test_walk_q6k_down_batch_and_dense(be):
         assert sorted(hits[t].tolist()) == sorted(idx.tolist()) and rel_l2(out[t], want) < OUT_TOL
     dense = be.walk_ffn(host(gate), host(up), host(down), xs[0], n)[0]
     assert rel_l2(dense.reshape(-1), oracle.walk_token_dense(gate, up, down, xs[0])) < OUT_TOL
+
+
+def test_walk_over_weights_read_from_a_vindex_directory(be, tmp_path):
+    """Files laid out as the reference's writer does (gate / up Q4_K, feature-major down Q6_K, hidden 2880 padded
+    to 3072), mapped by the reader and walked as they are: the activation is zero-padded to the padded width."""
+    import larql_b200
+    from test_vindex_files import write_vindex
+    hidden, feats, k = 2880, 512, 64
+    write_vindex(tmp_path, 2, hidden, feats)
+    v = larql_b200.VindexFiles(tmp_path)
+    for l in range(2):
+        gate, up, _, down_fm = v.layer(l)
+        og, ou, od = (oracle.Matrix(m.fmt, m.rows, m.cols, m.data) for m in (gate, up, down_fm))
+        x = np.zeros(gate.cols, np.float32)
+        x[:hidden] = oracle.rms_norm(seeded_x(0x7100 + l, hidden))
+        want, idx, _ = oracle.walk_token(og, ou, od, x, k)
+        out, hits = be.walk_ffn(gate, up, down_fm, x, k, larql_b200.WALK_FORCE_SPARSE)
+        assert sorted(hits[0].tolist()) == sorted(idx.tolist())
+        assert rel_l2(out.reshape(-1), want) < OUT_TOL
+        assert np.all(out.reshape(-1)[hidden:] == 0.0)      # the padded tail of every down row decodes to zero
+    v.close()
