@@ -417,6 +417,15 @@ float bound_c1(int hidden) {
     return (float)(n * u / (1.0 - n * u) * 1.01);
 }
 
+// Reference rows of Q8_0 / MXFP4 / NVFP4 are one f32 chain over the whole row: hidden + 3 roundings on a term's
+// path; the fast path has at most 64.  The 2 % margin also covers the rounding of the sum |w x| the bound is
+// taken from.
+float bound_c1_fmt(int hidden) {
+    const double u = std::ldexp(1.0, -24);
+    const double n = (double)hidden + 3.0 + 64.0;
+    return (float)(n * u / (1.0 - n * u) * 1.02);
+}
+
 FmtMat fmtmat_of(const lq_matrix& m) {
     return FmtMat{m.fmt & 0xff, (const uint8_t*)m.data, (const uint8_t*)m.scales, m.tensor_scale, (int)m.rows,
                   (int)m.cols};
@@ -452,9 +461,22 @@ int enqueue_walk_token_fmt(lq_ctx* ctx, const lq_matrix& gate, const lq_matrix& 
     const XPrep xp = xprep_of(w);
     const bool sparse = k < N;
     cudaStream_t st = ctx->stream;
-    // The reference rows of these formats are one running f32 sum over the whole row: a rigorous
-    // bound on a re-associated fast score is wide (thousands of band rows at 28672 x 8192), so the
-    // scan itself runs in the reference's order and the selection works on exact scores.
+    // The reference rows of these formats are one running f32 sum over the whole row, so the rounding part of a
+    // rigorous bound on a re-associated fast score grows with the row length.  For the FP4 formats the fast
+    // scan accumulates sum |w x| of every row beside the dot, which keeps the band (rows within the bound of the
+    // threshold, re-scored in the reference's order) to a few percent of the rows: fast scan + band.  Q8_0
+    // (and LARQL_B200_FMT_EXACT_SCAN=1) scans every row in the reference's order instead: no bound, no band.
+    static const bool force_exact = [] { const char* e = getenv("LARQL_B200_FMT_EXACT_SCAN"); return e && e[0] == '1'; }();
+    if (sparse && !force_exact && (g.fmt == LQ_FMT_MXFP4 || g.fmt == LQ_FMT_NVFP4)) {
+        CK(launch_scan_fmt(g, xp, w.scores, w.hist, &w.sel->bound_bits, bound_c1_fmt(H), ctx->d_err, ctx->sm_count, st));
+        CK(launch_classify(w.scores, N, k, w, ctx->d_err, st));
+        CK(launch_rescore_fmt(g, w.xn, w.band_idx, &w.sel->n_band, 0, w.band_exact, ctx->sm_count, st));
+        CK(launch_final_pick(w, ctx->d_err, st));
+        CK(launch_gather_fmt(u, d, xp, w.hit_idx, w.hit_score, &w.sel->n_sel, k, ctx->partials, ctx->gather_grid, st));
+        CK(launch_finish(ctx->partials, ctx->gather_grid, H, residual, out, st));
+        ctx->launches += 6;
+        return LQ_OK;
+    }
     CK(launch_scan_exact_fmt(g, w.xn, w.scores, ctx->d_err, st));
     CK(launch_select(w.scores, N, k, w, ctx->d_err, st));
     ctx->launches += 2;

@@ -31,8 +31,11 @@ __device__ __forceinline__ float warp_sum(float v) {
 // 2 * e2m1 magnitude per code, sign in bit 3: {0,.5,1,1.5,2,3,4,6}
 __device__ __forceinline__ float fp4_lut_lane(int lane) { return e2m1_to_f32((uint32_t)lane & 15u); }
 
-// One warp: fast dot of row `row` with the prepared activation; also the bound term
-// sum |w||x| (upper estimate) scaled by c1, plus the fixed-point error term for Q8_0.
+// One warp: fast dot of row `row` with the prepared activation; also the row's bound on
+// |fast - reference|: c1 sum |w x| (for the FP4 formats the sum itself, accumulated beside the dot; for
+// Q8_0 an upper estimate plus the fixed-point error term).  c1 covers the roundings of the reference's
+// one running sum over the row and of this evaluation; sum |w x| here is itself rounded, which the 1 %
+// margin in c1 absorbs.
 template <int FMT>
 __device__ __forceinline__ float fast_row(const FmtMat& m, size_t row, const XPrep& xp, float c1, float& bound, int lane,
                                           float lut) {
@@ -65,7 +68,7 @@ __device__ __forceinline__ float fast_row(const FmtMat& m, size_t row, const XPr
                 scale = e8m0_to_f32(m.scales[(size_t)row * nb + blk]);
             }
             const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
-            float s = 0.0f;
+            float s = 0.0f, sa = 0.0f;  // sum w x and sum |w x| of the block (before the scale)
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 float4 x0 = make_float4(0, 0, 0, 0), x1 = x0;
@@ -78,11 +81,12 @@ __device__ __forceinline__ float fast_row(const FmtMat& m, size_t row, const XPr
                 for (int e = 0; e < 8; ++e) {
                     const float t = __shfl_sync(0xffffffffu, lut, (qw[j] >> (4 * e)) & 15u);
                     s = fmaf(t, xs[e], s);
+                    sa = fmaf(fabsf(t), fabsf(xs[e]), sa);
                 }
             }
             if (on) {
                 acc += s * scale;
-                bnd += c1 * 6.0f * fabsf(scale) * xp.abs[blk];
+                bnd += c1 * fabsf(scale) * sa;
             }
         }
     } else {  // NVFP4: groups of 16
@@ -97,7 +101,7 @@ __device__ __forceinline__ float fast_row(const FmtMat& m, size_t row, const XPr
                 step = m.ts * e4m3_to_f32(m.scales[(size_t)row * ng + g]);
             }
             const uint32_t qw[2] = {q.x, q.y};
-            float s = 0.0f, ax = 0.0f;
+            float s = 0.0f, sa = 0.0f;  // sum w x and sum |w x| of the group (before the scale)
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 float4 x0 = make_float4(0, 0, 0, 0), x1 = x0;
@@ -110,12 +114,12 @@ __device__ __forceinline__ float fast_row(const FmtMat& m, size_t row, const XPr
                 for (int e = 0; e < 8; ++e) {
                     const float t = __shfl_sync(0xffffffffu, lut, (qw[j] >> (4 * e)) & 15u);
                     s = fmaf(t, xs[e], s);
-                    ax += fabsf(xs[e]);
+                    sa = fmaf(fabsf(t), fabsf(xs[e]), sa);
                 }
             }
             if (on) {
                 acc += s * step;
-                bnd += c1 * 6.0f * fabsf(step) * ax;
+                bnd += c1 * fabsf(step) * sa;
             }
         }
     }
