@@ -462,11 +462,13 @@ int enqueue_walk_token_fmt(lq_ctx* ctx, const lq_matrix& gate, const lq_matrix& 
     const bool sparse = k < N;
     cudaStream_t st = ctx->stream;
     // The reference rows of these formats are one running f32 sum over the whole row, so the rounding part of a
-    // rigorous bound on a re-associated fast score grows with the row length.  For the FP4 formats the fast
-    // scan accumulates sum |w x| of every row beside the dot, which keeps the band (rows within the bound of the
-    // threshold, re-scored in the reference's order) to a few percent of the rows: fast scan + band.  Q8_0
-    // (and LARQL_B200_FMT_EXACT_SCAN=1) scans every row in the reference's order instead: no bound, no band.
-    static const bool force_exact = [] { const char* e = getenv("LARQL_B200_FMT_EXACT_SCAN"); return e && e[0] == '1'; }();
+    // rigorous bound on a re-associated fast score grows with the row length: even with sum |w x| accumulated per
+    // row beside the dot, the band at 28672 x 8192 costs more to re-score in the reference's order than scanning
+    // every row in that order from the start (measured on B200: 631 against 371 us per NVFP4 layer).  The scan
+    // therefore runs in the reference's order and the selection works on exact scores: no bound, no band.
+    // LARQL_B200_FMT_FAST_SCAN=1 selects fast scan + band for the FP4 formats.
+    static const bool fast_scan = [] { const char* e = getenv("LARQL_B200_FMT_FAST_SCAN"); return e && e[0] == '1'; }();
+    const bool force_exact = !fast_scan;
     if (sparse && !force_exact && (g.fmt == LQ_FMT_MXFP4 || g.fmt == LQ_FMT_NVFP4)) {
         CK(launch_scan_fmt(g, xp, w.scores, w.hist, &w.sel->bound_bits, bound_c1_fmt(H), ctx->d_err, ctx->sm_count, st));
         CK(launch_classify(w.scores, N, k, w, ctx->d_err, st));

@@ -747,19 +747,30 @@ __device__ __noinline__ void phase_scan(int l) {
         }
     }
     for (int o = 16; o > 0; o >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
-    if (lane == 0 && kmax > 0u) atomicMax(&a.ctrs[CTR_MAXBIN0 + (l & 1)], kmax);
     if (!a.pf_late) prefetch_next_gate(sm, l);
-    // bound: sum over the team's cells of each thread's largest cell bound
-    if (in_team) {
+    // bound: sum over the team's cells of each thread's largest cell bound; one atomic per CTA for the bound and
+    // one for the largest occupied bin (they all go to two words that every CTA of the grid is updating)
+    {
         for (int o = 16; o > 0; o >>= 1) bmax += __shfl_xor_sync(0xffffffffu, bmax, o);
-        float* wb = sm.red() + team * gm.Wt;
-        if (lane == 0) wb[wt] = bmax;
-        bar_sync(1 + team, gm.TS);
-        if (c == 0) {
-            float t = 0.0f;
-            for (int w = 0; w < gm.Wt; ++w) t += wb[w];
-            t *= 1.0001f;  // the sums above round to nearest
-            if (t > 0.0f) atomicMax(&a.ctrs[CTR_BOUND0 + (l & 1)], __float_as_uint(t));
+        float* wb = sm.red();                                       // [warp] bound partials
+        uint32_t* wk = reinterpret_cast<uint32_t*>(sm.red()) + 32;  // [warp] largest bins
+        if (lane == 0) {
+            wb[tid >> 5] = in_team ? bmax : 0.0f;
+            wk[tid >> 5] = kmax;
+        }
+        bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+        if (tid == 0) {
+            float best = 0.0f;
+            for (int t = 0; t < P; ++t) {
+                float sum = 0.0f;
+                for (int w = 0; w < gm.Wt; ++w) sum += wb[t * gm.Wt + w];
+                best = fmaxf(best, sum);
+            }
+            best *= 1.0001f;  // the sums above round to nearest
+            uint32_t kb = 0u;
+            for (int w = 0; w < FW_NWARPS; ++w) kb = max(kb, wk[w]);
+            if (best > 0.0f) atomicMax(&a.ctrs[CTR_BOUND0 + (l & 1)], __float_as_uint(best));
+            if (kb > 0u) atomicMax(&a.ctrs[CTR_MAXBIN0 + (l & 1)], kb);
         }
     }
     if (tid == 0) {

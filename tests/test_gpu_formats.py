@@ -267,3 +267,34 @@ def test_q4k_matvec_topk_by_value(be):
     sf = oracle.gemv16(wf, xs, 3000, 512, 0)
     gotf = be.f16_gemv_topk(wf, xs, 3000, 512, 16)
     assert [r for r, _ in gotf] == oracle.top_k_by_value(sf, 16)[0].tolist()
+
+
+def test_fp4_fast_scan_with_band_keeps_the_exact_selection():
+    """The switchable fast scan + band route of the FP4 walks (bound c1 * sum |w x| per row) selects the same rows
+    as the exact-order scan.  The switch is read once per process, so the check runs in a child process."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    child = textwrap.dedent('''
+        import sys
+        sys.path.insert(0, %r); sys.path.insert(0, %r)
+        import numpy as np, larql_b200, oracle
+        from conftest import seeded_weights, seeded_x, rel_l2
+        be = larql_b200.CudaBackend(0)
+        ok = True
+        for fmt in (oracle.FMT_MXFP4, oracle.FMT_NVFP4):
+            n, h, k = 3072, 2048, 400
+            g, u, d = (oracle.quantize_matrix(fmt, seeded_weights(0xF4 + i + fmt, n, h)) for i in range(3))
+            hm = lambda m: larql_b200.HostMatrix(m.fmt, m.rows, m.cols, m.data, m.scales, float(m.tensor_scale))
+            for q in range(3):
+                x = oracle.rms_norm(seeded_x(0xF5 + q, h))
+                want, idx, _ = oracle.walk_token(g, u, d, x, k)
+                out, hits = be.walk_ffn(hm(g), hm(u), hm(d), x, k, larql_b200.WALK_FORCE_SPARSE)
+                ok = ok and sorted(hits[0].tolist()) == sorted(idx.tolist()) and rel_l2(out.reshape(-1), want) < 1e-3
+        sys.exit(0 if ok else 3)
+    ''') % (root, os.path.join(root, "tests"))
+    env = dict(os.environ, LARQL_B200_FMT_FAST_SCAN="1")
+    r = subprocess.run([sys.executable, "-c", child], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
