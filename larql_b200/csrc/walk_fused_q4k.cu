@@ -51,9 +51,6 @@ namespace {
 #ifndef FW_CFG_THREADS
 #define FW_CFG_THREADS 512
 #endif
-#ifndef FW_CFG_UB
-#define FW_CFG_UB 2
-#endif
 constexpr int FW_CONSUMERS = FW_CFG_THREADS;
 constexpr int FW_THREADS = FW_CONSUMERS;
 constexpr int FW_NWARPS = FW_CONSUMERS / 32;
@@ -64,7 +61,6 @@ constexpr float FW_NOISE_FLOOR = 1e-10f;  // ACTIVATION_NOISE_FLOOR, walk_config
 constexpr int FW_PICK_CAP = 8192;    // band entries the final pick can stage in shared memory
 constexpr int FW_RANK_CAP = 2048;    // up to this many band entries the pick ranks by counting
 constexpr int FW_STAMPS = 13;
-constexpr int FW_UB = FW_CFG_UB;             // up rows a thread fetches per batch in the gather
 constexpr int FW_MAX_WORLD = 8;              // ranks of one feature-sharded walk
 
 struct FusedGeom {
@@ -351,11 +347,11 @@ __device__ __forceinline__ float cell_value(const uint4& hdr, const uint4& q0, c
 
 // Gather of one chunk of rows (global row numbers and gate scores in shared memory).
 // Team t takes items t, t+P, ...; a thread owns one 64-weight cell of every row.
-//   1. the chunk's down rows start moving into the idle ring (row i at i * row_bytes): one TMA bulk
-//      copy per row, issued by thread i, all completing on one mbarrier;
-//   2. meanwhile every thread fetches its own 48 bytes of its team's up rows, FW_UB rows at a time,
-//      into registers: up dot partials against the activation planes (held in registers), reduced per
-//      warp into psum[i][warp of the team];
+//   1. the chunk's up rows move into the idle ring (row i at i * row_bytes): one TMA bulk copy per row,
+//      issued by thread i, all completing on one mbarrier;
+//   2. up dots out of shared memory against the activation planes (held in registers), reduced per warp
+//      into psum[i][warp of the team]; as soon as a team is done with a row's slot, one of its threads
+//      starts the copy of the same feature's down row into it (a second mbarrier collects those);
 //   3. thread i turns row i's partials into act_i = silu(gate_i) * up_i;
 //   4. once the down rows have landed: axpy of each of the team's rows into the thread's 64 accumulators;
 //   5. every thread leaves its accumulators in the ring (one region of G * 65 floats per team,
@@ -369,6 +365,7 @@ struct GatherArgs {
     float* psum;       // [FW_MAX_GROWS][Wt]
     float* act;        // [FW_MAX_GROWS]
     uint64_t* bar;     // mbarrier of the down-row copies
+    uint64_t* ubar;    // mbarrier of the up-row copies
     const uint32_t* xa_s;
     const uint32_t* xb_s;
     const float* blk_s;
@@ -381,42 +378,44 @@ __device__ __forceinline__ void gather_stage(const GatherArgs& ga, int base, int
     const bool in_team = team < ga.P;
     const bool active = in_team && c < ga.G;
     const int s = c >> 2, g = c & 3, nblk = ga.nsb * 8, P = ga.P;
-    // 1. down rows -> ring
-    if (tid == 0) mbar_expect_tx(ga.bar, (uint32_t)nn * (uint32_t)ga.row_bytes);
-    bar_sync(FW_BAR_CONS, FW_CONSUMERS);  // the expectation is armed before any copy can complete
+    // 1. the chunk's up rows -> ring (row i at i * row_bytes), one bulk copy per row, issued by thread i
+    if (tid == 0) {
+        mbar_expect_tx(ga.ubar, (uint32_t)nn * (uint32_t)ga.row_bytes);
+        mbar_expect_tx(ga.bar, (uint32_t)nn * (uint32_t)ga.row_bytes);  // the down rows follow slot by slot
+    }
+    bar_sync(FW_BAR_CONS, FW_CONSUMERS);  // the expectations are armed before any copy can complete
     for (int i = tid; i < nn; i += FW_CONSUMERS)
-        tma_bulk_g2s(ga.ring + (size_t)i * ga.row_bytes, ga.down + (size_t)(uint32_t)ga.rows[base + i] * ga.row_bytes,
-                     (uint32_t)ga.row_bytes, ga.bar);
-    // 2. up dots
+        tma_bulk_g2s(ga.ring + (size_t)i * ga.row_bytes, ga.up + (size_t)(uint32_t)ga.rows[base + i] * ga.row_bytes,
+                     (uint32_t)ga.row_bytes, ga.ubar);
+    // 2. up dots out of shared memory; a team takes rows team, team + P, ...; as soon as all of the team's
+    //    threads have read a row, its slot takes the same feature's down row
     if (in_team) {
         CellX x;
         {
             const int cl = active ? c : 0;  // unconditional: see the scan
             load_cellx(x, ga.xa_s, ga.xb_s, ga.blk_s, nblk, (cl >> 2) * 8 + 2 * (cl & 3), ga.G, cl);
         }
-        for (int i0 = team; i0 < nn; i0 += P * FW_UB) {
-            uint4 hd[FW_UB], q0[FW_UB], q1[FW_UB];
-#pragma unroll
-            for (int k = 0; k < FW_UB; ++k) {
-                const int i = i0 + k * P;
-                if (active && i < nn) {
-                    const uint8_t* cell = ga.up + (size_t)(uint32_t)ga.rows[base + i] * ga.row_bytes + s * 144;
-                    hd[k] = __ldg(reinterpret_cast<const uint4*>(cell));
-                    q0[k] = __ldg(reinterpret_cast<const uint4*>(cell + 16 + g * 32));
-                    q1[k] = __ldg(reinterpret_cast<const uint4*>(cell + 32 + g * 32));
-                }
+        if (!failed && !mbar_wait(ga.ubar, bar_parity)) failed = true;
+        for (int i = team; i < nn; i += P) {
+            float val = 0.0f;
+            if (active) {
+                const uint8_t* cell = ga.ring + (size_t)i * ga.row_bytes + s * 144;
+                const uint4 hd = *reinterpret_cast<const uint4*>(cell);
+                const uint4 q0 = *reinterpret_cast<const uint4*>(cell + 16 + g * 32);
+                const uint4 q1 = *reinterpret_cast<const uint4*>(cell + 32 + g * 32);
+                val = cell_value(hd, q0, q1, g, x);
             }
-#pragma unroll
-            for (int k = 0; k < FW_UB; ++k) {
-                const int i = i0 + k * P;
-                if (i < nn) {
-                    float val = 0.0f;
-                    if (active) val = cell_value(hd[k], q0[k], q1[k], g, x);
-                    for (int o = 16; o > 0; o >>= 1) val += __shfl_xor_sync(0xffffffffu, val, o);
-                    if (lane == 0) ga.psum[i * ga.Wt + wt] = val;
-                }
+            for (int o = 16; o > 0; o >>= 1) val += __shfl_xor_sync(0xffffffffu, val, o);
+            if (lane == 0) ga.psum[i * ga.Wt + wt] = val;
+            bar_sync(1 + team, ga.TS);  // every thread of the team is done with the up row
+            if (c == 0) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // plain reads before the TMA write
+                tma_bulk_g2s(ga.ring + (size_t)i * ga.row_bytes,
+                             ga.down + (size_t)(uint32_t)ga.rows[base + i] * ga.row_bytes, (uint32_t)ga.row_bytes, ga.bar);
             }
         }
+    } else if (!failed && !mbar_wait(ga.ubar, bar_parity)) {
+        failed = true;  // (threads outside the teams pass the phase too)
     }
     bar_sync(FW_BAR_CONS, FW_CONSUMERS);
     // 3. activations
@@ -1325,7 +1324,7 @@ __device__ __noinline__ void phase_gather(int l) {
     for (int base = 0; base == 0 || base < n_g2; base += gm.D2) {
         GatherArgs ga;
         ga.up = ly.up; ga.down = ly.down; ga.rows = sm.g_rows(); ga.scores = sm.g_scores(); ga.ring = sm.ring();
-        ga.psum = sm.psum(); ga.act = sm.psum() + FW_MAX_GROWS * gm.Wt; ga.bar = sm.gbar();
+        ga.psum = sm.psum(); ga.act = sm.psum() + FW_MAX_GROWS * gm.Wt; ga.bar = sm.gbar(); ga.ubar = sm.gbar() + 1;
         ga.xa_s = sm.xa(); ga.xb_s = sm.xb(); ga.blk_s = sm.blk();
         ga.nsb = gm.nsb; ga.G = gm.G; ga.TS = gm.TS; ga.P = P; ga.Wt = gm.Wt; ga.row_bytes = gm.row_bytes;
         // leaves the accumulators staged in the ring
@@ -1469,6 +1468,7 @@ __device__ __forceinline__ void fused_setup(const FusedGeom& gm_in, const FusedA
             sm.released()[i] = 0;
         }
         mbar_init(sm.gbar(), 1);
+        mbar_init(sm.gbar() + 1, 1);
         fence_mbar_init();
     }
     __syncthreads();
