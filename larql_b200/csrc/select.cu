@@ -104,6 +104,9 @@ classify_kernel(const float* __restrict__ scores_g, int n, int top_k, TokenWs ws
     __shared__ uint32_t s_wsum[SEL_T / 32];
     constexpr int PER = LQ_HIST_BINS / SEL_T;  // bins per thread, contiguous
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // top_k above the number of counted scores (a shard step called with the global K): no bin holds the K-th
+    // score; bin 0 then makes every row a candidate, which is the "take all" answer
+    if (tid == 0) sm.bcast[0] = 0;
     // stage the scores in shared memory (independent loads), so the two compaction passes
     // do not pay a global-memory round trip per element
     if (use_smem)
