@@ -400,7 +400,7 @@ int check_device_err(lq_ctx* ctx) {
     if (h == DEV_OK) return LQ_OK;
     CK(cudaMemsetAsync(ctx->d_err, 0, sizeof(int), ctx->stream));
     // a failed fused launch may leave its histogram / counters dirty
-    if (ctx->fws) CK(cudaMemsetAsync(ctx->fws, 0, (size_t)2 * LQ_HIST_BINS * 4 + 256, ctx->stream));
+    if (ctx->fws) CK(cudaMemsetAsync(ctx->fws, 0, fused_q4k_ws_dirty_bytes(), ctx->stream));
     if (h == DEV_ERR_NAN_SCORE) return fail(ctx, LQ_ERR_NAN_SCORE, "NaN gate score or non-finite activation");
     if (h == DEV_ERR_TMA_TIMEOUT) return fail(ctx, LQ_ERR_TIMEOUT, "a bounded device-side wait ran out");
     return fail(ctx, LQ_ERR_CUDA, "device-side internal error");

@@ -166,4 +166,5 @@ cudaError_t launch_finish(const float* partials, int n_partials, int hidden, con
 bool fused_q4k_supported(int hidden, int n_rows, int top_k, int sm_count);
 size_t fused_q4k_ws_bytes(int hidden, int n_rows, int sm_count);
 int fused_q4k_stamp_count();
+size_t fused_q4k_ws_dirty_bytes();
 }  // namespace lq

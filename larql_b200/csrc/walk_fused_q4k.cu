@@ -62,6 +62,12 @@ constexpr int FW_PICK_CAP = 8192;    // band entries the final pick can stage in
 constexpr int FW_RANK_CAP = 2048;    // up to this many band entries the pick ranks by counting
 constexpr int FW_STAMPS = 13;
 constexpr int FW_MAX_WORLD = 8;              // ranks of one feature-sharded walk
+// The |score| keys of a layer crowd into a few hundred neighbouring histogram bins, i.e. a handful of cache
+// lines, and every CTA adds its rows at the same moment: the histogram is kept as FW_HIST_COPIES copies
+// (a warp adds to copy (CTA + warp) mod copies, readers sum the copies) so that those adds spread over
+// that many times more lines.
+constexpr int FW_HIST_COPIES = 8;
+constexpr int FW_HIST_WORDS = FW_HIST_COPIES * LQ_HIST_BINS;
 
 struct FusedGeom {
     int nsb, G, TS, P, Wt;      // super-blocks/row, cells/row, team size, teams, warps per team
@@ -111,11 +117,12 @@ struct FusedArgs {
     int pf_tiles;          // tiles of the next layer's gate share each CTA prefetches into L2 during the tail
     int pf_late;           // 1: start that prefetch only after the gather (0: right after the scan)
     int pf_dist;           // tiles the L2 prefetch runs ahead of the ring inside a layer's scan
+    int stamp_cta;         // the CTA whose clock stamps are recorded
     const float* h_in;
     float* h_out;
     float* hbuf0;
     float* hbuf1;
-    uint32_t* hist;        // [2][LQ_HIST_BINS]
+    uint32_t* hist;        // [2][FW_HIST_COPIES][LQ_HIST_BINS]
     uint32_t* ctrs;        // see CTR_* below
     uint32_t* band_row;    // [n_rows]
     float* band_exact;     // [n_rows]
@@ -522,7 +529,7 @@ static_assert(192 + sizeof(Ctx) <= 1024 - 128, "context does not fit the barrier
 
 #define FW_STAMP(i)                                                                                    \
     do {                                                                                               \
-        if (a.phase_ns && l == cx.stamp_layer && blockIdx.x == 0 && threadIdx.x == 0) a.phase_ns[i] = gtimer(); \
+        if (a.phase_ns && l == cx.stamp_layer && (int)blockIdx.x == a.stamp_cta && threadIdx.x == 0) a.phase_ns[i] = gtimer(); \
     } while (0)
 
 __device__ __forceinline__ FusedLayer layer_of(const FusedArgs& a, int l) { return a.layers ? a.layers[l] : a.single; }
@@ -682,7 +689,8 @@ __device__ __noinline__ void phase_scan(int l) {
     const int my_count = cx.my_count;
     const uint32_t scan_it = (uint32_t)l * (uint32_t)my_count;
     const FusedLayer ly = layer_of(a, l);
-    uint32_t* hist = a.hist + (size_t)(l & 1) * LQ_HIST_BINS;
+    uint32_t* hist = a.hist + (size_t)(l & 1) * FW_HIST_WORDS +
+                     (size_t)((blockIdx.x + (tid >> 5)) % FW_HIST_COPIES) * LQ_HIST_BINS;
     float* my_scores = sm.scores();
     float* wpart = sm.wpart();
     uint64_t* full = sm.full();
@@ -789,12 +797,18 @@ __device__ __noinline__ void phase_xhist(int l) {
     const FusedPeers& px = a.px;
     const int tid = threadIdx.x, par = l & 1;
     const uint32_t ep = x_epoch(a, l);
-    const uint2* hist2 = reinterpret_cast<const uint2*>(a.hist + (size_t)par * LQ_HIST_BINS);
+    const uint2* hist2 = reinterpret_cast<const uint2*>(a.hist + (size_t)par * FW_HIST_WORDS);
     constexpr int N2 = LQ_HIST_BINS / 2;
     const int per = (N2 + gridDim.x - 1) / gridDim.x, c0 = blockIdx.x * per, n = max(0, min(per, N2 - c0));
     for (int i = tid; i < n * px.world; i += FW_CONSUMERS) {
         const int p = i / n, j = i - p * n;
-        const uint2 v = __ldcg(hist2 + c0 + j);
+        uint2 v = make_uint2(0u, 0u);
+#pragma unroll
+        for (int hc = 0; hc < FW_HIST_COPIES; ++hc) {
+            const uint2 t = __ldcg(hist2 + (size_t)hc * N2 + c0 + j);
+            v.x += t.x;
+            v.y += t.y;
+        }
         line_store(reinterpret_cast<uint4*>(px.area[p] + px.off_hist) + (size_t)px.rank * N2 + c0 + j, v.x, v.y, ep);
     }
     if (blockIdx.x == 0 && tid < px.world)
@@ -812,7 +826,7 @@ __device__ __noinline__ void phase_select(int l) {
     const FusedArgs& a = cx.a;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int par = l & 1;
-    const uint32_t* hist = a.hist + (size_t)par * LQ_HIST_BINS;
+    const uint32_t* hist = a.hist + (size_t)par * FW_HIST_WORDS;
     int* s_ctl = sm.ctl();
     float* red = sm.red();
     float* my_scores = sm.scores();
@@ -865,7 +879,11 @@ __device__ __noinline__ void phase_select(int l) {
                         t4.x += w0[r]; t4.y += w1[r]; t4.z += w2[r]; t4.w += w3[r];
                     }
                 } else {
-                    t4 = __ldcg(reinterpret_cast<const uint4*>(hist + b0));
+#pragma unroll
+                    for (int hc = 0; hc < FW_HIST_COPIES; ++hc) {
+                        const uint4 t = __ldcg(reinterpret_cast<const uint4*>(hist + (size_t)hc * LQ_HIST_BINS + b0));
+                        t4.x += t.x; t4.y += t.y; t4.z += t.z; t4.w += t.w;
+                    }
                 }
             }
             const uint32_t own = t4.x + t4.y + t4.z + t4.w;
@@ -977,8 +995,13 @@ __device__ __noinline__ void phase_select(int l) {
     bar_sync(FW_BAR_CONS, FW_CONSUMERS);
     FW_STAMP(4);
     const int n_in_mine = s_ctl[SC_N_IN], n_band_mine = s_ctl[SC_N_BAND];
-
     // ---- exact re-score of own band rows (one warp per row), publish them ----------
+    // (this CTA's place in the band arrays is asked for first: the answer travels while the rows are re-scored)
+    int band_base_t0 = 0;
+    if (tid == 0) {
+        atomicAdd(&a.ctrs[CTR_IN], (uint32_t)n_in_mine);
+        band_base_t0 = n_band_mine ? (int)atomicAdd(&a.ctrs[CTR_BAND], (uint32_t)n_band_mine) : 0;
+    }
     {
         const FusedLayer ly = layer_of(a, l);
         const float* xs = sm.xs();
@@ -988,10 +1011,7 @@ __device__ __noinline__ void phase_select(int l) {
             if (lane == 0) band_ex[i] = v;
         }
     }
-    if (tid == 0) {
-        atomicAdd(&a.ctrs[CTR_IN], (uint32_t)n_in_mine);
-        s_ctl[SC_BAND_BASE] = n_band_mine ? (int)atomicAdd(&a.ctrs[CTR_BAND], (uint32_t)n_band_mine) : 0;
-    }
+    if (tid == 0) s_ctl[SC_BAND_BASE] = band_base_t0;
     bar_sync(FW_BAR_CONS, FW_CONSUMERS);
     {
         const int base = s_ctl[SC_BAND_BASE];
@@ -1366,8 +1386,9 @@ __device__ __noinline__ void phase_gather(int l) {
         for (int k = 0; k < cx.n_ahead; ++k) issue_tile(sm, nx, k, it0 + k);
     }
     // housekeeping for the layer after next (nobody reads these before two more grid barriers)
-    uint32_t* hist = a.hist + (size_t)(l & 1) * LQ_HIST_BINS;
-    for (int i = blockIdx.x * FW_CONSUMERS + tid; i < LQ_HIST_BINS; i += gridDim.x * FW_CONSUMERS) hist[i] = 0;
+    uint4* hist4 = reinterpret_cast<uint4*>(a.hist + (size_t)(l & 1) * FW_HIST_WORDS);
+    for (int i = blockIdx.x * FW_CONSUMERS + tid; i < FW_HIST_WORDS / 4; i += gridDim.x * FW_CONSUMERS)
+        hist4[i] = make_uint4(0u, 0u, 0u, 0u);
     if (blockIdx.x == 0 && tid == 0) {
         a.ctrs[CTR_BOUND0 + (l & 1)] = 0;
         a.ctrs[CTR_MAXBIN0 + (l & 1)] = 0;
@@ -1584,11 +1605,14 @@ size_t fused_q4k_ws_bytes(int hidden, int n_rows, int sm_count) {
     FusedGeom g;
     size_t pool = 0;
     if (fused_geom(hidden, n_rows, sm_count, g)) pool = ((size_t)sm_count * g.max_slots * 4 + 255) / 256 * 256;
-    return (size_t)2 * LQ_HIST_BINS * 4 + CTR_WORDS * 4 + (size_t)n_rows * 8 + 2 * pool + 4096 +
+    return (size_t)2 * FW_HIST_WORDS * 4 + 256 + (size_t)n_rows * 8 + 512 + 2 * pool + 4096 +
            (size_t)sm_count * hidden * 4 + (size_t)2 * hidden * 4 + 4096;
 }
 
 int fused_q4k_stamp_count() { return FW_STAMPS; }
+
+// The leading part of the workspace that a failed launch may leave dirty: histograms and counters.
+size_t fused_q4k_ws_dirty_bytes() { return (size_t)2 * FW_HIST_WORDS * 4 + 256; }
 
 namespace {
 
@@ -1629,10 +1653,14 @@ cudaError_t fill_args(FusedArgs& a, const FusedGeom& g, const void* layers_dev, 
     a.pf_dist = pf_dist_env;
     a.pf_tiles = (a.layers && n_layers > 1 && pf_env > 0) ? pf_env : 0;
     a.pf_late = pf_late_env ? 1 : 0;
+    {
+        const char* v = stats_dev ? getenv("LARQL_B200_FUSED_STAMP_CTA") : nullptr;  // (read per stamped launch: a diagnostic)
+        a.stamp_cta = v ? atoi(v) : 0;
+    }
     a.h_in = h_in;
     a.h_out = h_out;
     uint8_t* p = ws;
-    a.hist = reinterpret_cast<uint32_t*>(p);        p += (size_t)2 * LQ_HIST_BINS * 4;
+    a.hist = reinterpret_cast<uint32_t*>(p);        p += (size_t)2 * FW_HIST_WORDS * 4;
     a.ctrs = reinterpret_cast<uint32_t*>(p);        p += 256;
     a.band_row = reinterpret_cast<uint32_t*>(p);    p += ((size_t)n_rows * 4 + 255) / 256 * 256;
     a.band_exact = reinterpret_cast<float*>(p);     p += ((size_t)n_rows * 4 + 255) / 256 * 256;
