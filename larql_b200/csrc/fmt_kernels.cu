@@ -285,11 +285,25 @@ struct StagedGeom {
     static constexpr int WARP_BYTES = 32 * ROWB + 32 * 32;
 };
 
+// Two IEEE round-to-nearest f32 multiplies in one instruction (sm_100 packed f32x2): {a0 * b0, a1 * b1}.
+__device__ __forceinline__ void fmul2_rn(float a0, float a1, float b0, float b1, float& r0, float& r1) {
+    asm("{\n\t.reg .b64 ra, rb, rr;\n\t"
+        "mov.b64 ra, {%2, %3};\n\t"
+        "mov.b64 rb, {%4, %5};\n\t"
+        "mul.rn.f32x2 rr, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rr;\n\t}"
+        : "=f"(r0), "=f"(r1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+
 // The 32 reference products (decoded weight times activation, each rounded as the reference
-// rounds it) of one 32-element block of a staged row chunk.
+// rounds it) of one 32-element block of a staged row chunk.  For the FP4 formats the code -> value table
+// sits in the lanes of the warp (lane i holds the value of code i & 15, `lut`): a weight is decoded by one
+// shuffle whose source lane is the word shifted down to the nibble (a shuffle takes its source lane modulo
+// 32, and lanes 16..31 repeat the table), so every lane of the warp must call this together.
 template <int FMT>
 __device__ __forceinline__ void block_products(const uint8_t* mine, const uint8_t* sc, float ts, int b, const float* xc,
-                                               float (&p)[32]) {
+                                               float lut, float (&p)[32]) {
     float xe[32];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -308,16 +322,21 @@ __device__ __forceinline__ void block_products(const uint8_t* mine, const uint8_
     } else {
         const uint4 w = *reinterpret_cast<const uint4*>(mine + b * 16);
         const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+        float s0, s1;
         if (FMT == LQ_FMT_MXFP4) {
-            const float scale = e8m0_to_f32(sc[b]);
-#pragma unroll
-            for (int e = 0; e < 32; ++e)
-                p[e] = __fmul_rn(__fmul_rn(e2m1_to_f32((ww[e >> 3] >> (4 * (e & 7))) & 15u), scale), xe[e]);
+            s0 = s1 = e8m0_to_f32(sc[b]);
         } else {
-            const float s0 = __fmul_rn(ts, e4m3_to_f32(sc[2 * b])), s1 = __fmul_rn(ts, e4m3_to_f32(sc[2 * b + 1]));
+            s0 = __fmul_rn(ts, e4m3_to_f32(sc[2 * b]));
+            s1 = __fmul_rn(ts, e4m3_to_f32(sc[2 * b + 1]));
+        }
 #pragma unroll
-            for (int e = 0; e < 32; ++e)
-                p[e] = __fmul_rn(__fmul_rn(e < 16 ? s0 : s1, e2m1_to_f32((ww[e >> 3] >> (4 * (e & 7))) & 15u)), xe[e]);
+        for (int e = 0; e < 32; e += 2) {
+            const float v0 = __shfl_sync(0xffffffffu, lut, (int)(ww[e >> 3] >> (4 * (e & 7))));
+            const float v1 = __shfl_sync(0xffffffffu, lut, (int)(ww[e >> 3] >> (4 * (e & 7) + 4)));
+            const float s = e < 16 ? s0 : s1;
+            float w0, w1;
+            fmul2_rn(v0, v1, s, s, w0, w1);  // (multiplication commutes: the reference's scale * value or value * scale)
+            fmul2_rn(w0, w1, xe[e], xe[e + 1], p[e], p[e + 1]);
         }
     }
 }
@@ -364,6 +383,7 @@ __global__ void __launch_bounds__(128) scan_exact_staged_kernel(FmtMat m, const 
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     float acc = 0.0f;
+    const float lut = fp4_lut_lane(lane);
     stage(0);
     for (int c = 0; c < n_chunks; ++c) {
         if (c + 1 < n_chunks) {
@@ -380,9 +400,9 @@ __global__ void __launch_bounds__(128) scan_exact_staged_kernel(FmtMat m, const 
         // products of block b+1 are independent of the running sum: they fill the issue slots that
         // the chain of dependent adds of block b leaves empty
         float p[32], pn[32];
-        block_products<FMT>(mine, sc, m.ts, 0, xc, p);
+        block_products<FMT>(mine, sc, m.ts, 0, xc, lut, p);
         for (int b = 0; b < 8; ++b) {
-            if (b + 1 < 8) block_products<FMT>(mine, sc, m.ts, b + 1, xc, pn);
+            if (b + 1 < 8) block_products<FMT>(mine, sc, m.ts, b + 1, xc, lut, pn);
 #pragma unroll
             for (int e = 0; e < 32; ++e) acc = __fadd_rn(acc, p[e]);
 #pragma unroll
@@ -437,6 +457,53 @@ __device__ __forceinline__ void decode_block32(const FmtMat& m, size_t row, int 
     }
 }
 
+// Packed f32x2 helpers (sm_100): two IEEE round-to-nearest operations per instruction on register pairs.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
+// One 32-weight block of an FP4 row as stored: 16 bytes of codes and its scale byte(s).
+template <int FMT>
+__device__ __forceinline__ void load_raw32(const FmtMat& m, size_t row, int blk, uint4& w, uint32_t& sc) {
+    const size_t nblk = (size_t)(m.cols / 32);
+    w = *reinterpret_cast<const uint4*>(m.data + (row * nblk + blk) * 16);
+    if (FMT == LQ_FMT_MXFP4) sc = m.scales[row * nblk + blk];
+    else sc = *reinterpret_cast<const uint16_t*>(m.scales + (row * nblk + blk) * 2);
+}
+// acc += act * dequantised block, the weights decoded as the reference's dequantiser does (scale * value,
+// rounded once); the code -> value table sits in the lanes of the warp (`lut`), so every lane calls this together.
+template <int FMT>
+__device__ __forceinline__ void axpy_raw32(const uint4& w, uint32_t sc, float ts, float act, float lut,
+                                           unsigned long long (&acc2)[16]) {
+    float s0, s1;
+    if (FMT == LQ_FMT_MXFP4) {
+        s0 = s1 = e8m0_to_f32(sc);
+    } else {
+        s0 = __fmul_rn(ts, e4m3_to_f32(sc & 0xff));
+        s1 = __fmul_rn(ts, e4m3_to_f32(sc >> 8));
+    }
+    const unsigned long long s0p = pack2(s0, s0), s1p = pack2(s1, s1), ap = pack2(act, act);
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+        const float v0 = __shfl_sync(0xffffffffu, lut, (int)(ww[e >> 3] >> (4 * (e & 7))));
+        const float v1 = __shfl_sync(0xffffffffu, lut, (int)(ww[e >> 3] >> (4 * (e & 7) + 4)));
+        acc2[e >> 1] = fma2(ap, mul2(pack2(v0, v1), e < 16 ? s0p : s1p), acc2[e >> 1]);
+    }
+}
+
 template <int FMT, int BPT>
 __global__ void __launch_bounds__(FK_THREADS) gather_fmt_kernel(FmtMat up, FmtMat down, XPrep xp,
                                                                const uint32_t* __restrict__ hit_idx,
@@ -448,11 +515,17 @@ __global__ void __launch_bounds__(FK_THREADS) gather_fmt_kernel(FmtMat up, FmtMa
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int H = up.cols, nblk = H / 32;
     const float lut = fp4_lut_lane(lane);
-    float acc[BPT][32];
+    constexpr bool FP4 = FMT != LQ_FMT_Q8_0;
+    float acc[FP4 ? 1 : BPT][32];            // Q8_0
+    unsigned long long acc2[FP4 ? BPT : 1][16];  // FP4 formats: packed pairs
 #pragma unroll
-    for (int b = 0; b < BPT; ++b)
+    for (int b = 0; b < (FP4 ? 1 : BPT); ++b)
 #pragma unroll
         for (int e = 0; e < 32; ++e) acc[b][e] = 0.0f;
+#pragma unroll
+    for (int b = 0; b < (FP4 ? BPT : 1); ++b)
+#pragma unroll
+        for (int e = 0; e < 16; ++e) acc2[b][e] = 0ull;
     const int n_hits = n_hits_dev ? *n_hits_dev : n_hits_host;
     const int per = (n_hits + gridDim.x - 1) / gridDim.x;
     const int h0 = min(n_hits, (int)blockIdx.x * per), h1 = min(n_hits, h0 + per);
@@ -471,18 +544,56 @@ __global__ void __launch_bounds__(FK_THREADS) gather_fmt_kernel(FmtMat up, FmtMa
             }
         }
         __syncthreads();
-        for (int i = 0; i < nh; ++i) {
-            const float act = act_s[i];
-            if (act == 0.0f) continue;
-            const size_t row = row_s[i];
+        if (FP4) {
+            // The raw blocks of the next DEPTH hits are in flight while one hit is decoded and added: a hit's row is
+            // known only from the list, so nothing else hides the latency of its first touch.
+            constexpr int DEPTH = 4;
+            uint4 wq[DEPTH][BPT];
+            uint32_t sq[DEPTH][BPT];
+            auto fetch = [&](int i, uint4 (&wv)[BPT], uint32_t (&sv)[BPT]) {
 #pragma unroll
-            for (int b = 0; b < BPT; ++b) {
-                const int blk = tid + b * FK_THREADS;
-                if (blk < nblk) {
-                    float v[32];
-                    decode_block32<FMT>(down, row, blk, v);
+                for (int b = 0; b < BPT; ++b) {
+                    const int blk = tid + b * FK_THREADS;
+                    wv[b] = make_uint4(0u, 0u, 0u, 0u);
+                    sv[b] = 0u;
+                    if (i < nh && blk < nblk) load_raw32<FMT>(down, (size_t)row_s[i], blk, wv[b], sv[b]);
+                }
+            };
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) acc[b][e] = fmaf(act, v[e], acc[b][e]);
+            for (int u = 0; u < DEPTH; ++u) fetch(u, wq[u], sq[u]);
+            for (int i0 = 0; i0 < nh; i0 += DEPTH) {
+#pragma unroll
+                for (int u = 0; u < DEPTH; ++u) {
+                    const int i = i0 + u;
+                    uint4 wc[BPT];
+                    uint32_t sc[BPT];
+#pragma unroll
+                    for (int b = 0; b < BPT; ++b) {
+                        wc[b] = wq[u][b];
+                        sc[b] = sq[u][b];
+                    }
+                    fetch(i + DEPTH, wq[u], sq[u]);
+                    const float act = i < nh ? act_s[i] : 0.0f;
+                    if (act != 0.0f) {  // (the same for every thread of the CTA)
+#pragma unroll
+                        for (int b = 0; b < BPT; ++b) axpy_raw32<FMT>(wc[b], sc[b], down.ts, act, lut, acc2[b]);
+                    }
+                }
+            }
+        } else {
+            for (int i = 0; i < nh; ++i) {
+                const float act = act_s[i];
+                if (act == 0.0f) continue;
+                const size_t row = row_s[i];
+#pragma unroll
+                for (int b = 0; b < BPT; ++b) {
+                    const int blk = tid + b * FK_THREADS;
+                    if (blk < nblk) {
+                        float v[32];
+                        decode_block32<FMT>(down, row, blk, v);
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) acc[b][e] = fmaf(act, v[e], acc[b][e]);
+                    }
                 }
             }
         }
@@ -493,9 +604,15 @@ __global__ void __launch_bounds__(FK_THREADS) gather_fmt_kernel(FmtMat up, FmtMa
     for (int b = 0; b < BPT; ++b) {
         const int blk = tid + b * FK_THREADS;
         if (blk < nblk) {
+            if (FP4) {
 #pragma unroll
-            for (int e = 0; e < 32; e += 4)
-                *reinterpret_cast<float4*>(dst + blk * 32 + e) = make_float4(acc[b][e], acc[b][e + 1], acc[b][e + 2], acc[b][e + 3]);
+                for (int e = 0; e < 16; e += 2)
+                    *reinterpret_cast<ulonglong2*>(dst + blk * 32 + 2 * e) = make_ulonglong2(acc2[b][e], acc2[b][e + 1]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 32; e += 4)
+                    *reinterpret_cast<float4*>(dst + blk * 32 + e) = make_float4(acc[b][e], acc[b][e + 1], acc[b][e + 2], acc[b][e + 3]);
+            }
         }
     }
 }

@@ -8,26 +8,33 @@ namespace lq {
 
 // xs: the activation in shared memory, 64-float chunks at a stride of 68 floats so that the
 // eight lanes of a 128-bit load phase (chunks 64 floats apart) fall in different banks.
+// IN_SMEM: the row was staged in shared memory (plain loads); otherwise it is read from global memory through
+// the read-only path.
+template <bool IN_SMEM = false>
 __device__ __forceinline__ float exact_row_q4k(const uint8_t* __restrict__ row, const float* __restrict__ xs, int nsb,
                                                float* sb_part /* [nsb] per-warp scratch */, int lane) {
     const int g = lane & 3;
+    auto ld16 = [](const uint8_t* p) -> uint4 {
+        return IN_SMEM ? *reinterpret_cast<const uint4*>(p) : __ldg(reinterpret_cast<const uint4*>(p));
+    };
     // The loads of the next eight super-blocks are issued before the current eight are summed, so the
     // passes of a row overlap their memory latency (the arithmetic and its order are unchanged).
     uint4 n_hdr = make_uint4(0u, 0u, 0u, 0u), n_q0 = n_hdr, n_q1 = n_hdr;
     if ((lane >> 2) < nsb) {
         const uint8_t* cell = row + (size_t)(lane >> 2) * 144;
-        n_hdr = __ldg(reinterpret_cast<const uint4*>(cell));
-        n_q0 = __ldg(reinterpret_cast<const uint4*>(cell + 16 + g * 32));
-        n_q1 = __ldg(reinterpret_cast<const uint4*>(cell + 32 + g * 32));
+        n_hdr = ld16(cell);
+        n_q0 = ld16(cell + 16 + g * 32);
+        n_q1 = ld16(cell + 32 + g * 32);
     }
+#pragma unroll 1
     for (int s0 = 0; s0 < nsb; s0 += 8) {
         const int s = s0 + (lane >> 2);
         const uint4 hdr = n_hdr, q0 = n_q0, q1 = n_q1;
         if (s + 8 < nsb) {
             const uint8_t* cell = row + (size_t)(s + 8) * 144;
-            n_hdr = __ldg(reinterpret_cast<const uint4*>(cell));
-            n_q0 = __ldg(reinterpret_cast<const uint4*>(cell + 16 + g * 32));
-            n_q1 = __ldg(reinterpret_cast<const uint4*>(cell + 32 + g * 32));
+            n_hdr = ld16(cell);
+            n_q0 = ld16(cell + 16 + g * 32);
+            n_q1 = ld16(cell + 32 + g * 32);
         }
         float u_lo = 0.0f, u_hi = 0.0f;
         if (s < nsb) {

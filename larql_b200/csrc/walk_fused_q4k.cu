@@ -74,6 +74,8 @@ struct FusedGeom {
     int row_bytes, R, Rt;       // rows per scan tile, rows per team per tile
     int tile_bytes, S;          // scan ring
     int D2;                     // rows of one gather chunk (down rows staged in the idle ring)
+    int E;                      // ring slots that may be filled before the final pick (the pick stages a small band behind them)
+    int off_pick;               // where in the ring the pick stages a band of up to FW_RANK_CAP entries
     int max_slots;              // score slots per CTA (tiles per CTA * R)
     int off_xs, off_xa, off_xb, off_blk, off_wpart, off_psum, off_scores, off_lists, off_red, off_ring;
     int ring_bytes, smem_bytes;
@@ -184,6 +186,10 @@ __host__ inline bool fused_geom(int hidden, int n_rows, int grid_hint, FusedGeom
     if (g.S > FW_MAX_STAGES) g.S = FW_MAX_STAGES;
     g.D2 = g.ring_bytes / g.row_bytes;
     if (g.D2 > FW_MAX_GROWS) g.D2 = FW_MAX_GROWS;
+    const int pick_small = fw_align(FW_RANK_CAP * 8 + g.max_slots * 4, 128);
+    g.off_pick = g.ring_bytes - pick_small;
+    g.E = g.off_pick / g.row_bytes;
+    if (g.E > g.D2) g.E = g.D2;
     g.smem_bytes = off + g.ring_bytes;
     return true;
 }
@@ -352,6 +358,59 @@ __device__ __forceinline__ float cell_value(const uint4& hdr, const uint4& q0, c
            dmin * ((float)(m2 & 0xff) * x.su_lo + (float)(m2 >> 8) * x.su_hi);
 }
 
+// One cell (registers) against the activation planes read from shared memory: the same value as
+// cell_value(), for code that cannot afford to keep a CellX in registers.
+__device__ __forceinline__ float cell_value_smem(const uint4& hdr, const uint4& q0, const uint4& q1, int g,
+                                                 const uint32_t* xa, const uint32_t* xb, const float* blk, int nblk,
+                                                 int blk_lo, int G, int c) {
+    const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    int ia_lo = 0, ib_lo = 0, ia_hi = 0, ib_hi = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t lo = qw[j] & 0x0F0F0F0Fu, hi = qw[j] & 0xF0F0F0F0u;
+        ia_lo = dp4a_us(lo, xa[j * G + c], ia_lo);
+        ib_lo = dp4a_uu(lo, xb[j * G + c], ib_lo);
+        ia_hi = dp4a_us(hi, xa[(8 + j) * G + c], ia_hi);
+        ib_hi = dp4a_uu(hi, xb[(8 + j) * G + c], ib_hi);
+    }
+    const float d = f16_bits_to_f32(hdr.x), dmin = f16_bits_to_f32(hdr.x >> 16);
+    uint32_t sc2, m2;
+    q4k_pair_scales(hdr.y, hdr.z, hdr.w, g, sc2, m2);
+    const float dot_lo = blk[blk_lo] * (float)(ia_lo * 256 + ib_lo);
+    const float dot_hi = blk[blk_lo + 1] * (float)((ia_hi * 256 + ib_hi) >> 4);
+    return d * ((float)(sc2 & 0xff) * dot_lo + (float)(sc2 >> 8) * dot_hi) -
+           dmin * ((float)(m2 & 0xff) * blk[nblk + blk_lo] + (float)(m2 >> 8) * blk[nblk + blk_lo + 1]);
+}
+
+// out += act * (one 64-weight cell of a down row), into the thread's 64 accumulators.  q enters as
+// f = 1 + q/128 built by a byte permute: out += A*f, corrected by -A at the end (corr_*).
+__device__ __forceinline__ void axpy_cell(const uint8_t* cell, int g, float act, float (&acc_lo)[32], float (&acc_hi)[32],
+                                          float& corr_lo, float& corr_hi) {
+    const uint4 hdr = *reinterpret_cast<const uint4*>(cell);
+    const uint4 d0 = *reinterpret_cast<const uint4*>(cell + 16 + g * 32);
+    const uint4 d1 = *reinterpret_cast<const uint4*>(cell + 32 + g * 32);
+    const uint32_t qw[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+    const float d = f16_bits_to_f32(hdr.x), dmin = f16_bits_to_f32(hdr.x >> 16);
+    uint32_t sc2, m2;
+    q4k_pair_scales(hdr.y, hdr.z, hdr.w, g, sc2, m2);
+    const float ad = act * d, am = act * dmin;
+    const float A_lo = ad * (float)(sc2 & 0xff) * 128.0f, A_hi = ad * (float)(sc2 >> 8) * 128.0f;
+    corr_lo += A_lo + am * (float)(m2 & 0xff);
+    corr_hi += A_hi + am * (float)(m2 >> 8);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t lo = (qw[j] & 0x0F0F0F0Fu) | 0x80808080u;
+        const uint32_t hi = ((qw[j] >> 4) & 0x0F0F0F0Fu) | 0x80808080u;
+#pragma unroll
+        for (int bb = 0; bb < 4; ++bb) {
+            const float fl = __uint_as_float(__byte_perm(lo, 0x3F000000u, 0x7044u | (bb << 8)));
+            const float fh = __uint_as_float(__byte_perm(hi, 0x3F000000u, 0x7044u | (bb << 8)));
+            acc_lo[4 * j + bb] = fmaf(A_lo, fl, acc_lo[4 * j + bb]);
+            acc_hi[4 * j + bb] = fmaf(A_hi, fh, acc_hi[4 * j + bb]);
+        }
+    }
+}
+
 // Gather of one chunk of rows (global row numbers and gate scores in shared memory).
 // Team t takes items t, t+P, ...; a thread owns one 64-weight cell of every row.
 //   1. the chunk's up rows move into the idle ring (row i at i * row_bytes): one TMA bulk copy per row,
@@ -391,6 +450,7 @@ __device__ __forceinline__ void gather_stage(const GatherArgs& ga, int base, int
         mbar_expect_tx(ga.bar, (uint32_t)nn * (uint32_t)ga.row_bytes);  // the down rows follow slot by slot
     }
     bar_sync(FW_BAR_CONS, FW_CONSUMERS);  // the expectations are armed before any copy can complete
+#pragma unroll 1
     for (int i = tid; i < nn; i += FW_CONSUMERS)
         tma_bulk_g2s(ga.ring + (size_t)i * ga.row_bytes, ga.up + (size_t)(uint32_t)ga.rows[base + i] * ga.row_bytes,
                      (uint32_t)ga.row_bytes, ga.ubar);
@@ -403,6 +463,7 @@ __device__ __forceinline__ void gather_stage(const GatherArgs& ga, int base, int
             load_cellx(x, ga.xa_s, ga.xb_s, ga.blk_s, nblk, (cl >> 2) * 8 + 2 * (cl & 3), ga.G, cl);
         }
         if (!failed && !mbar_wait(ga.ubar, bar_parity)) failed = true;
+#pragma unroll 1
         for (int i = team; i < nn; i += P) {
             float val = 0.0f;
             if (active) {
@@ -426,8 +487,10 @@ __device__ __forceinline__ void gather_stage(const GatherArgs& ga, int base, int
     }
     bar_sync(FW_BAR_CONS, FW_CONSUMERS);
     // 3. activations
+#pragma unroll 1
     for (int i = tid; i < nn; i += FW_CONSUMERS) {
         float upv = 0.0f;
+#pragma unroll 1
         for (int w = 0; w < ga.Wt; ++w) upv += ga.psum[i * ga.Wt + w];
         const float gs = ga.scores[base + i];
         const float sig = __fdiv_rn(1.0f, 1.0f + expf(-gs));
@@ -442,34 +505,11 @@ __device__ __forceinline__ void gather_stage(const GatherArgs& ga, int base, int
     for (int j = 0; j < 32; ++j) acc_lo[j] = acc_hi[j] = 0.0f;
     float corr_lo = 0.0f, corr_hi = 0.0f;
     if (active) {
+#pragma unroll 1
         for (int i = team; i < nn; i += P) {
             const float act = ga.act[i];
             if (act == 0.0f) continue;
-            const uint8_t* cell = ga.ring + (size_t)i * ga.row_bytes + s * 144;
-            const uint4 hdr = *reinterpret_cast<const uint4*>(cell);
-            const uint4 d0 = *reinterpret_cast<const uint4*>(cell + 16 + g * 32);
-            const uint4 d1 = *reinterpret_cast<const uint4*>(cell + 32 + g * 32);
-            const uint32_t qw[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
-            const float d = f16_bits_to_f32(hdr.x), dmin = f16_bits_to_f32(hdr.x >> 16);
-            uint32_t sc2, m2;
-            q4k_pair_scales(hdr.y, hdr.z, hdr.w, g, sc2, m2);
-            const float ad = act * d, am = act * dmin;
-            // q enters as f = 1 + q/128 built by a byte permute; out += A*f, corrected by -A at the end
-            const float A_lo = ad * (float)(sc2 & 0xff) * 128.0f, A_hi = ad * (float)(sc2 >> 8) * 128.0f;
-            corr_lo += A_lo + am * (float)(m2 & 0xff);
-            corr_hi += A_hi + am * (float)(m2 >> 8);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const uint32_t lo = (qw[j] & 0x0F0F0F0Fu) | 0x80808080u;
-                const uint32_t hi = ((qw[j] >> 4) & 0x0F0F0F0Fu) | 0x80808080u;
-#pragma unroll
-                for (int bb = 0; bb < 4; ++bb) {
-                    const float fl = __uint_as_float(__byte_perm(lo, 0x3F000000u, 0x7044u | (bb << 8)));
-                    const float fh = __uint_as_float(__byte_perm(hi, 0x3F000000u, 0x7044u | (bb << 8)));
-                    acc_lo[4 * j + bb] = fmaf(A_lo, fl, acc_lo[4 * j + bb]);
-                    acc_hi[4 * j + bb] = fmaf(A_hi, fh, acc_hi[4 * j + bb]);
-                }
-            }
+            axpy_cell(ga.ring + (size_t)i * ga.row_bytes + s * 144, g, act, acc_lo, acc_hi, corr_lo, corr_hi);
         }
     }
     // 5. every team has finished reading the staged rows: the ring now takes the accumulators
@@ -498,13 +538,17 @@ struct Ctx {
 
 // control words (ints), in the last 64 bytes of the barrier page
 enum { SC_N_IN = 0, SC_N_BAND = 1, SC_N_G2 = 2, SC_BAND_BASE = 3, SC_BSTAR = 4, SC_HIT_BASE = 5, SC_FAILED = 6,
-       SC_FOUND = 7, SC_GATHER_USES = 9, SC_N_KEEP = 10 };
+       SC_FOUND = 7, SC_GATHER_USES = 9, SC_N_KEEP = 10, SC_N_EARLY = 11, SC_BAND_USES = 12 };
 
 struct Smem {
     uint8_t* base;
     __device__ __forceinline__ Ctx& cx() const { return *reinterpret_cast<Ctx*>(base + 192); }
     __device__ __forceinline__ uint64_t* full() const { return reinterpret_cast<uint64_t*>(base); }
     __device__ __forceinline__ uint64_t* gbar() const { return reinterpret_cast<uint64_t*>(base) + 2 * FW_MAX_STAGES; }
+    // mbarriers of a layer's first gather chunk, each completing exactly once per layer (phase parity = layer & 1):
+    // up rows staged before the pick, their down rows, the up rows of the rows added by the pick, their down rows;
+    // ebar(4): the band rows staged for the exact re-score (its phase parity is counted in SC_BAND_USES)
+    __device__ __forceinline__ uint64_t* ebar(int i) const { return gbar() + 2 + i; }
     __device__ __forceinline__ int* ctl() const { return reinterpret_cast<int*>(base + 1024 - 64); }
     // warps that have finished reading each ring stage's current tile
     __device__ __forceinline__ int* released() const { return reinterpret_cast<int*>(base + 1024 - 128); }
@@ -601,6 +645,7 @@ __device__ __noinline__ void phase_prepare(int l, const float* h_cur) {
         if (lane == 0) dred[warp] = sq;
         bar_sync(FW_BAR_CONS, FW_CONSUMERS);
         double t = 0.0;
+#pragma unroll 1
         for (int w = 0; w < FW_NWARPS; ++w) t += dred[w];
         rms = (float)sqrt(t / (double)hidden + 1e-6);
     } else {
@@ -708,6 +753,7 @@ __device__ __noinline__ void phase_scan(int l) {
     int* released = sm.released();
     const int covered = tiles_covered_at_scan_start(cx);
     if (l == 0 && tid == 0 && a.pf_dist > 0) prefetch_tiles(sm, ly, gm.S, covered);  // later layers: done in the previous tail
+#pragma unroll 1
     for (int k = 0; k < my_count; ++k) {
         const uint32_t it = scan_it + k;
         const int stg = it % gm.S;
@@ -718,6 +764,7 @@ __device__ __noinline__ void phase_scan(int l) {
         float* wp = wpart + (size_t)k * R * gm.Wt;  // [row of the tile][warp of the team]
         if (in_team) {
             // rows past the end of a ragged last tile are computed on whatever the stage holds and discarded
+#pragma unroll 1
             for (int j = 0; j < gm.Rt; ++j) {
                 const int r0 = team + j * P;
                 const bool ok0 = active && r0 < rows_here;
@@ -742,8 +789,10 @@ __device__ __noinline__ void phase_scan(int l) {
     }
     // every warp's partials are in place: scores of this CTA's rows, histogram, largest occupied bin
     bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+#pragma unroll 1
     for (int m = tid; m < cx.n_slots; m += FW_CONSUMERS) {
         float sc = 0.0f;
+#pragma unroll 1
         for (int w = 0; w < gm.Wt; ++w) sc += wpart[m * gm.Wt + w];
         my_scores[m] = sc;
         if (row_of_slot(cx, m) < a.n_rows) {
@@ -766,18 +815,23 @@ __device__ __noinline__ void phase_scan(int l) {
             wk[tid >> 5] = kmax;
         }
         bar_sync(FW_BAR_CONS, FW_CONSUMERS);
-        if (tid == 0) {
+        if (tid < 32) {
+            // lane t: the bound of team t (its warps' partials in warp order) and the largest bin of warp t
             float best = 0.0f;
-            for (int t = 0; t < P; ++t) {
-                float sum = 0.0f;
-                for (int w = 0; w < gm.Wt; ++w) sum += wb[t * gm.Wt + w];
-                best = fmaxf(best, sum);
+            if (lane < P) {
+#pragma unroll 1
+                for (int w = 0; w < gm.Wt; ++w) best += wb[lane * gm.Wt + w];
+            }
+            uint32_t kb = lane < FW_NWARPS ? wk[lane] : 0u;
+            for (int o = 16; o > 0; o >>= 1) {
+                best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o));
+                kb = max(kb, __shfl_xor_sync(0xffffffffu, kb, o));
             }
             best *= 1.0001f;  // the sums above round to nearest
-            uint32_t kb = 0u;
-            for (int w = 0; w < FW_NWARPS; ++w) kb = max(kb, wk[w]);
-            if (best > 0.0f) atomicMax(&a.ctrs[CTR_BOUND0 + (l & 1)], __float_as_uint(best));
-            if (kb > 0u) atomicMax(&a.ctrs[CTR_MAXBIN0 + (l & 1)], kb);
+            if (lane == 0) {
+                if (best > 0.0f) atomicMax(&a.ctrs[CTR_BOUND0 + (l & 1)], __float_as_uint(best));
+                if (kb > 0u) atomicMax(&a.ctrs[CTR_MAXBIN0 + (l & 1)], kb);
+            }
         }
     }
     if (tid == 0) {
@@ -800,6 +854,7 @@ __device__ __noinline__ void phase_xhist(int l) {
     const uint2* hist2 = reinterpret_cast<const uint2*>(a.hist + (size_t)par * FW_HIST_WORDS);
     constexpr int N2 = LQ_HIST_BINS / 2;
     const int per = (N2 + gridDim.x - 1) / gridDim.x, c0 = blockIdx.x * per, n = max(0, min(per, N2 - c0));
+#pragma unroll 1
     for (int i = tid; i < n * px.world; i += FW_CONSUMERS) {
         const int p = i / n, j = i - p * n;
         uint2 v = make_uint2(0u, 0u);
@@ -863,6 +918,7 @@ __device__ __noinline__ void phase_select(int l) {
         const uint32_t K = (uint32_t)a.top_k;
         uint32_t* wsum = reinterpret_cast<uint32_t*>(red);
         uint32_t above_total = 0;
+#pragma unroll 1
         for (int base_end = (int)(maxbin / 4u + 1u) * 4; base_end > 0; base_end -= 4 * HT) {
             const int b0 = base_end - 4 * (tid + 1);
             uint4 t4 = make_uint4(0u, 0u, 0u, 0u);
@@ -947,6 +1003,7 @@ __device__ __noinline__ void phase_select(int l) {
             return v > hi ? 1 : (v >= lo ? 2 : 0);
         };
         int ca = 0, cb = 0;
+#pragma unroll 1
         for (int m0 = beg; m0 < end; m0 += 32) {
             const int m = m0 + lane;
             const int cc = m < end ? cls(m) : 0;
@@ -959,6 +1016,7 @@ __device__ __noinline__ void phase_select(int l) {
         }
         bar_sync(FW_BAR_CONS, FW_CONSUMERS);
         int oa = 0, ob = 0, ta = 0, tb2 = 0;
+#pragma unroll 1
         for (int w = 0; w < FW_NWARPS; ++w) {
             if (w < warp) {
                 oa += wcnt[w];
@@ -969,6 +1027,7 @@ __device__ __noinline__ void phase_select(int l) {
         }
         const int n_ctas = (int)gridDim.x * (X ? a.px.world : 1);
         n_fair = max(0, (a.top_k + n_ctas - 1) / n_ctas + 1 - tb2);
+#pragma unroll 1
         for (int m0 = beg; m0 < end; m0 += 32) {
             const int m = m0 + lane;
             const int cc = m < end ? cls(m) : 0;
@@ -990,11 +1049,40 @@ __device__ __noinline__ void phase_select(int l) {
             s_ctl[SC_N_IN] = ta;     // certainly-in rows of this CTA
             s_ctl[SC_N_BAND] = tb2;  // band rows of this CTA
             s_ctl[SC_N_KEEP] = min(ta, n_fair);
+            // The rows this CTA will gather whatever the pick decides (its own certainly-in rows up to the fair
+            // share) do not wait for the pick: their up rows start moving into the idle ring now, the up dots
+            // run while the grid barrier collects, and their down rows land while the pick runs.
+            const int n_early = min(min(ta, n_fair), gm.E);
+            s_ctl[SC_N_EARLY] = n_early;
+            mbar_expect_tx(sm.ebar(0), (uint32_t)n_early * (uint32_t)gm.row_bytes);
+            mbar_expect_tx(sm.ebar(1), (uint32_t)n_early * (uint32_t)gm.row_bytes);
         }
     }
     bar_sync(FW_BAR_CONS, FW_CONSUMERS);
     FW_STAMP(4);
     const int n_in_mine = s_ctl[SC_N_IN], n_band_mine = s_ctl[SC_N_BAND];
+    // The band rows of the gate matrix are staged for the exact re-score in the slots behind the early rows,
+    // and asked for FIRST: the re-score is on the critical path, the early rows have until the pick is over.
+    const int n_early_sel = s_ctl[SC_N_EARLY];
+    const int band_cap = max(1, gm.E - n_early_sel);  // band rows staged per round
+    uint32_t band_uses = (uint32_t)s_ctl[SC_BAND_USES];
+    {
+        const FusedLayer ly = layer_of(a, l);
+        const int nb0 = min(n_band_mine, band_cap);
+        if (tid == 0 && nb0 > 0) mbar_expect_tx(sm.ebar(4), (uint32_t)nb0 * (uint32_t)gm.row_bytes);
+        // (armed by thread 0, in program order, before it issues the first copy; copies of other warps may only
+        // complete later than that: see the barrier below)
+        if (nb0 > 32) bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+        else __syncwarp();
+#pragma unroll 1
+        for (int i = tid; i < nb0; i += FW_CONSUMERS)
+            tma_bulk_g2s(sm.ring() + (size_t)(n_early_sel + i) * gm.row_bytes,
+                         ly.gate + (size_t)row_of_slot(cx, band_list[i]) * gm.row_bytes, (uint32_t)gm.row_bytes, sm.ebar(4));
+#pragma unroll 1
+        for (int i = tid; i < n_early_sel; i += FW_CONSUMERS)
+            tma_bulk_g2s(sm.ring() + (size_t)i * gm.row_bytes, ly.up + (size_t)(uint32_t)g2_rows[i] * gm.row_bytes,
+                         (uint32_t)gm.row_bytes, sm.ebar(0));
+    }
     // ---- exact re-score of own band rows (one warp per row), publish them ----------
     // (this CTA's place in the band arrays is asked for first: the answer travels while the rows are re-scored)
     int band_base_t0 = 0;
@@ -1005,16 +1093,40 @@ __device__ __noinline__ void phase_select(int l) {
     {
         const FusedLayer ly = layer_of(a, l);
         const float* xs = sm.xs();
-        for (int i = warp; i < n_band_mine; i += FW_NWARPS) {
-            const size_t row = (size_t)row_of_slot(cx, band_list[i]);
-            const float v = exact_row_q4k(ly.gate + row * gm.row_bytes, xs, gm.nsb, red + 256 + warp * gm.nsb, lane);
-            if (lane == 0) band_ex[i] = v;
+        const uint8_t* stage = sm.ring() + (size_t)n_early_sel * gm.row_bytes;
+#pragma unroll 1
+        for (int r0 = 0; r0 < n_band_mine; r0 += band_cap) {
+            const int nb = min(band_cap, n_band_mine - r0);
+            if (r0 > 0) {
+                // (a CTA with more band rows than free slots: further rounds through the same slots)
+                bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+                if (tid == 0) {
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    mbar_expect_tx(sm.ebar(4), (uint32_t)nb * (uint32_t)gm.row_bytes);
+#pragma unroll 1
+                    for (int i = 0; i < nb; ++i)
+                        tma_bulk_g2s(sm.ring() + (size_t)(n_early_sel + i) * gm.row_bytes,
+                                     ly.gate + (size_t)row_of_slot(cx, band_list[r0 + i]) * gm.row_bytes,
+                                     (uint32_t)gm.row_bytes, sm.ebar(4));
+                }
+            }
+            if (!mbar_wait(sm.ebar(4), band_uses & 1u)) s_ctl[SC_FAILED] = 1;
+            band_uses += 1;
+#pragma unroll 1
+            for (int i = warp; i < nb; i += FW_NWARPS) {
+                const float v = exact_row_q4k<true>(stage + (size_t)i * gm.row_bytes, xs, gm.nsb, red + 256 + warp * gm.nsb, lane);
+                if (lane == 0) band_ex[r0 + i] = v;
+            }
         }
     }
-    if (tid == 0) s_ctl[SC_BAND_BASE] = band_base_t0;
+    if (tid == 0) {
+        s_ctl[SC_BAND_BASE] = band_base_t0;
+        s_ctl[SC_BAND_USES] = (int)band_uses;
+    }
     bar_sync(FW_BAR_CONS, FW_CONSUMERS);
     {
         const int base = s_ctl[SC_BAND_BASE];
+#pragma unroll 1
         for (int i = tid; i < n_band_mine; i += FW_CONSUMERS) {
             const float v = band_ex[i];
             if (v != v) set_err(a.err, DEV_ERR_NAN_SCORE);
@@ -1035,6 +1147,7 @@ __device__ __noinline__ void phase_select(int l) {
     {
         uint32_t* pr = a.pool_row + (size_t)blockIdx.x * gm.max_slots;
         float* ps = a.pool_score + (size_t)blockIdx.x * gm.max_slots;
+#pragma unroll 1
         for (int i = tid; i < n_over; i += FW_CONSUMERS) {
             const int m = in_list[n_keep + i];
             pr[i] = (uint32_t)row_of_slot(cx, m);
@@ -1061,6 +1174,133 @@ __device__ __noinline__ void phase_select(int l) {
             }
         }
     }
+}
+
+// ---- 2b. up dots of the rows staged before the pick; their down rows take the slots ----------------
+// Runs between the arrival at grid barrier B and the wait for it.  Team t takes rows t, t + P, ...; as soon as
+// a team is done with a row's slot, the same feature's down row starts moving into it.
+__device__ __noinline__ void phase_early(int l) {
+    extern __shared__ __align__(128) uint8_t smem[];  // the kernel's dynamic shared memory
+    const Smem sm{smem};
+    const Ctx& cx = sm.cx();
+    const FusedGeom& gm = cx.gm;
+    const FusedArgs& a = cx.a;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int team = tid / gm.TS, c = tid % gm.TS, wt = c >> 5;
+    const bool in_team = team < gm.P;
+    const bool active = in_team && c < gm.G;
+    const int s = c >> 2, g = c & 3, nblk = gm.nsb * 8;
+    int* s_ctl = sm.ctl();
+    const int n_early = s_ctl[SC_N_EARLY];
+    const uint32_t par = (uint32_t)l & 1u;
+    float* psum = sm.psum();
+    float* act_s = psum + FW_MAX_GROWS * gm.Wt;
+    const int* rows = sm.g_rows();
+    const float* scores = sm.g_scores();
+    uint8_t* ring = sm.ring();
+    const uint8_t* down = layer_of(a, l).down;
+    bool failed = false;
+    if (in_team) {
+        CellX x;
+        {
+            const int cl = active ? c : 0;  // unconditional: see the scan
+            load_cellx(x, sm.xa(), sm.xb(), sm.blk(), nblk, (cl >> 2) * 8 + 2 * (cl & 3), gm.G, cl);
+        }
+        if (!mbar_wait(sm.ebar(0), par)) failed = true;
+#pragma unroll 1
+        for (int i = team; i < n_early; i += gm.P) {
+            float val = 0.0f;
+            if (active) {
+                const uint8_t* cell = ring + (size_t)i * gm.row_bytes + s * 144;
+                const uint4 hd = *reinterpret_cast<const uint4*>(cell);
+                const uint4 q0 = *reinterpret_cast<const uint4*>(cell + 16 + g * 32);
+                const uint4 q1 = *reinterpret_cast<const uint4*>(cell + 32 + g * 32);
+                val = cell_value(hd, q0, q1, g, x);
+            }
+            for (int o = 16; o > 0; o >>= 1) val += __shfl_xor_sync(0xffffffffu, val, o);
+            if (lane == 0) psum[i * gm.Wt + wt] = val;
+            bar_sync(1 + team, gm.TS);  // every thread of the team is done with the up row
+            if (c == 0) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // plain reads before the TMA write
+                tma_bulk_g2s(ring + (size_t)i * gm.row_bytes, down + (size_t)(uint32_t)rows[i] * gm.row_bytes,
+                             (uint32_t)gm.row_bytes, sm.ebar(1));
+            }
+        }
+    } else if (!mbar_wait(sm.ebar(0), par)) {
+        failed = true;  // (threads outside the teams pass the phase too)
+    }
+    bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+#pragma unroll 1
+    for (int i = tid; i < n_early; i += FW_CONSUMERS) {
+        float upv = 0.0f;
+#pragma unroll 1
+        for (int w = 0; w < gm.Wt; ++w) upv += psum[i * gm.Wt + w];
+        const float gs = scores[i];
+        const float sig = __fdiv_rn(1.0f, 1.0f + expf(-gs));
+        const float act = (gs * sig) * upv;
+        act_s[i] = fabsf(act) > FW_NOISE_FLOOR ? act : 0.0f;
+    }
+    if (failed) s_ctl[SC_FAILED] = 1;
+}
+
+// The pick's rare path, kept out of line so that the usual path stays short: a band of more than
+// FW_RANK_CAP entries.  Radix select of the threshold key among all band entries, then of the row cut among
+// the entries that tie with it (the lowest rows win).  Up to FW_PICK_CAP entries are staged at the start of the
+// ring by the caller; beyond that every read goes back to the band arrays.
+template <bool X>
+__device__ __noinline__ void pick_big_band(int l, int n_band_tot, int need, const int* seg_pre, uint32_t& tau_key,
+                                           uint32_t& row_cut) {
+    extern __shared__ __align__(128) uint8_t smem[];  // the kernel's dynamic shared memory
+    const Smem sm{smem};
+    const FusedArgs& a = sm.cx().a;
+    uint8_t* ring = sm.ring();
+    const uint32_t* keys = reinterpret_cast<const uint32_t*>(ring);
+    const uint32_t* rows = keys + FW_PICK_CAP;
+    const bool staged = n_band_tot <= FW_PICK_CAP;
+    const uint32_t* band_row_g = a.band_row;
+    const float* band_exact_g = a.band_exact;
+    const uint4* band_lines = X ? reinterpret_cast<const uint4*>(a.px.area[a.px.rank] + a.px.off_band) : nullptr;
+    auto band_at = [&](int i) -> int {  // where entry i of all band entries sits in the band arrays
+        if (!X) return i;
+        int pre = 0, off = a.px.seg_off[0];
+#pragma unroll 1
+        for (int q = 1; q < a.px.world; ++q) {
+            if (i >= seg_pre[q]) {
+                pre = seg_pre[q];
+                off = a.px.seg_off[q];
+            }
+        }
+        return off + (i - pre);
+    };
+    SelectSmem<FW_CONSUMERS>& ssm = *reinterpret_cast<SelectSmem<FW_CONSUMERS>*>(ring + FW_PICK_CAP * 8);
+    int cnt_gt, need_eq;
+    // (a band too large to stage: every read waits for its line again, which costs nothing once it is there)
+    auto entry = [&](int i, uint32_t& row) -> uint32_t {
+        if (X) {
+            uint32_t ex;
+            line_wait(band_lines + band_at(i), x_epoch(a, l), row, ex, a.err);
+            return abs_key(__uint_as_float(ex));
+        }
+        row = __ldcg(&band_row_g[i]);
+        return abs_key(__ldcg(&band_exact_g[i]));
+    };
+    auto keyf = [&](int i) -> uint32_t {
+        uint32_t row;
+        return staged ? keys[i] : entry(i, row);
+    };
+    block_kth_largest_keys<FW_CONSUMERS, FW_BAR_CONS>(keyf, n_band_tot, need, ssm, tau_key, cnt_gt, need_eq);
+    // ties at the threshold: the need_eq lowest rows win
+    const uint32_t tau = tau_key;
+    auto rowf = [&](int i) -> uint32_t {
+        uint32_t row = 0u;
+        const uint32_t key = staged ? keys[i] : entry(i, row);
+        if (key != tau) return 0u;
+        return ~(staged ? rows[i] : row);
+    };
+    uint32_t cut_key;
+    int c2, n2;
+    block_kth_largest_keys<FW_CONSUMERS, FW_BAR_CONS>(rowf, n_band_tot, need_eq, ssm, cut_key, c2, n2);
+    row_cut = ~cut_key;
 }
 
 // ---- 3. final pick among all band rows, identically in every CTA ---------------------------------
@@ -1125,7 +1365,17 @@ __device__ __noinline__ void phase_pick(int l) {
     // Small bands (the usual case): every CTA ranks its own band rows against all band
     // entries by counting; large bands fall back to a radix select of the threshold.
     const bool by_rank = !take_all && need > 0 && n_band_tot <= FW_RANK_CAP;
-    int* win_s = reinterpret_cast<int*>(ring + FW_PICK_CAP * 8);
+    // A band of up to FW_RANK_CAP entries (the usual case) is staged at the end of the ring, behind the slots
+    // that were filled before the pick; a larger one needs the ring from its start: the rows staged early
+    // are then given up (their copies are waited for first) and the gather fetches them again.
+    uint32_t* keys = reinterpret_cast<uint32_t*>(by_rank ? ring + gm.off_pick : ring);
+    uint32_t* rows = keys + (by_rank ? FW_RANK_CAP : FW_PICK_CAP);
+    int* win_s = by_rank ? reinterpret_cast<int*>(rows + FW_RANK_CAP) : reinterpret_cast<int*>(ring + FW_PICK_CAP * 8);
+    if (!take_all && need > 0 && !by_rank) {
+        if (!mbar_wait(sm.ebar(1), (uint32_t)l & 1u)) s_ctl[SC_FAILED] = 1;
+        bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+        if (tid == 0) s_ctl[SC_N_EARLY] = 0;
+    }
     int* ired = reinterpret_cast<int*>(red);
     int* scal = ired + 1240;     // my first pool item, my share
     int* prefix = ired + 1280;   // [NC + 1] pool segments (start of every CTA's rows in the pool)
@@ -1207,11 +1457,10 @@ __device__ __noinline__ void phase_pick(int l) {
     }
     if (!take_all && need > 0) {
         // stage (|v| key, row) of every band entry in the idle ring
-        uint32_t* keys = reinterpret_cast<uint32_t*>(ring);
-        uint32_t* rows = keys + FW_PICK_CAP;
         const bool staged = n_band_tot <= FW_PICK_CAP;
         if (staged) {
             if (tid < STAGERS)
+#pragma unroll 1
                 for (int i = tid; i < n_band_tot; i += STAGERS) {
                     if (X) {
                         uint32_t row, ex;
@@ -1226,6 +1475,7 @@ __device__ __noinline__ void phase_pick(int l) {
             bar_sync(FW_BAR_CONS, FW_CONSUMERS);
         }
         if (by_rank) {
+#pragma unroll 1
             for (int i = warp; i < n_band_mine; i += FW_NWARPS) {
                 const uint32_t key = abs_key(band_ex[i]);
                 const uint32_t row = (uint32_t)(row_of_slot(cx, band_list[i]) + row_add);
@@ -1239,40 +1489,14 @@ __device__ __noinline__ void phase_pick(int l) {
             }
             bar_sync(FW_BAR_CONS, FW_CONSUMERS);
         } else {
-            SelectSmem<FW_CONSUMERS>& ssm = *reinterpret_cast<SelectSmem<FW_CONSUMERS>*>(ring + FW_PICK_CAP * 8);
-            int cnt_gt, need_eq;
-            // (a band too large to stage: every read waits for its line again, which costs nothing once it is there)
-            auto entry = [&](int i, uint32_t& row) -> uint32_t {
-                if (X) {
-                    uint32_t ex;
-                    line_wait(band_lines + band_at(i), x_epoch(a, l), row, ex, a.err);
-                    return abs_key(__uint_as_float(ex));
-                }
-                row = __ldcg(&band_row_g[i]);
-                return abs_key(__ldcg(&band_exact_g[i]));
-            };
-            auto keyf = [&](int i) -> uint32_t {
-                uint32_t row;
-                return staged ? keys[i] : entry(i, row);
-            };
-            block_kth_largest_keys<FW_CONSUMERS, FW_BAR_CONS>(keyf, n_band_tot, need, ssm, tau_key, cnt_gt, need_eq);
-            // ties at the threshold: the need_eq lowest rows win
-            auto rowf = [&](int i) -> uint32_t {
-                uint32_t row = 0u;
-                const uint32_t key = staged ? keys[i] : entry(i, row);
-                if (key != tau_key) return 0u;
-                return ~(staged ? rows[i] : row);
-            };
-            uint32_t cut_key;
-            int c2, n2;
-            block_kth_largest_keys<FW_CONSUMERS, FW_BAR_CONS>(rowf, n_band_tot, need_eq, ssm, cut_key, c2, n2);
-            row_cut = ~cut_key;
+            pick_big_band<X>(l, n_band_tot, need, seg_pre, tau_key, row_cut);
             bar_sync(FW_BAR_CONS, FW_CONSUMERS);
         }
     }
     // winners among this CTA's band rows, in slot order, after the CTA's own certainly-in rows
     if (warp == 0) {
         int cnt = 0;
+#pragma unroll 1
         for (int i0 = 0; i0 < n_band_mine; i0 += 32) {
             const int i = i0 + lane;
             bool win = false;
@@ -1297,6 +1521,7 @@ __device__ __noinline__ void phase_pick(int l) {
         const int NC = (int)gridDim.x;
         const int n_win = s_ctl[SC_N_G2];  // own rows and winners so far
         const int my_first = scal[0], n_pool_mine = scal[1];
+#pragma unroll 1
         for (int i = tid; i < n_pool_mine; i += FW_CONSUMERS) {
             const int j = my_first + i;
             int sa = 0, sb = NC;  // prefix[sa] <= j < prefix[sb]
@@ -1325,6 +1550,54 @@ __device__ __noinline__ void phase_pick(int l) {
     bar_sync(FW_BAR_CONS, FW_CONSUMERS);
 }
 
+// The teams' accumulators, staged in the ring (one region per team, 64-float chunks at a stride of 65), are
+// summed in team order into this CTA's partial out[H] (first: stored; later chunks: added).
+__device__ __forceinline__ void merge_partials(bool first) {
+    extern __shared__ __align__(128) uint8_t smem[];  // the kernel's dynamic shared memory
+    const Smem sm{smem};
+    const FusedGeom& gm = sm.cx().gm;
+    const int tid = threadIdx.x, hidden = gm.nsb * 256, P = gm.P;
+    const float* out_r = reinterpret_cast<const float*>(sm.ring());
+    const int region = gm.G * 65;
+    float* dst = sm.cx().a.partials + (size_t)blockIdx.x * hidden;
+    for (int i = tid; i < hidden; i += FW_CONSUMERS) {
+        const int o = (i >> 6) * 65 + (i & 63);
+        float v = out_r[o];
+        for (int p = 1; p < P; ++p) v += out_r[p * region + o];
+        dst[i] = first ? v : dst[i] + v;
+    }
+    // the merge used the ring with plain loads and stores; order them before the next TMA writes
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    bar_sync(FW_BAR_CONS, FW_CONSUMERS);  // the staging area is free again
+}
+
+// The gather's rare path, kept out of line: a CTA with more rows than the ring stages at once takes the rest
+// chunk by chunk (up rows staged, dotted, down rows into the same slots, added), each chunk merged into the partial.
+__device__ __noinline__ void gather_more_chunks(int l, int n0, int n_g2) {
+    extern __shared__ __align__(128) uint8_t smem[];  // the kernel's dynamic shared memory
+    const Smem sm{smem};
+    const FusedGeom& gm = sm.cx().gm;
+    int* s_ctl = sm.ctl();
+    const FusedLayer ly = layer_of(sm.cx().a, l);
+    uint32_t gather_uses = (uint32_t)s_ctl[SC_GATHER_USES];
+    bool failed = false;
+#pragma unroll 1
+    for (int base = n0; base < n_g2; base += gm.D2) {
+        GatherArgs ga;
+        ga.up = ly.up; ga.down = ly.down; ga.rows = sm.g_rows(); ga.scores = sm.g_scores(); ga.ring = sm.ring();
+        ga.psum = sm.psum(); ga.act = sm.psum() + FW_MAX_GROWS * gm.Wt; ga.bar = sm.gbar(); ga.ubar = sm.gbar() + 1;
+        ga.xa_s = sm.xa(); ga.xb_s = sm.xb(); ga.blk_s = sm.blk();
+        ga.nsb = gm.nsb; ga.G = gm.G; ga.TS = gm.TS; ga.P = gm.P; ga.Wt = gm.Wt; ga.row_bytes = gm.row_bytes;
+        gather_stage(ga, base, min(gm.D2, n_g2 - base), gather_uses & 1u, failed);  // leaves the accumulators staged in the ring
+        gather_uses += 1;
+        bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+        merge_partials(false);
+    }
+    bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+    if (threadIdx.x == 0) s_ctl[SC_GATHER_USES] = (int)gather_uses;
+    if (failed) s_ctl[SC_FAILED] = 1;
+}
+
 // ---- gather: own certainly-in rows (up to the fair share), band winners, pool share; merge ------
 __device__ __noinline__ void phase_gather(int l) {
     extern __shared__ __align__(128) uint8_t smem[];  // the kernel's dynamic shared memory
@@ -1333,41 +1606,123 @@ __device__ __noinline__ void phase_gather(int l) {
     const FusedGeom& gm = cx.gm;
     const FusedArgs& a = cx.a;
     const int tid = threadIdx.x;
-    const int hidden = gm.nsb * 256, P = gm.P;
+    const int P = gm.P;
     int* s_ctl = sm.ctl();
     const int n_g2 = s_ctl[SC_N_G2];
-    uint32_t gather_uses = (uint32_t)s_ctl[SC_GATHER_USES];
     bool failed = false;
     const FusedLayer ly = layer_of(a, l);
-    // A chunk is what the ring can stage (D2 rows, more than a CTA's usual share); each chunk ends in the
-    // teams' accumulators, summed in team order into this CTA's partial out[H].
-    for (int base = 0; base == 0 || base < n_g2; base += gm.D2) {
-        GatherArgs ga;
-        ga.up = ly.up; ga.down = ly.down; ga.rows = sm.g_rows(); ga.scores = sm.g_scores(); ga.ring = sm.ring();
-        ga.psum = sm.psum(); ga.act = sm.psum() + FW_MAX_GROWS * gm.Wt; ga.bar = sm.gbar(); ga.ubar = sm.gbar() + 1;
-        ga.xa_s = sm.xa(); ga.xb_s = sm.xb(); ga.blk_s = sm.blk();
-        ga.nsb = gm.nsb; ga.G = gm.G; ga.TS = gm.TS; ga.P = P; ga.Wt = gm.Wt; ga.row_bytes = gm.row_bytes;
-        // leaves the accumulators staged in the ring
-        gather_stage(ga, base, max(0, min(gm.D2, n_g2 - base)), gather_uses & 1u, failed);
-        gather_uses += 1;
-        if (base == 0 && a.pf_late) prefetch_next_gate(sm, l);
-        bar_sync(FW_BAR_CONS, FW_CONSUMERS);
-        if (base == 0) FW_STAMP(8);
-        // one region per team in the ring, 64-float chunks at a stride of 65
-        const float* out_r = reinterpret_cast<const float*>(sm.ring());
-        const int region = gm.G * 65;
-        float* dst = a.partials + (size_t)blockIdx.x * hidden;
-        for (int i = tid; i < hidden; i += FW_CONSUMERS) {
-            const int o = (i >> 6) * 65 + (i & 63);
-            float v = out_r[o];
-            for (int p = 1; p < P; ++p) v += out_r[p * region + o];
-            dst[i] = base == 0 ? v : dst[i] + v;
+    // First chunk: rows [0, n_early) were staged before the pick (up dots done, activations in place, down rows
+    // on their way into the same slots); rows [n_early, n0) are what the pick added (band winners, pool share).
+    // Their up rows go to slots n_early.. and, where the ring has room, their down rows to slots n0.. at once;
+    // while those copies travel the early rows are added into the accumulators.
+    const int n0 = min(n_g2, gm.D2);
+    {
+        const int lane = tid & 31;
+        const int team = tid / gm.TS, c = tid % gm.TS, wt = c >> 5;
+        const bool in_team = team < P;
+        const bool active = in_team && c < gm.G;
+        const int s = c >> 2, g = c & 3, nblk = gm.nsb * 8, rb = gm.row_bytes;
+        const uint32_t par = (uint32_t)l & 1u;
+        const int n_early = min(s_ctl[SC_N_EARLY], n0);
+        const int n_x = n0 - n_early;
+        const bool both = n0 + n_x <= gm.D2;
+        const int* rows = sm.g_rows();
+        const float* scores = sm.g_scores();
+        uint8_t* ring = sm.ring();
+        float* psum = sm.psum();
+        float* act_s = psum + FW_MAX_GROWS * gm.Wt;
+        if (tid == 0) {
+            mbar_expect_tx(sm.ebar(2), (uint32_t)n_x * (uint32_t)rb);
+            mbar_expect_tx(sm.ebar(3), (uint32_t)n_x * (uint32_t)rb);
         }
-        // the merge used the ring with plain loads and stores; order them before the next TMA writes
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        bar_sync(FW_BAR_CONS, FW_CONSUMERS);  // the staging area is free again
+        bar_sync(FW_BAR_CONS, FW_CONSUMERS);  // the expectations are armed before any copy can complete
+#pragma unroll 1
+        for (int i = tid; i < n_x; i += FW_CONSUMERS) {
+            const size_t src = (size_t)(uint32_t)rows[n_early + i] * rb;
+            tma_bulk_g2s(ring + (size_t)(n_early + i) * rb, ly.up + src, (uint32_t)rb, sm.ebar(2));
+            if (both) tma_bulk_g2s(ring + (size_t)(n0 + i) * rb, ly.down + src, (uint32_t)rb, sm.ebar(3));
+        }
+        float acc_lo[32], acc_hi[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc_lo[j] = acc_hi[j] = 0.0f;
+        float corr_lo = 0.0f, corr_hi = 0.0f;
+        // the early rows' down rows
+        if (!failed && !mbar_wait(sm.ebar(1), par)) failed = true;
+        if (active) {
+#pragma unroll 1
+            for (int i = team; i < n_early; i += P) {
+                const float act = act_s[i];
+                if (act == 0.0f) continue;
+                axpy_cell(ring + (size_t)i * rb + s * 144, g, act, acc_lo, acc_hi, corr_lo, corr_hi);
+            }
+        }
+        // the added rows: up dots against the planes in shared memory (the accumulators hold the registers)
+        if (!failed && !mbar_wait(sm.ebar(2), par)) failed = true;
+        if (in_team) {
+            const int cl = active ? c : 0;
+#pragma unroll 1
+            for (int i = team; i < n0; i += P) {
+                if (i < n_early) continue;
+                float val = 0.0f;
+                if (active) {
+                    const uint8_t* cell = ring + (size_t)i * rb + s * 144;
+                    const uint4 hd = *reinterpret_cast<const uint4*>(cell);
+                    const uint4 q0 = *reinterpret_cast<const uint4*>(cell + 16 + g * 32);
+                    const uint4 q1 = *reinterpret_cast<const uint4*>(cell + 32 + g * 32);
+                    val = cell_value_smem(hd, q0, q1, g, sm.xa(), sm.xb(), sm.blk(), nblk, (cl >> 2) * 8 + 2 * (cl & 3),
+                                          gm.G, cl);
+                }
+                for (int o = 16; o > 0; o >>= 1) val += __shfl_xor_sync(0xffffffffu, val, o);
+                if (lane == 0) psum[i * gm.Wt + wt] = val;
+                if (!both) {
+                    bar_sync(1 + team, gm.TS);  // every thread of the team is done with the up row
+                    if (c == 0) {
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // plain reads before the TMA write
+                        tma_bulk_g2s(ring + (size_t)i * rb, ly.down + (size_t)(uint32_t)rows[i] * rb, (uint32_t)rb, sm.ebar(3));
+                    }
+                }
+            }
+        }
+        bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+#pragma unroll 1
+        for (int i = n_early + tid; i < n0; i += FW_CONSUMERS) {
+            float upv = 0.0f;
+#pragma unroll 1
+            for (int w = 0; w < gm.Wt; ++w) upv += psum[i * gm.Wt + w];
+            const float gs = scores[i];
+            const float sig = __fdiv_rn(1.0f, 1.0f + expf(-gs));
+            const float act = (gs * sig) * upv;
+            act_s[i] = fabsf(act) > FW_NOISE_FLOOR ? act : 0.0f;
+        }
+        bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+        if (!failed && !mbar_wait(sm.ebar(3), par)) failed = true;
+        if (active) {
+#pragma unroll 1
+            for (int i = team; i < n0; i += P) {
+                if (i < n_early) continue;
+                const float act = act_s[i];
+                if (act == 0.0f) continue;
+                const int slot = both ? n0 + (i - n_early) : i;
+                axpy_cell(ring + (size_t)slot * rb + s * 144, g, act, acc_lo, acc_hi, corr_lo, corr_hi);
+            }
+        }
+        // every team has finished reading the staged rows: the ring now takes the accumulators
+        bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+        if (active) {
+            float* o_lo = reinterpret_cast<float*>(ring) + team * (gm.G * 65) + c * 65;
+            float* o_hi = o_lo + 32;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                o_lo[j] = acc_lo[j] - corr_lo;
+                o_hi[j] = acc_hi[j] - corr_hi;
+            }
+        }
     }
-    if (tid == 0) s_ctl[SC_GATHER_USES] = (int)gather_uses;
+    if (a.pf_late) prefetch_next_gate(sm, l);
+    bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+    FW_STAMP(8);
+    merge_partials(true);
+    if (n0 < n_g2) gather_more_chunks(l, n0, n_g2);
     if (failed) s_ctl[SC_FAILED] = 1;
 
     // optional: selected rows of the last layer (unordered)
@@ -1376,6 +1731,7 @@ __device__ __noinline__ void phase_gather(int l) {
         bar_sync(FW_BAR_CONS, FW_CONSUMERS);
         const int base = s_ctl[SC_HIT_BASE];
         const int* g2_rows = sm.g_rows();
+#pragma unroll 1
         for (int i = tid; i < n_g2; i += FW_CONSUMERS)
             if (base + i < a.top_k) a.hit_out[base + i] = (uint32_t)g2_rows[i];  // (a sharded walk: this rank's own row numbers)
     }
@@ -1383,6 +1739,7 @@ __device__ __noinline__ void phase_gather(int l) {
     if (tid == 0 && l + 1 < a.n_layers) {
         const FusedLayer nx = a.layers[l + 1];
         const uint32_t it0 = (uint32_t)(l + 1) * (uint32_t)cx.my_count;
+#pragma unroll 1
         for (int k = 0; k < cx.n_ahead; ++k) issue_tile(sm, nx, k, it0 + k);
     }
     // housekeeping for the layer after next (nobody reads these before two more grid barriers)
@@ -1471,7 +1828,9 @@ __device__ __forceinline__ void fused_setup(const FusedGeom& gm_in, const FusedA
     const uint32_t* asrc = reinterpret_cast<const uint32_t*>(&a_in);
     uint32_t* gdst = reinterpret_cast<uint32_t*>(&cxw.gm);
     uint32_t* adst = reinterpret_cast<uint32_t*>(&cxw.a);
+#pragma unroll 1
     for (int i = tid; i < (int)(sizeof(FusedGeom) / 4); i += FW_THREADS) gdst[i] = gsrc[i];
+#pragma unroll 1
     for (int i = tid; i < (int)(sizeof(FusedArgs) / 4); i += FW_THREADS) adst[i] = asrc[i];
     if (tid == 0) {
         const int R = gm_in.R;
@@ -1484,18 +1843,21 @@ __device__ __forceinline__ void fused_setup(const FusedGeom& gm_in, const FusedA
         cxw.stamp_layer = a_in.n_layers >= 2 ? a_in.n_layers - 2 : 0;
         int* s_ctl = sm.ctl();
         for (int i = 0; i < 16; ++i) s_ctl[i] = 0;
+#pragma unroll 1
         for (int i = 0; i < gm_in.S; ++i) {
             mbar_init(&sm.full()[i], 1);
             sm.released()[i] = 0;
         }
         mbar_init(sm.gbar(), 1);
         mbar_init(sm.gbar() + 1, 1);
+        for (int i = 0; i < 5; ++i) mbar_init(sm.ebar(i), 1);
         fence_mbar_init();
     }
     __syncthreads();
     if (tid == 0) {
         const Ctx& cx = sm.cx();
         const FusedLayer l0 = layer_of(cx.a, 0);
+#pragma unroll 1
         for (int k = 0; k < cx.n_ahead; ++k) issue_tile(sm, l0, k, (uint32_t)k);
     }
 }
@@ -1523,7 +1885,11 @@ walk_fused_q4k_kernel(const __grid_constant__ FusedGeom gm_in, const __grid_cons
         FW_STAMP(3);
         phase_select<false>(l);
         FW_STAMP(5);
-        grid_sync(&a.ctrs[CTR_SYNC], epoch, a.err, failed, &s_ctl[SC_FAILED]);  // B: band and pool rows published
+        // B: band and pool rows published.  Between arriving and waiting, the up dots of the rows staged early.
+        epoch += 1;
+        grid_arrive(&a.ctrs[CTR_SYNC], failed);
+        phase_early(l);
+        grid_wait(&a.ctrs[CTR_SYNC], epoch * gridDim.x, a.err, failed, &s_ctl[SC_FAILED]);
         FW_STAMP(6);
         phase_pick<false>(l);
         FW_STAMP(7);
@@ -1573,6 +1939,7 @@ walk_fused_q4k_sharded_kernel(const __grid_constant__ FusedGeom gm_in, const __g
         FW_STAMP(3);
         phase_select<true>(l);
         FW_STAMP(5);
+        phase_early(l);
         FW_STAMP(6);
         phase_pick<true>(l);
         FW_STAMP(7);
