@@ -283,6 +283,7 @@ struct StagedGeom {
     static constexpr int SCB = FMT == LQ_FMT_NVFP4 ? 16 : (FMT == LQ_FMT_MXFP4 ? 8 : 0);  // scale bytes
     static constexpr int ROWB = CHB + (FMT == LQ_FMT_Q8_0 ? 32 : 16);                    // padded: shifts the banks per row
     static constexpr int WARP_BYTES = 32 * ROWB + 32 * 32;
+    static constexpr int NBUF = FMT == LQ_FMT_Q8_0 ? 2 : 3;  // chunk buffers per warp (two CTAs of four warps fit an SM)
 };
 
 // Two IEEE round-to-nearest f32 multiplies in one instruction (sm_100 packed f32x2): {a0 * b0, a1 * b1}.
@@ -301,9 +302,12 @@ __device__ __forceinline__ void fmul2_rn(float a0, float a1, float b0, float b1,
 // sits in the lanes of the warp (lane i holds the value of code i & 15, `lut`): a weight is decoded by one
 // shuffle whose source lane is the word shifted down to the nibble (a shuffle takes its source lane modulo
 // 32, and lanes 16..31 repeat the table), so every lane of the warp must call this together.
-template <int FMT>
+// CHAIN: the running sum takes the previous block's products (`prev`) in between, in the reference's order, so the
+// dependent adds and the independent products alternate in program order.
+template <int FMT, bool CHAIN = false>
 __device__ __forceinline__ void block_products(const uint8_t* mine, const uint8_t* sc, float ts, int b, const float* xc,
-                                               float lut, float (&p)[32]) {
+                                               float lut, float (&p)[32], const float* prev = nullptr, float* acc_io = nullptr) {
+    float acc = CHAIN ? *acc_io : 0.0f;
     float xe[32];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -316,8 +320,14 @@ __device__ __forceinline__ void block_products(const uint8_t* mine, const uint8_
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const uint32_t w = q[1 + j];
-            p[2 * j] = __fmul_rn(__fmul_rn((float)(int)(int8_t)(w & 0xff), d), xe[2 * j]);
-            p[2 * j + 1] = __fmul_rn(__fmul_rn((float)(int)(int8_t)(w >> 8), d), xe[2 * j + 1]);
+            const float n0 = __fmul_rn(__fmul_rn((float)(int)(int8_t)(w & 0xff), d), xe[2 * j]);
+            const float n1 = __fmul_rn(__fmul_rn((float)(int)(int8_t)(w >> 8), d), xe[2 * j + 1]);
+            if (CHAIN) {
+                acc = __fadd_rn(acc, prev[2 * j]);
+                acc = __fadd_rn(acc, prev[2 * j + 1]);
+            }
+            p[2 * j] = n0;
+            p[2 * j + 1] = n1;
         }
     } else {
         const uint4 w = *reinterpret_cast<const uint4*>(mine + b * 16);
@@ -334,11 +344,18 @@ __device__ __forceinline__ void block_products(const uint8_t* mine, const uint8_
             const float v0 = __shfl_sync(0xffffffffu, lut, (int)(ww[e >> 3] >> (4 * (e & 7))));
             const float v1 = __shfl_sync(0xffffffffu, lut, (int)(ww[e >> 3] >> (4 * (e & 7) + 4)));
             const float s = e < 16 ? s0 : s1;
-            float w0, w1;
+            float w0, w1, n0, n1;
             fmul2_rn(v0, v1, s, s, w0, w1);  // (multiplication commutes: the reference's scale * value or value * scale)
-            fmul2_rn(w0, w1, xe[e], xe[e + 1], p[e], p[e + 1]);
+            fmul2_rn(w0, w1, xe[e], xe[e + 1], n0, n1);
+            if (CHAIN) {
+                acc = __fadd_rn(acc, prev[e]);
+                acc = __fadd_rn(acc, prev[e + 1]);
+            }
+            p[e] = n0;
+            p[e + 1] = n1;
         }
     }
+    if (CHAIN) *acc_io = acc;
 }
 
 __device__ __forceinline__ void cp_async16_f(void* smem_dst, const void* gsrc) {
@@ -355,7 +372,7 @@ __global__ void __launch_bounds__(128) scan_exact_staged_kernel(FmtMat m, const 
     extern __shared__ __align__(16) uint8_t smem_raw[];
     float* xs = reinterpret_cast<float*>(smem_raw);  // [cols]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    uint8_t* wbase = smem_raw + (size_t)m.cols * 4 + (size_t)warp * 2 * SG::WARP_BYTES;  // two buffers per warp
+    uint8_t* wbase = smem_raw + (size_t)m.cols * 4 + (size_t)warp * SG::NBUF * SG::WARP_BYTES;
     for (int i = threadIdx.x; i < m.cols; i += blockDim.x) xs[i] = xn[i];
     __syncthreads();
     const int row0 = (blockIdx.x * 4 + warp) * 32;
@@ -365,15 +382,15 @@ __global__ void __launch_bounds__(128) scan_exact_staged_kernel(FmtMat m, const 
     const size_t data_stride = (size_t)n_chunks * SG::CHB;
     const size_t sc_stride = (size_t)n_chunks * SG::SCB;
     constexpr int PIECES = SG::CHB / 16;  // 16-byte pieces per row and chunk
-    // coalesced asynchronous copy of chunk c of this warp's 32 rows into buffer (c & 1)
+    // coalesced asynchronous copy of chunk c of this warp's 32 rows into buffer (c mod NBUF); past the end: an empty group
     auto stage = [&](int c) {
-        uint8_t* wbuf = wbase + (c & 1) * SG::WARP_BYTES;
-        for (int p = lane; p < 32 * PIECES; p += 32) {
+        uint8_t* wbuf = wbase + (c % SG::NBUF) * SG::WARP_BYTES;
+        for (int p = lane; c < n_chunks && p < 32 * PIECES; p += 32) {
             const int r = p / PIECES, piece = p % PIECES;
             const int rr = min(row0 + r, m.rows - 1);
             cp_async16_f(wbuf + r * SG::ROWB + piece * 16, m.data + (size_t)rr * data_stride + (size_t)c * SG::CHB + piece * 16);
         }
-        if (SG::SCB) {
+        if (SG::SCB && c < n_chunks) {
             const int rr = min(row0 + lane, m.rows - 1);
             uint8_t* sdst = wbuf + 32 * SG::ROWB + lane * 32;
             const uint8_t* ssrc = m.scales + (size_t)rr * sc_stride + (size_t)c * SG::SCB;
@@ -384,32 +401,44 @@ __global__ void __launch_bounds__(128) scan_exact_staged_kernel(FmtMat m, const 
     };
     float acc = 0.0f;
     const float lut = fp4_lut_lane(lane);
-    stage(0);
+    // NBUF - 1 chunks are in flight while one is summed.  The products of a block are formed while the running sum
+    // takes the previous block's (across chunk borders too), so the chain of dependent adds never waits for them.
+#pragma unroll
+    for (int c = 0; c < SG::NBUF; ++c) stage(c);
+    if (SG::NBUF == 3) asm volatile("cp.async.wait_group 2;" ::: "memory");
+    else asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncwarp();
+    float p[32], pn[32];
+    block_products<FMT>(wbase + lane * SG::ROWB, wbase + 32 * SG::ROWB + lane * 32, m.ts, 0, xs, lut, p);
     for (int c = 0; c < n_chunks; ++c) {
-        if (c + 1 < n_chunks) {
-            stage(c + 1);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
-        __syncwarp();
-        const uint8_t* wbuf = wbase + (c & 1) * SG::WARP_BYTES;
+        const uint8_t* wbuf = wbase + (c % SG::NBUF) * SG::WARP_BYTES;
         const uint8_t* mine = wbuf + lane * SG::ROWB;
         const uint8_t* sc = wbuf + 32 * SG::ROWB + lane * 32;
         const float* xc = xs + c * 256;
-        // products of block b+1 are independent of the running sum: they fill the issue slots that
-        // the chain of dependent adds of block b leaves empty
-        float p[32], pn[32];
-        block_products<FMT>(mine, sc, m.ts, 0, xc, lut, p);
-        for (int b = 0; b < 8; ++b) {
-            if (b + 1 < 8) block_products<FMT>(mine, sc, m.ts, b + 1, xc, lut, pn);
-#pragma unroll
-            for (int e = 0; e < 32; ++e) acc = __fadd_rn(acc, p[e]);
+#pragma unroll 1
+        for (int b = 1; b < 8; ++b) {
+            block_products<FMT, true>(mine, sc, m.ts, b, xc, lut, pn, p, &acc);
 #pragma unroll
             for (int e = 0; e < 32; ++e) p[e] = pn[e];
         }
-        __syncwarp();  // every lane is done with this buffer before chunk c+2 is copied into it
+        // this chunk's buffer is free (its last block sits in p): chunk c + NBUF goes into it
+        __syncwarp();
+        stage(c + SG::NBUF);
+        if (c + 1 < n_chunks) {
+            // chunk c + 1 has landed (the later ones may be in flight)
+            if (SG::NBUF == 3) asm volatile("cp.async.wait_group 2;" ::: "memory");
+            else asm volatile("cp.async.wait_group 1;" ::: "memory");
+            __syncwarp();
+            const uint8_t* nbuf = wbase + ((c + 1) % SG::NBUF) * SG::WARP_BYTES;
+            block_products<FMT, true>(nbuf + lane * SG::ROWB, nbuf + 32 * SG::ROWB + lane * 32, m.ts, 0, xc + 256, lut, pn, p, &acc);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) p[e] = pn[e];
+        } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) acc = __fadd_rn(acc, p[e]);
+        }
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     if (row < m.rows) {
         scores[row] = acc;
         if (acc != acc) set_err(err, DEV_ERR_NAN_SCORE);
@@ -651,8 +680,8 @@ cudaError_t launch_scan_exact_fmt(const FmtMat& m, const float* xn, float* score
         const int sgrid = (m.rows + 127) / 128;
 #define SCALL(F)                                                                                                   \
     {                                                                                                              \
-        const size_t sm = (size_t)m.cols * 4 + 8 * (size_t)StagedGeom<F>::WARP_BYTES;                              \
-        cudaError_t e = set_max_dyn_smem((const void*)scan_exact_staged_kernel<F>, 128 * 1024);                    \
+        const size_t sm = (size_t)m.cols * 4 + 4 * (size_t)StagedGeom<F>::NBUF * StagedGeom<F>::WARP_BYTES;                              \
+        cudaError_t e = set_max_dyn_smem((const void*)scan_exact_staged_kernel<F>, 200 * 1024);                    \
         if (e != cudaSuccess) return e;                                                                            \
         scan_exact_staged_kernel<F><<<sgrid, 128, sm, st>>>(m, xn, scores, err);                                   \
     }
