@@ -19,7 +19,7 @@
 using namespace lq;
 
 namespace lq {
-cudaError_t launch_final_pick(TokenWs ws, int* err, cudaStream_t st);
+cudaError_t launch_final_pick(TokenWs ws, int* err, cudaStream_t st, int batch = 1, size_t ws_stride = 0);
 cudaError_t launch_topk_abs_sorted(const float* scores, int n, int top_k, TokenWs ws, uint32_t* idx_out,
                                    float* val_out, int* count_out, unsigned long long* sort_buf, int* err,
                                    cudaStream_t st);
@@ -1444,6 +1444,68 @@ int lq_moe_walk_ffn(lq_ctx* ctx, const lq_matrix* gates, const lq_matrix* ups, c
     CK(cudaMemcpyAsync(dl, logits, batch * n_experts * 4, cudaMemcpyHostToDevice, ctx->stream));
     CK(cudaMemcpyAsync(dx, x, batch * H * 4, cudaMemcpyHostToDevice, ctx->stream));
     CK(cudaMemsetAsync(dout, 0, batch * H * 4, ctx->stream));
+    // Experts in one block format and one shape (what a mixture-of-experts layer holds): every (token, expert)
+    // pair is walked by the same few launches, pair y reading its expert's matrices through a device table, and
+    // nothing comes back to the host between routing and the result.  LARQL_B200_MOE_GROUPED=0 keeps the
+    // per-pair walks below (also the route for Q4_K experts and mixed shapes).
+    static const bool grouped_on = [] { const char* e = getenv("LARQL_B200_MOE_GROUPED"); return !(e && e[0] == '0'); }();
+    bool uniform = grouped_on && ke > 0 && gates[0].fmt != LQ_FMT_Q4_K && gates[0].fmt != LQ_FMT_Q6_K;
+    for (size_t e = 0; uniform && e < n_experts; ++e) {
+        uniform = g[e].fmt == g[0].fmt && u[e].fmt == g[0].fmt && d[e].fmt == g[0].fmt && g[e].rows == g[0].rows &&
+                  u[e].rows == g[0].rows && d[e].rows == g[0].rows && u[e].cols == H && d[e].cols == H &&
+                  fmt_aligned(g[e]) && fmt_aligned(u[e]) && fmt_aligned(d[e]);
+    }
+    if (uniform && g[0].rows > 0 && H % 32 == 0 && H <= 16384) {
+        const size_t N = (size_t)g[0].rows, n_pairs = batch * ke;
+        const int kk = (int)std::min<size_t>(top_k, N);
+        const int gx = (int)std::max<size_t>(1, std::min<size_t>(8, (size_t)(2 * ctx->sm_count) / n_pairs));  // gather CTAs per pair
+        if ((rc = ensure_ws(ctx, n_pairs, H, N))) return rc;
+        // (ensure_ws may have moved nothing the pointers above use: they live in the staging buffer)
+        const size_t tb = a256(3 * n_experts * sizeof(FmtMat)), xpb = a256(n_pairs * H * 4),
+                     pb = a256(n_pairs * (size_t)gx * H * 4);
+        const size_t base = lb + 2 * rb + 2 * xb + a256(H * 4);
+        if (base + tb + xpb + pb > ctx->stage_cap) {
+            // grow the staging buffer once, before anything is enqueued into it
+            if ((rc = ensure_stage(ctx, base + tb + xpb + pb))) return rc;
+            dl = (float*)ctx->stage;
+            di = (uint32_t*)(ctx->stage + lb);
+            dw = (float*)(ctx->stage + lb + rb);
+            dx = (float*)(ctx->stage + lb + 2 * rb);
+            dout = (float*)(ctx->stage + lb + 2 * rb + xb);
+            CK(cudaMemcpyAsync(dl, logits, batch * n_experts * 4, cudaMemcpyHostToDevice, ctx->stream));
+            CK(cudaMemcpyAsync(dx, x, batch * H * 4, cudaMemcpyHostToDevice, ctx->stream));
+        }
+        FmtMat* dtab = (FmtMat*)(ctx->stage + base);
+        float* dxp = (float*)(ctx->stage + base + tb);
+        float* dpart = (float*)(ctx->stage + base + tb + xpb);
+        std::vector<FmtMat> tab(3 * n_experts);
+        for (size_t e = 0; e < n_experts; ++e) {
+            tab[e] = fmtmat_of(g[e]);
+            tab[n_experts + e] = fmtmat_of(u[e]);
+            tab[2 * n_experts + e] = fmtmat_of(d[e]);
+        }
+        CK(cudaMemcpyAsync(dtab, tab.data(), tab.size() * sizeof(FmtMat), cudaMemcpyHostToDevice, ctx->stream));
+        CK(cudaStreamSynchronize(ctx->stream));  // (the table is a local: its copy must have left before it goes away)
+        cudaStream_t st = ctx->stream;
+        const TokenWs& w0 = ctx->tok[0];
+        const size_t ws_stride = n_pairs > 1 ? (size_t)((uint8_t*)ctx->tok[1].xn - (uint8_t*)ctx->tok[0].xn) : 0;
+        CK(launch_moe_route(dl, (int)batch, (int)n_experts, (int)ke, renormalise, di, dw, st));
+        CK(launch_moe_replicate(dx, (int)batch, (int)ke, (int)H, dxp, st));
+        launch_prep(dxp, (int)n_pairs, (int)H, 0, 1e-6, w0.xn, w0.xa, w0.xb, w0.bscale, w0.bsum, w0.babs,
+                    ws_stride / sizeof(float), ctx->d_err, st);
+        CK(cudaGetLastError());
+        CK(launch_scan_exact_pairs(g[0].fmt, dtab, di, (int)n_pairs, (int)N, (int)H, w0, ws_stride, ctx->d_err, st));
+        CK(launch_select(w0.scores, (int)N, kk, w0, ctx->d_err, st, (int)n_pairs, ws_stride));
+        if ((size_t)kk < N) CK(launch_final_pick(w0, ctx->d_err, st, (int)n_pairs, ws_stride));
+        CK(launch_gather_fmt_pairs(g[0].fmt, dtab + n_experts, dtab + 2 * n_experts, di, (int)n_pairs, (int)H, w0, ws_stride,
+                                   dpart, gx, st));
+        CK(launch_moe_combine(dpart, dw, (int)batch, (int)ke, gx, (int)H, dout, st));
+        ctx->launches += 8;
+        if (expert_idx_out) CK(cudaMemcpyAsync(expert_idx_out, di, batch * ke * 4, cudaMemcpyDeviceToHost, st));
+        if (expert_w_out) CK(cudaMemcpyAsync(expert_w_out, dw, batch * ke * 4, cudaMemcpyDeviceToHost, st));
+        CK(cudaMemcpyAsync(out, dout, batch * H * 4, cudaMemcpyDeviceToHost, st));
+        return lq_synchronize(ctx);
+    }
     std::vector<uint32_t> hi(batch * ke);
     if (ke) {
         CK(launch_moe_route(dl, (int)batch, (int)n_experts, (int)ke, renormalise, di, dw, ctx->stream));

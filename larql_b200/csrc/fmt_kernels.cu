@@ -204,13 +204,15 @@ __global__ void rescore_fmt_kernel(FmtMat m, const float* __restrict__ xn, const
 // rows are the parallelism (one row per thread, the activation broadcast from shared memory, each
 // thread streaming its own row with 16-byte loads that the L1 turns into whole lines).
 template <int FMT>
-__global__ void __launch_bounds__(64) scan_exact_fmt_kernel(FmtMat m, const float* __restrict__ xn,
-                                                           float* __restrict__ scores, int* err) {
+__device__ __forceinline__ void scan_exact_fmt_body(const FmtMat& m, const float* __restrict__ xn,
+                                                    float* __restrict__ scores, int* err) {
     extern __shared__ __align__(16) float xs[];  // [cols]
     for (int i = threadIdx.x; i < m.cols; i += blockDim.x) xs[i] = xn[i];
     __syncthreads();
-    const int row = blockIdx.x * blockDim.x + threadIdx.x;
-    if (row >= m.rows) return;
+    const int row_raw = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row_raw - (int)(threadIdx.x & 31) >= m.rows) return;  // (a whole warp past the end)
+    const int row = min(row_raw, m.rows - 1);  // lanes past the end redo the last row: the FP4 table read is a shuffle
+    const float lut = fp4_lut_lane(threadIdx.x & 31);
     float acc = 0.0f;
     if (FMT == LQ_FMT_Q8_0) {
         const int nb = m.cols / 32;
@@ -247,7 +249,7 @@ __global__ void __launch_bounds__(64) scan_exact_fmt_kernel(FmtMat m, const floa
                 const float xe[8] = {xa4.x, xa4.y, xa4.z, xa4.w, xb4.x, xb4.y, xb4.z, xb4.w};
 #pragma unroll
                 for (int e = 0; e < 8; ++e)  // nibble e of the word: low nibble of a byte first
-                    acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(e2m1_to_f32((ww[j] >> (4 * e)) & 15u), scale), xe[e]));
+                    acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(__shfl_sync(0xffffffffu, lut, (int)(ww[j] >> (4 * e))), scale), xe[e]));
             }
         }
     } else {
@@ -265,12 +267,32 @@ __global__ void __launch_bounds__(64) scan_exact_fmt_kernel(FmtMat m, const floa
                 const float xe[8] = {xa4.x, xa4.y, xa4.z, xa4.w, xb4.x, xb4.y, xb4.z, xb4.w};
 #pragma unroll
                 for (int e = 0; e < 8; ++e)
-                    acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(step, e2m1_to_f32((ww[j] >> (4 * e)) & 15u)), xe[e]));
+                    acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(step, __shfl_sync(0xffffffffu, lut, (int)(ww[j] >> (4 * e)))), xe[e]));
             }
         }
     }
-    scores[row] = acc;
-    if (acc != acc) set_err(err, DEV_ERR_NAN_SCORE);
+    if (row_raw < m.rows) {
+        scores[row] = acc;
+        if (acc != acc) set_err(err, DEV_ERR_NAN_SCORE);
+    }
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(64) scan_exact_fmt_kernel(FmtMat m, const float* __restrict__ xn,
+                                                           float* __restrict__ scores, int* err) {
+    scan_exact_fmt_body<FMT>(m, xn, scores, err);
+}
+
+// The same scan for many (token, expert) pairs of a mixture-of-experts layer in one launch: pair blockIdx.y
+// scans the gate matrix of ITS expert (table[pair_expert[y]]) against its token's activation; workspaces of
+// the pairs lie a constant stride apart.
+template <int FMT>
+__global__ void __launch_bounds__(64) scan_exact_pairs_kernel(const FmtMat* __restrict__ table,
+                                                             const uint32_t* __restrict__ pair_expert, TokenWs ws0,
+                                                             size_t ws_stride, int* err) {
+    const FmtMat m = table[pair_expert[blockIdx.y]];
+    const TokenWs ws = ws_at(ws0, ws_stride * blockIdx.y);
+    scan_exact_fmt_body<FMT>(m, ws.xn, ws.scores, err);
 }
 
 // Exact-order scan, staged: the same arithmetic as scan_exact_fmt_kernel, but a warp brings the next
@@ -534,11 +556,11 @@ __device__ __forceinline__ void axpy_raw32(const uint4& w, uint32_t sc, float ts
 }
 
 template <int FMT, int BPT>
-__global__ void __launch_bounds__(FK_THREADS) gather_fmt_kernel(FmtMat up, FmtMat down, XPrep xp,
-                                                               const uint32_t* __restrict__ hit_idx,
-                                                               const float* __restrict__ hit_score,
-                                                               const int* __restrict__ n_hits_dev, int n_hits_host,
-                                                               float* __restrict__ partials) {
+__device__ __forceinline__ void gather_fmt_body(const FmtMat& up, const FmtMat& down, const XPrep& xp,
+                                                const uint32_t* __restrict__ hit_idx,
+                                                const float* __restrict__ hit_score,
+                                                const int* __restrict__ n_hits_dev, int n_hits_host,
+                                                float* __restrict__ partials) {
     __shared__ float act_s[64];
     __shared__ uint32_t row_s[64];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -646,6 +668,31 @@ __global__ void __launch_bounds__(FK_THREADS) gather_fmt_kernel(FmtMat up, FmtMa
     }
 }
 
+template <int FMT, int BPT>
+__global__ void __launch_bounds__(FK_THREADS) gather_fmt_kernel(FmtMat up, FmtMat down, XPrep xp,
+                                                               const uint32_t* __restrict__ hit_idx,
+                                                               const float* __restrict__ hit_score,
+                                                               const int* __restrict__ n_hits_dev, int n_hits_host,
+                                                               float* __restrict__ partials) {
+    gather_fmt_body<FMT, BPT>(up, down, xp, hit_idx, hit_score, n_hits_dev, n_hits_host, partials);
+}
+
+// Gather for many (token, expert) pairs in one launch: pair blockIdx.y takes its expert's up / down matrices,
+// its own hit list and activation, and writes gridDim.x partial outputs at partials[y][blockIdx.x][H].
+template <int FMT, int BPT>
+__global__ void __launch_bounds__(FK_THREADS) gather_fmt_pairs_kernel(const FmtMat* __restrict__ up_table,
+                                                                     const FmtMat* __restrict__ down_table,
+                                                                     const uint32_t* __restrict__ pair_expert,
+                                                                     TokenWs ws0, size_t ws_stride,
+                                                                     float* __restrict__ partials) {
+    const uint32_t e = pair_expert[blockIdx.y];
+    const FmtMat up = up_table[e], down = down_table[e];
+    const TokenWs ws = ws_at(ws0, ws_stride * blockIdx.y);
+    const XPrep xp{ws.xn, ws.xa, ws.xb, ws.bscale, ws.bsum, ws.babs};
+    gather_fmt_body<FMT, BPT>(up, down, xp, ws.hit_idx, ws.hit_score, &ws.sel->n_sel, 0,
+                              partials + (size_t)blockIdx.y * gridDim.x * up.cols);
+}
+
 }  // namespace
 
 #define FMT_DISPATCH(fmt, CALL)                         \
@@ -728,6 +775,44 @@ cudaError_t launch_gather_fmt(const FmtMat& up, const FmtMat& down, const XPrep&
                                                                 n_hits_host, partials);                        \
     }
     FMT_DISPATCH(up.fmt, CALL)
+#undef CALL
+    return cudaGetLastError();
+}
+
+// Pair-batched launches (mixture of experts): all matrices of one table share format and shape.
+cudaError_t launch_scan_exact_pairs(int fmt, const FmtMat* table, const uint32_t* pair_expert, int n_pairs, int rows,
+                                    int cols, TokenWs ws0, size_t ws_stride, int* err, cudaStream_t st) {
+    if (n_pairs <= 0 || rows <= 0) return cudaSuccess;
+    const dim3 grid((rows + 63) / 64, n_pairs);
+    const size_t smem = (size_t)cols * sizeof(float);
+#define CALL(F)                                                                                             \
+    {                                                                                                       \
+        cudaError_t e = set_max_dyn_smem((const void*)scan_exact_pairs_kernel<F>, 64 * 1024);              \
+        if (e != cudaSuccess) return e;                                                                     \
+        scan_exact_pairs_kernel<F><<<grid, 64, smem, st>>>(table, pair_expert, ws0, ws_stride, err);        \
+    }
+    FMT_DISPATCH(fmt, CALL)
+#undef CALL
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gather_fmt_pairs(int fmt, const FmtMat* up_table, const FmtMat* down_table,
+                                    const uint32_t* pair_expert, int n_pairs, int cols, TokenWs ws0, size_t ws_stride,
+                                    float* partials, int grid_x, cudaStream_t st) {
+    if (n_pairs <= 0) return cudaSuccess;
+    if (cols % 32 != 0 || cols > 16384) return cudaErrorInvalidValue;
+    const int bpt = (cols / 32 + FK_THREADS - 1) / FK_THREADS;
+    const dim3 grid(grid_x, n_pairs);
+#define CALL(F)                                                                                                      \
+    {                                                                                                                \
+        if (bpt <= 1)                                                                                                \
+            gather_fmt_pairs_kernel<F, 1><<<grid, FK_THREADS, 0, st>>>(up_table, down_table, pair_expert, ws0,        \
+                                                                      ws_stride, partials);                         \
+        else                                                                                                         \
+            gather_fmt_pairs_kernel<F, 2><<<grid, FK_THREADS, 0, st>>>(up_table, down_table, pair_expert, ws0,        \
+                                                                      ws_stride, partials);                         \
+    }
+    FMT_DISPATCH(fmt, CALL)
 #undef CALL
     return cudaGetLastError();
 }

@@ -97,9 +97,21 @@ cudaError_t launch_rescore_fmt(const FmtMat& m, const float* xn, const uint32_t*
 cudaError_t launch_gather_fmt(const FmtMat& up, const FmtMat& down, const XPrep& xp, const uint32_t* hit_idx,
                               const float* hit_score, const int* n_hits_dev, int n_hits_host, float* partials,
                               int grid, cudaStream_t st);
+// Pair-batched launches for a mixture-of-experts layer: pair y = (token, one of its experts) uses workspace y
+// (a constant stride apart) and the matrices of expert pair_expert[y] from a device table.
+cudaError_t launch_scan_exact_pairs(int fmt, const FmtMat* table, const uint32_t* pair_expert, int n_pairs, int rows,
+                                    int cols, TokenWs ws0, size_t ws_stride, int* err, cudaStream_t st);
+cudaError_t launch_gather_fmt_pairs(int fmt, const FmtMat* up_table, const FmtMat* down_table,
+                                    const uint32_t* pair_expert, int n_pairs, int cols, TokenWs ws0, size_t ws_stride,
+                                    float* partials, int grid_x, cudaStream_t st);
 // moe.cu: softmax over all experts, top-k by (value desc, index asc), optional renormalisation
 cudaError_t launch_moe_route(const float* logits, int n_tokens, int n_experts, int top_k, int renormalise,
                              uint32_t* idx_out, float* w_out, cudaStream_t st);
+// rows_out[p] = x[p / per_token] for p < n_tokens * per_token (every pair gets its token's activation)
+cudaError_t launch_moe_replicate(const float* x, int n_tokens, int per_token, int hidden, float* rows_out, cudaStream_t st);
+// out[t] = sum_j w[t][j] * (sum_c partials[t * per_token + j][c]), c and j ascending: fixed order
+cudaError_t launch_moe_combine(const float* partials, const float* w, int n_tokens, int per_token, int n_partials,
+                               int hidden, float* out, cudaStream_t st);
 
 // prep.cu
 void launch_prep(const float* x_in, int batch, int hidden, int apply_norm, double eps, float* xn, uint32_t* xa,
@@ -129,7 +141,8 @@ cudaError_t launch_scan_q4k_mma(const Q4kMat& m, TokenWs ws0, size_t ws_stride, 
                                 int* err, int sm_count, cudaStream_t st);
 
 // select.cu
-cudaError_t launch_select(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st);
+cudaError_t launch_select(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st, int batch = 1,
+                          size_t ws_stride = 0);
 // Band classification from the scan's coarse histogram (walk path).
 cudaError_t launch_classify(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st,
                             int batch = 1, size_t ws_stride = 0);

@@ -44,7 +44,43 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int n_tokens,
         for (int j = 0; j < k; ++j) w_out[(size_t)t * k + j] = __fdiv_rn(w_out[(size_t)t * k + j], wsum);
 }
 
+__global__ void moe_replicate_kernel(const float* __restrict__ x, int per_token, int hidden, float* __restrict__ out) {
+    const float* src = x + (size_t)(blockIdx.y / per_token) * hidden;
+    float* dst = out + (size_t)blockIdx.y * hidden;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden; i += gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+// One thread per output column of a token: the experts' outputs (each the fixed-order sum of its partial blocks)
+// weighted by the routing weights, in slot order (crates/larql-compute/src/cpu/ops/moe/forward.rs:24-140 adds the
+// selected experts' outputs, scaled by their weights, in selection order).
+__global__ void moe_combine_kernel(const float* __restrict__ partials, const float* __restrict__ w, int per_token,
+                                   int n_partials, int hidden, float* __restrict__ out) {
+    const int t = blockIdx.y, col = blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= hidden) return;
+    float acc = 0.0f;
+    for (int j = 0; j < per_token; ++j) {
+        const float* p = partials + ((size_t)(t * per_token + j) * n_partials) * hidden + col;
+        float s = 0.0f;
+        for (int c = 0; c < n_partials; ++c) s += p[(size_t)c * hidden];
+        acc = fmaf(w[t * per_token + j], s, acc);
+    }
+    out[(size_t)t * hidden + col] = acc;
+}
+
 }  // namespace
+
+cudaError_t launch_moe_replicate(const float* x, int n_tokens, int per_token, int hidden, float* rows_out, cudaStream_t st) {
+    if (n_tokens <= 0 || per_token <= 0) return cudaSuccess;
+    moe_replicate_kernel<<<dim3((hidden + 1023) / 1024, n_tokens * per_token), 256, 0, st>>>(x, per_token, hidden, rows_out);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_combine(const float* partials, const float* w, int n_tokens, int per_token, int n_partials,
+                               int hidden, float* out, cudaStream_t st) {
+    if (n_tokens <= 0) return cudaSuccess;
+    moe_combine_kernel<<<dim3((hidden + 255) / 256, n_tokens), 256, 0, st>>>(partials, w, per_token, n_partials, hidden, out);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_moe_route(const float* logits, int n_tokens, int n_experts, int top_k, int renormalise,
                              uint32_t* idx_out, float* w_out, cudaStream_t st) {

@@ -18,7 +18,9 @@ constexpr int SEL_SMEM_VALS_MAX = 40 * 1024;  // floats cached in shared memory 
 // reference scores, every row at or below tau (fewer than K rows are above tau); a
 // row below tau - 2B is beaten by the >= K rows at or above tau.
 __global__ void __launch_bounds__(SEL_T, 1)
-select_kernel(const float* __restrict__ scores, int n, int top_k, TokenWs ws, int* err, int use_smem) {
+select_kernel(const float* __restrict__ scores, int n, int top_k, TokenWs ws, int* err, int use_smem, size_t ws_stride) {
+    ws = ws_at(ws, ws_stride * blockIdx.y);  // (batched launches: workspace blockIdx.y, a constant stride apart)
+    scores = tok_off(scores, ws_stride * blockIdx.y);
     extern __shared__ __align__(16) float s_vals[];
     __shared__ SelectSmem<SEL_T> sm;
     __shared__ float s_red[SEL_T / 32];
@@ -166,9 +168,9 @@ classify_kernel(const float* __restrict__ scores_g, int n, int top_k, TokenWs ws
     (void)err;
 }
 
-__global__ void __launch_bounds__(256) final_pick_kernel(TokenWs ws, int* err) {
+__global__ void __launch_bounds__(256) final_pick_kernel(TokenWs ws, int* err, size_t ws_stride) {
     __shared__ SelectSmem<256> sm;
-    final_pick_block<256>(ws, err, sm);
+    final_pick_block<256>(ws_at(ws, ws_stride * blockIdx.y), err, sm);
 }
 
 // Sort the hit list by (|v| desc, idx asc) with a bitonic network over 64-bit keys
@@ -303,12 +305,13 @@ cudaError_t launch_topk_value_sorted(const float* scores, int n, int top_k, uint
     return cudaGetLastError();
 }
 
-cudaError_t launch_select(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st) {
+cudaError_t launch_select(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st, int batch,
+                          size_t ws_stride) {
     cudaError_t e = set_max_dyn_smem((const void*)select_kernel, SEL_SMEM_VALS_MAX * 4);
     if (e != cudaSuccess) return e;
     const int use_smem = n <= SEL_SMEM_VALS_MAX;
     const size_t smem = use_smem ? (size_t)((n + 3) / 4 * 4) * sizeof(float) : 0;
-    select_kernel<<<1, SEL_T, smem, st>>>(scores, n, top_k, ws, err, use_smem);
+    select_kernel<<<dim3(1, batch), SEL_T, smem, st>>>(scores, n, top_k, ws, err, use_smem, ws_stride);
     return cudaGetLastError();
 }
 
@@ -322,17 +325,17 @@ cudaError_t launch_classify(const float* scores, int n, int top_k, TokenWs ws, i
     return cudaGetLastError();
 }
 
-cudaError_t launch_final_pick(TokenWs ws, int* err, cudaStream_t st) {
-    final_pick_kernel<<<1, 256, 0, st>>>(ws, err);
+cudaError_t launch_final_pick(TokenWs ws, int* err, cudaStream_t st, int batch, size_t ws_stride) {
+    final_pick_kernel<<<dim3(1, batch), 256, 0, st>>>(ws, err, ws_stride);
     return cudaGetLastError();
 }
 
 cudaError_t launch_topk_abs_sorted(const float* scores, int n, int top_k, TokenWs ws, uint32_t* idx_out,
                                    float* val_out, int* count_out, unsigned long long* sort_buf, int* err,
                                    cudaStream_t st) {
-    cudaError_t e = launch_select(scores, n, top_k, ws, err, st);
+    cudaError_t e = launch_select(scores, n, top_k, ws, err, st, 1, 0);
     if (e != cudaSuccess) return e;
-    e = launch_final_pick(ws, err, st);
+    e = launch_final_pick(ws, err, st, 1, 0);
     if (e != cudaSuccess) return e;
     const int count = top_k < n ? top_k : n;
     if (count <= 0) {
