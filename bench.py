@@ -644,6 +644,21 @@ def run_ours(args, wl):
     fused = fmt == FMT_Q4_K and B == 1
     phase_us = be.fused_phase_us() if fused else None
     phase = dict(zip(PHASE_NAMES, [float(v) for v in phase_us])) if phase_us else {}
+    phase_all = None
+    if fused and args.phase_sweep:
+        # The kernel records the clock stamps of ONE CTA (of the last but one layer); which one is read from the
+        # environment at every stamped launch.
+        import torch as _t
+        rows = []
+        for cta in range(_t.cuda.get_device_properties(local).multi_processor_count):
+            os.environ["LARQL_B200_FUSED_STAMP_CTA"] = str(cta)
+            step(0)
+            be.synchronize()
+            rows.append([float(v) for v in be.fused_phase_us()][:len(PHASE_NAMES)])
+        os.environ.pop("LARQL_B200_FUSED_STAMP_CTA", None)
+        arr = np.array(rows)
+        phase_all = {n: {"min": float(arr[:, j].min()), "median": float(np.median(arr[:, j])), "max": float(arr[:, j].max())}
+                     for j, n in enumerate(PHASE_NAMES)}
     peak, peak_kind = measured_peaks()
     achieved = step_bytes / (ms_step * 1e-3) / 1e9
 
@@ -696,7 +711,7 @@ def run_ours(args, wl):
         "config": config_of(args, wl),
         "walk_gbs": walk_gbs, "walk_frac_of_measured_hbm": walk_gbs / peak,
         "algorithmic_bytes_per_token": alg_bytes,
-        "phase_us_cta0": phase,
+        "phase_us_cta0": phase, "phase_us_all_ctas": phase_all,
         "roofline": {"kernel": kernel, "bound": "hbm", "achieved": achieved, "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": (step_bytes * traffic_ratio) if (args.workload == "llama70b_q4k" and B == 1) else None,
@@ -729,6 +744,9 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU baseline work (0: skip)")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (small profiling cases)")
+    ap.add_argument("--phase-sweep", action="store_true",
+                    help="fused walk only: after the timed steps, stamp every CTA in turn (one more token per CTA) and "
+                         "print min / median / max of every phase over the CTAs as `phase_us_all_ctas`")
     args = ap.parse_args()
     wl = dict(WORKLOADS[args.workload])
     if args.layers > 0:

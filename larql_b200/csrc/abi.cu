@@ -1458,7 +1458,8 @@ int lq_moe_walk_ffn(lq_ctx* ctx, const lq_matrix* gates, const lq_matrix* ups, c
     if (uniform && g[0].rows > 0 && H % 32 == 0 && H <= 16384) {
         const size_t N = (size_t)g[0].rows, n_pairs = batch * ke;
         const int kk = (int)std::min<size_t>(top_k, N);
-        const int gx = (int)std::max<size_t>(1, std::min<size_t>(8, (size_t)(2 * ctx->sm_count) / n_pairs));  // gather CTAs per pair
+        // gather CTAs per pair: about six CTAs per SM over all pairs (what a narrow gather CTA lets an SM hold)
+        const int gx = (int)std::max<size_t>(1, std::min<size_t>(16, (size_t)(6 * ctx->sm_count) / n_pairs));
         if ((rc = ensure_ws(ctx, n_pairs, H, N))) return rc;
         // (ensure_ws may have moved nothing the pointers above use: they live in the staging buffer)
         const size_t tb = a256(3 * n_experts * sizeof(FmtMat)), xpb = a256(n_pairs * H * 4),

@@ -555,7 +555,7 @@ __device__ __forceinline__ void axpy_raw32(const uint4& w, uint32_t sc, float ts
     }
 }
 
-template <int FMT, int BPT>
+template <int FMT, int BPT, int NT = FK_THREADS>
 __device__ __forceinline__ void gather_fmt_body(const FmtMat& up, const FmtMat& down, const XPrep& xp,
                                                 const uint32_t* __restrict__ hit_idx,
                                                 const float* __restrict__ hit_score,
@@ -582,7 +582,7 @@ __device__ __forceinline__ void gather_fmt_body(const FmtMat& up, const FmtMat& 
     const int h0 = min(n_hits, (int)blockIdx.x * per), h1 = min(n_hits, h0 + per);
     for (int c0 = h0; c0 < h1; c0 += 64) {
         const int nh = min(64, h1 - c0);
-        for (int i = warp; i < nh; i += FK_THREADS / 32) {
+        for (int i = warp; i < nh; i += NT / 32) {
             const uint32_t row = hit_idx[c0 + i];
             float b;
             const float u = fast_row<FMT>(up, row, xp, 0.0f, b, lane, lut);
@@ -604,7 +604,7 @@ __device__ __forceinline__ void gather_fmt_body(const FmtMat& up, const FmtMat& 
             auto fetch = [&](int i, uint4 (&wv)[BPT], uint32_t (&sv)[BPT]) {
 #pragma unroll
                 for (int b = 0; b < BPT; ++b) {
-                    const int blk = tid + b * FK_THREADS;
+                    const int blk = tid + b * NT;
                     wv[b] = make_uint4(0u, 0u, 0u, 0u);
                     sv[b] = 0u;
                     if (i < nh && blk < nblk) load_raw32<FMT>(down, (size_t)row_s[i], blk, wv[b], sv[b]);
@@ -638,7 +638,7 @@ __device__ __forceinline__ void gather_fmt_body(const FmtMat& up, const FmtMat& 
                 const size_t row = row_s[i];
 #pragma unroll
                 for (int b = 0; b < BPT; ++b) {
-                    const int blk = tid + b * FK_THREADS;
+                    const int blk = tid + b * NT;
                     if (blk < nblk) {
                         float v[32];
                         decode_block32<FMT>(down, row, blk, v);
@@ -653,7 +653,7 @@ __device__ __forceinline__ void gather_fmt_body(const FmtMat& up, const FmtMat& 
     float* dst = partials + (size_t)blockIdx.x * H;
 #pragma unroll
     for (int b = 0; b < BPT; ++b) {
-        const int blk = tid + b * FK_THREADS;
+        const int blk = tid + b * NT;
         if (blk < nblk) {
             if (FP4) {
 #pragma unroll
@@ -679,8 +679,10 @@ __global__ void __launch_bounds__(FK_THREADS) gather_fmt_kernel(FmtMat up, FmtMa
 
 // Gather for many (token, expert) pairs in one launch: pair blockIdx.y takes its expert's up / down matrices,
 // its own hit list and activation, and writes gridDim.x partial outputs at partials[y][blockIdx.x][H].
-template <int FMT, int BPT>
-__global__ void __launch_bounds__(FK_THREADS) gather_fmt_pairs_kernel(const FmtMat* __restrict__ up_table,
+// NT: threads per CTA; narrow activations (at most 128 blocks of 32 columns) take 128, so that fewer threads idle in
+// the down rows' pass and more CTAs share an SM.
+template <int FMT, int BPT, int NT>
+__global__ void __launch_bounds__(NT) gather_fmt_pairs_kernel(const FmtMat* __restrict__ up_table,
                                                                      const FmtMat* __restrict__ down_table,
                                                                      const uint32_t* __restrict__ pair_expert,
                                                                      TokenWs ws0, size_t ws_stride,
@@ -689,8 +691,8 @@ __global__ void __launch_bounds__(FK_THREADS) gather_fmt_pairs_kernel(const FmtM
     const FmtMat up = up_table[e], down = down_table[e];
     const TokenWs ws = ws_at(ws0, ws_stride * blockIdx.y);
     const XPrep xp{ws.xn, ws.xa, ws.xb, ws.bscale, ws.bsum, ws.babs};
-    gather_fmt_body<FMT, BPT>(up, down, xp, ws.hit_idx, ws.hit_score, &ws.sel->n_sel, 0,
-                              partials + (size_t)blockIdx.y * gridDim.x * up.cols);
+    gather_fmt_body<FMT, BPT, NT>(up, down, xp, ws.hit_idx, ws.hit_score, &ws.sel->n_sel, 0,
+                                  partials + (size_t)blockIdx.y * gridDim.x * up.cols);
 }
 
 }  // namespace
@@ -801,16 +803,19 @@ cudaError_t launch_gather_fmt_pairs(int fmt, const FmtMat* up_table, const FmtMa
                                     float* partials, int grid_x, cudaStream_t st) {
     if (n_pairs <= 0) return cudaSuccess;
     if (cols % 32 != 0 || cols > 16384) return cudaErrorInvalidValue;
-    const int bpt = (cols / 32 + FK_THREADS - 1) / FK_THREADS;
+    const int nblk = cols / 32;
     const dim3 grid(grid_x, n_pairs);
-#define CALL(F)                                                                                                      \
-    {                                                                                                                \
-        if (bpt <= 1)                                                                                                \
-            gather_fmt_pairs_kernel<F, 1><<<grid, FK_THREADS, 0, st>>>(up_table, down_table, pair_expert, ws0,        \
-                                                                      ws_stride, partials);                         \
-        else                                                                                                         \
-            gather_fmt_pairs_kernel<F, 2><<<grid, FK_THREADS, 0, st>>>(up_table, down_table, pair_expert, ws0,        \
-                                                                      ws_stride, partials);                         \
+#define CALL(F)                                                                                                        \
+    {                                                                                                                  \
+        if (nblk <= 128)                                                                                               \
+            gather_fmt_pairs_kernel<F, 1, 128><<<grid, 128, 0, st>>>(up_table, down_table, pair_expert, ws0, ws_stride, \
+                                                                    partials);                                        \
+        else if (nblk <= FK_THREADS)                                                                                   \
+            gather_fmt_pairs_kernel<F, 1, FK_THREADS><<<grid, FK_THREADS, 0, st>>>(up_table, down_table, pair_expert,   \
+                                                                                  ws0, ws_stride, partials);          \
+        else                                                                                                           \
+            gather_fmt_pairs_kernel<F, 2, FK_THREADS><<<grid, FK_THREADS, 0, st>>>(up_table, down_table, pair_expert,   \
+                                                                                  ws0, ws_stride, partials);          \
     }
     FMT_DISPATCH(fmt, CALL)
 #undef CALL

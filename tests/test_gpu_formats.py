@@ -195,6 +195,33 @@ def test_moe_expert_walk_gpt_oss_shape(be):
         assert rel_l2(got[t], want) < OUT_TOL
 
 
+@pytest.mark.parametrize("fmt", [oracle.FMT_Q4_K, oracle.FMT_NVFP4, oracle.FMT_Q8_0],
+                         ids=["q4k_pair_by_pair", "nvfp4_grouped", "q8_0_grouped"])
+def test_moe_expert_walk_both_routes(be, fmt):
+    """Block-format experts of one shape take the grouped route (all pairs in the same launches, experts through a
+    device table); Q4_K experts are walked pair by pair.  Same contract, same tolerance; one token routes to
+    every expert (top_e == experts), so every table entry is read."""
+    import larql_b200
+    E, H, N, K, T = 4, 512, 768, 96, 5
+    experts = [layer(0x900 + 10 * e, N, H, fmt) for e in range(E)]
+    rng = np.random.Generator(np.random.PCG64(23))
+    logits = rng.standard_normal((T, E)).astype(np.float32)
+    xs = oracle.rms_norm(seeded_x(0x91, T, H))
+    for top_e in (2, E):
+        got, idx, w = be.moe_walk_ffn([host(e[0]) for e in experts], [host(e[1]) for e in experts],
+                                      [host(e[2]) for e in experts], logits, xs, top_e, K, True,
+                                      larql_b200.WALK_FORCE_SPARSE)
+        for t in range(T):
+            wi, ww = oracle.moe_route(logits[t], top_e, True)
+            assert idx[t].tolist() == wi.tolist()
+            assert np.allclose(w[t], ww, rtol=0, atol=1e-6)
+            want = np.zeros(H, np.float32)
+            for e, we in zip(wi, ww):
+                o, _, _ = oracle.walk_token(*experts[int(e)], xs[t], K)
+                want += np.float32(we) * o
+            assert rel_l2(got[t], want) < OUT_TOL
+
+
 # ---------------------------------------------------- device seam: multi gemv, f16 / bf16, top-k by value
 def test_gemv_multi_matches_single_gemvs(be):
     """mxfp4_gemv_multi / nvfp4_gemv_multi (backend/matmul.rs:242-286): the results of the single gemvs."""
