@@ -241,7 +241,8 @@ int batch_gather_grid(const lq_ctx* ctx, size_t nb) {
 }
 size_t partial_blocks(const lq_ctx* ctx, size_t batch) {
     const size_t chunk = std::min<size_t>(batch, 64);
-    return std::max<size_t>((size_t)ctx->gather_grid, chunk * (size_t)batch_gather_grid(ctx, chunk));
+    // (the block-format gather of one token runs fmt_gather_grid() CTAs: several per SM keep more rows in flight)
+    return std::max<size_t>((size_t)3 * ctx->gather_grid, chunk * (size_t)batch_gather_grid(ctx, chunk));
 }
 
 int ensure_ws(lq_ctx* ctx, size_t batch, size_t hidden, size_t feat) {
@@ -393,6 +394,13 @@ int resolve_matrix(lq_ctx* ctx, const lq_matrix* m, lq_matrix* out) {
     return LQ_OK;
 }
 
+// CTAs of the block-format gather of one token: its CTAs are light (80 registers, 512 bytes of shared memory),
+// and what bounds it is how many scattered rows are in flight, so an SM takes several.
+int fmt_gather_grid(const lq_ctx* ctx) {
+    static const int mult = [] { const char* e = getenv("LARQL_B200_FMT_GATHER_CTAS"); const int v = e ? atoi(e) : 2; return v < 1 ? 1 : (v > 3 ? 3 : v); }();
+    return mult * ctx->gather_grid;
+}
+
 int check_device_err(lq_ctx* ctx) {
     int h = 0;
     CK(cudaMemcpyAsync(&h, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
@@ -474,8 +482,8 @@ int enqueue_walk_token_fmt(lq_ctx* ctx, const lq_matrix& gate, const lq_matrix& 
         CK(launch_classify(w.scores, N, k, w, ctx->d_err, st));
         CK(launch_rescore_fmt(g, w.xn, w.band_idx, &w.sel->n_band, 0, w.band_exact, ctx->sm_count, st));
         CK(launch_final_pick(w, ctx->d_err, st));
-        CK(launch_gather_fmt(u, d, xp, w.hit_idx, w.hit_score, &w.sel->n_sel, k, ctx->partials, ctx->gather_grid, st));
-        CK(launch_finish(ctx->partials, ctx->gather_grid, H, residual, out, st));
+        CK(launch_gather_fmt(u, d, xp, w.hit_idx, w.hit_score, &w.sel->n_sel, k, ctx->partials, fmt_gather_grid(ctx), st));
+        CK(launch_finish(ctx->partials, fmt_gather_grid(ctx), H, residual, out, st));
         ctx->launches += 6;
         return LQ_OK;
     }
@@ -486,8 +494,8 @@ int enqueue_walk_token_fmt(lq_ctx* ctx, const lq_matrix& gate, const lq_matrix& 
         CK(launch_final_pick(w, ctx->d_err, st));  // ties at the K-th |score|: the lower rows win
         ctx->launches += 1;
     }
-    CK(launch_gather_fmt(u, d, xp, w.hit_idx, w.hit_score, &w.sel->n_sel, k, ctx->partials, ctx->gather_grid, st));
-    CK(launch_finish(ctx->partials, ctx->gather_grid, H, residual, out, st));
+    CK(launch_gather_fmt(u, d, xp, w.hit_idx, w.hit_score, &w.sel->n_sel, k, ctx->partials, fmt_gather_grid(ctx), st));
+    CK(launch_finish(ctx->partials, fmt_gather_grid(ctx), H, residual, out, st));
     ctx->launches += 3;
     return LQ_OK;
 }

@@ -234,41 +234,52 @@ __device__ __forceinline__ void scan_exact_fmt_body(const FmtMat& m, const float
                 }
             }
         }
-    } else if (FMT == LQ_FMT_MXFP4) {
+    } else {
+        // FP4 formats: 32 weights (16 bytes of codes) at a time.  A thread streams its own row, so a load touches 32
+        // different lines of the matrix; two blocks (one whole 32-byte sector) are fetched together, one pair ahead
+        // of the pair being summed.
         const int nb = m.cols / 32;
         const uint4* p = reinterpret_cast<const uint4*>(m.data + (size_t)row * nb * 16);
-        const uint8_t* sc = m.scales + (size_t)row * nb;
-        for (int b = 0; b < nb; ++b) {
-            const uint4 w = p[b];
-            const float scale = e8m0_to_f32(sc[b]);
+        const uint8_t* sc = m.scales + (size_t)row * (FMT == LQ_FMT_MXFP4 ? nb : 2 * nb);
+        auto block = [&](const uint4& w, int b) {
+            float s0, s1;
+            if (FMT == LQ_FMT_MXFP4) {
+                s0 = s1 = e8m0_to_f32(sc[b]);
+            } else {
+                s0 = __fmul_rn(m.ts, e4m3_to_f32(sc[2 * b]));
+                s1 = __fmul_rn(m.ts, e4m3_to_f32(sc[2 * b + 1]));
+            }
             const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
             const float4* xv = reinterpret_cast<const float4*>(xs + b * 32);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float4 xa4 = xv[2 * j], xb4 = xv[2 * j + 1];
                 const float xe[8] = {xa4.x, xa4.y, xa4.z, xa4.w, xb4.x, xb4.y, xb4.z, xb4.w};
+                const float s = j < 2 ? s0 : s1;
 #pragma unroll
-                for (int e = 0; e < 8; ++e)  // nibble e of the word: low nibble of a byte first
-                    acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(__shfl_sync(0xffffffffu, lut, (int)(ww[j] >> (4 * e))), scale), xe[e]));
+                for (int e = 0; e < 8; ++e) {  // nibble e of the word: low nibble of a byte first
+                    const float v = __shfl_sync(0xffffffffu, lut, (int)(ww[j] >> (4 * e)));
+                    // MXFP4 multiplies value * scale, NVFP4 scale * value: the same product either way
+                    acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(v, s), xe[e]));
+                }
             }
-        }
-    } else {
-        const int ng = m.cols / 16;
-        const uint2* p = reinterpret_cast<const uint2*>(m.data + (size_t)row * ng * 8);
-        const uint8_t* sc = m.scales + (size_t)row * ng;
-        for (int g = 0; g < ng; ++g) {
-            const uint2 w = p[g];
-            const float step = __fmul_rn(m.ts, e4m3_to_f32(sc[g]));
-            const uint32_t ww[2] = {w.x, w.y};
-            const float4* xv = reinterpret_cast<const float4*>(xs + g * 16);
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const float4 xa4 = xv[2 * j], xb4 = xv[2 * j + 1];
-                const float xe[8] = {xa4.x, xa4.y, xa4.z, xa4.w, xb4.x, xb4.y, xb4.z, xb4.w};
-#pragma unroll
-                for (int e = 0; e < 8; ++e)
-                    acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(step, __shfl_sync(0xffffffffu, lut, (int)(ww[j] >> (4 * e)))), xe[e]));
-            }
+        };
+        const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+        // (an NVFP4 code stream is only promised 8-byte alignment: two 8-byte loads then)
+        const bool al16 = (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+        auto ld = [&](int b) -> uint4 {
+            if (al16) return p[b];
+            const uint2* q = reinterpret_cast<const uint2*>(p) + 2 * b;
+            const uint2 lo = q[0], hi = q[1];
+            return make_uint4(lo.x, lo.y, hi.x, hi.y);
+        };
+        uint4 n0 = ld(0), n1 = nb > 1 ? ld(1) : zero;
+        for (int b = 0; b < nb; b += 2) {
+            const uint4 w0 = n0, w1 = n1;
+            if (b + 2 < nb) n0 = ld(b + 2);
+            if (b + 3 < nb) n1 = ld(b + 3);
+            block(w0, b);
+            if (b + 1 < nb) block(w1, b + 1);
         }
     }
     if (row_raw < m.rows) {
@@ -361,13 +372,16 @@ __device__ __forceinline__ void block_products(const uint8_t* mine, const uint8_
             s0 = __fmul_rn(ts, e4m3_to_f32(sc[2 * b]));
             s1 = __fmul_rn(ts, e4m3_to_f32(sc[2 * b + 1]));
         }
+        // all 32 table reads first, back to back: a shuffle answers after some 25 cycles, and nothing below depends
+        // on more than its own two
+        float v[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) v[e] = __shfl_sync(0xffffffffu, lut, (int)(ww[e >> 3] >> (4 * (e & 7))));
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-            const float v0 = __shfl_sync(0xffffffffu, lut, (int)(ww[e >> 3] >> (4 * (e & 7))));
-            const float v1 = __shfl_sync(0xffffffffu, lut, (int)(ww[e >> 3] >> (4 * (e & 7) + 4)));
             const float s = e < 16 ? s0 : s1;
             float w0, w1, n0, n1;
-            fmul2_rn(v0, v1, s, s, w0, w1);  // (multiplication commutes: the reference's scale * value or value * scale)
+            fmul2_rn(v[e], v[e + 1], s, s, w0, w1);  // (multiplication commutes: the reference's scale * value or value * scale)
             fmul2_rn(w0, w1, xe[e], xe[e + 1], n0, n1);
             if (CHAIN) {
                 acc = __fadd_rn(acc, prev[e]);
@@ -430,6 +444,86 @@ __global__ void __launch_bounds__(128) scan_exact_staged_kernel(FmtMat m, const 
     if (SG::NBUF == 3) asm volatile("cp.async.wait_group 2;" ::: "memory");
     else asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncwarp();
+    if (FMT != LQ_FMT_Q8_0) {
+        // FP4 formats: a three-stage software pipeline over the row's 32-element blocks, two blocks per trip so that
+        // the stages' registers swap roles without copies.  In one step
+        //   S(B + 2): the codes and scales of block B + 2 leave shared memory and its 32 table shuffles are issued,
+        //   P(B + 1): the two rounded multiplies of block B + 1 (its shuffles were issued a step ago),
+        //   A(B):     the running sum takes block B's products, in the reference's order.
+        // Nothing in a step waits for a shuffle or a load issued in the same step, and the chain of dependent
+        // adds always has a step's worth of independent work beside it.
+        const int n_blocks = n_chunks * 8;
+        float va[32], vb[32], pa[32], pb[32];
+        float sa0 = 0.f, sa1 = 0.f, sb0 = 0.f, sb1 = 0.f;
+        // S: block B (all lanes together: the table read is a shuffle)
+        auto S = [&](int B, float (&v)[32], float& s0, float& s1) {
+            const int c = B >> 3, b = B & 7;
+            if (b == 0) {  // the first block of a chunk: the chunk has landed (the later ones may be in flight)
+                asm volatile("cp.async.wait_group 2;" ::: "memory");
+                __syncwarp();
+            }
+            const uint8_t* wbuf = wbase + (c % SG::NBUF) * SG::WARP_BYTES;
+            const uint4 w = *reinterpret_cast<const uint4*>(wbuf + lane * SG::ROWB + b * 16);
+            const uint8_t* sc = wbuf + 32 * SG::ROWB + lane * 32;
+            if (FMT == LQ_FMT_MXFP4) {
+                s0 = s1 = e8m0_to_f32(sc[b]);
+            } else {
+                s0 = __fmul_rn(m.ts, e4m3_to_f32(sc[2 * b]));
+                s1 = __fmul_rn(m.ts, e4m3_to_f32(sc[2 * b + 1]));
+            }
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = __shfl_sync(0xffffffffu, lut, (int)(ww[e >> 3] >> (4 * (e & 7))));
+            if (b == 7) {  // the chunk's buffer is free: chunk c + NBUF goes into it
+                __syncwarp();
+                stage(c + SG::NBUF);
+            }
+        };
+        // P: products of block B from its table values; A: the sum takes `prev` in between
+        auto PA = [&](int B, const float (&v)[32], float s0, float s1, float (&pout)[32], const float (&prev)[32],
+                      bool do_p, bool do_a) {
+            const float* xc = xs + B * 32;
+#pragma unroll
+            for (int e = 0; e < 32; e += 4) {
+                float n0 = 0.f, n1 = 0.f, n2 = 0.f, n3 = 0.f;
+                if (do_p) {
+                    const float4 x4 = *reinterpret_cast<const float4*>(xc + e);
+                    const float s = e < 16 ? s0 : s1;
+                    float w0, w1, w2, w3;
+                    fmul2_rn(v[e], v[e + 1], s, s, w0, w1);
+                    fmul2_rn(v[e + 2], v[e + 3], s, s, w2, w3);
+                    fmul2_rn(w0, w1, x4.x, x4.y, n0, n1);
+                    fmul2_rn(w2, w3, x4.z, x4.w, n2, n3);
+                }
+                if (do_a) {
+                    acc = __fadd_rn(acc, prev[e]);
+                    acc = __fadd_rn(acc, prev[e + 1]);
+                    acc = __fadd_rn(acc, prev[e + 2]);
+                    acc = __fadd_rn(acc, prev[e + 3]);
+                }
+                pout[e] = n0; pout[e + 1] = n1; pout[e + 2] = n2; pout[e + 3] = n3;
+            }
+        };
+        // prologue: S(0) -> va, S(1) -> vb, P(0) -> pa
+        S(0, va, sa0, sa1);
+        S(1, vb, sb0, sb1);
+        PA(0, va, sa0, sa1, pa, pb, true, false);
+#pragma unroll 1
+        for (int B = 0; B < n_blocks; B += 2) {
+            // step B (even): S(B + 2) -> va, P(B + 1) from vb -> pb, A(B) from pa
+            if (B + 2 < n_blocks) S(B + 2, va, sa0, sa1);
+            PA(B + 1, vb, sb0, sb1, pb, pa, true, true);
+            // step B + 1 (odd): S(B + 3) -> vb, P(B + 2) from va -> pa, A(B + 1) from pb
+            if (B + 3 < n_blocks) S(B + 3, vb, sb0, sb1);
+            PA(B + 2, va, sa0, sa1, pa, pb, B + 2 < n_blocks, true);
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (row < m.rows) {
+            scores[row] = acc;
+            if (acc != acc) set_err(err, DEV_ERR_NAN_SCORE);
+        }
+        return;
+    }
     float p[32], pn[32];
     block_products<FMT>(wbase + lane * SG::ROWB, wbase + 32 * SG::ROWB + lane * 32, m.ts, 0, xs, lut, p);
     for (int c = 0; c < n_chunks; ++c) {
