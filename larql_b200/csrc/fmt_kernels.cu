@@ -206,8 +206,19 @@ __global__ void rescore_fmt_kernel(FmtMat m, const float* __restrict__ xn, const
 template <int FMT>
 __device__ __forceinline__ void scan_exact_fmt_body(const FmtMat& m, const float* __restrict__ xn,
                                                     float* __restrict__ scores, int* err) {
-    extern __shared__ __align__(16) float xs[];  // [cols]
+    extern __shared__ __align__(16) float xs[];  // [cols], then the scale bytes of this CTA's rows (FP4 formats)
     for (int i = threadIdx.x; i < m.cols; i += blockDim.x) xs[i] = xn[i];
+    // A row's scale bytes sit hidden / 32 (or / 16) bytes apart from the next row's: read per thread, every load
+    // would touch 32 sectors for 32 bytes.  The rows of a CTA are consecutive, so their scales are one contiguous
+    // run: copied once, coalesced.
+    uint8_t* sc_s = reinterpret_cast<uint8_t*>(xs + m.cols);
+    const int nsc = FMT == LQ_FMT_MXFP4 ? m.cols / 32 : (FMT == LQ_FMT_NVFP4 ? m.cols / 16 : 0);
+    if (FMT != LQ_FMT_Q8_0) {
+        const int r0 = blockIdx.x * blockDim.x;
+        const int n_sc = max(0, min((int)blockDim.x, m.rows - r0)) * nsc;
+        const uint8_t* src = m.scales + (size_t)r0 * nsc;
+        for (int i = threadIdx.x; i < n_sc; i += blockDim.x) sc_s[i] = src[i];
+    }
     __syncthreads();
     const int row_raw = blockIdx.x * blockDim.x + threadIdx.x;
     if (row_raw - (int)(threadIdx.x & 31) >= m.rows) return;  // (a whole warp past the end)
@@ -240,7 +251,7 @@ __device__ __forceinline__ void scan_exact_fmt_body(const FmtMat& m, const float
         // of the pair being summed.
         const int nb = m.cols / 32;
         const uint4* p = reinterpret_cast<const uint4*>(m.data + (size_t)row * nb * 16);
-        const uint8_t* sc = m.scales + (size_t)row * (FMT == LQ_FMT_MXFP4 ? nb : 2 * nb);
+        const uint8_t* sc = sc_s + (size_t)(row - blockIdx.x * blockDim.x) * nsc;
         auto block = [&](const uint4& w, int b) {
             float s0, s1;
             if (FMT == LQ_FMT_MXFP4) {
@@ -833,10 +844,10 @@ cudaError_t launch_scan_exact_fmt(const FmtMat& m, const float* xn, float* score
         return cudaGetLastError();
     }
     const int grid = (m.rows + 63) / 64;
-    const size_t smem = (size_t)m.cols * sizeof(float);
+    const size_t smem = (size_t)m.cols * sizeof(float) + 64 * (size_t)(m.cols / 16);
 #define CALL(F)                                                                                                     \
     {                                                                                                               \
-        cudaError_t e = set_max_dyn_smem((const void*)scan_exact_fmt_kernel<F>, 64 * 1024);                         \
+        cudaError_t e = set_max_dyn_smem((const void*)scan_exact_fmt_kernel<F>, 140 * 1024);                         \
         if (e != cudaSuccess) return e;                                                                             \
         scan_exact_fmt_kernel<F><<<grid, 64, smem, st>>>(m, xn, scores, err);                                        \
     }
@@ -880,10 +891,10 @@ cudaError_t launch_scan_exact_pairs(int fmt, const FmtMat* table, const uint32_t
                                     int cols, TokenWs ws0, size_t ws_stride, int* err, cudaStream_t st) {
     if (n_pairs <= 0 || rows <= 0) return cudaSuccess;
     const dim3 grid((rows + 63) / 64, n_pairs);
-    const size_t smem = (size_t)cols * sizeof(float);
+    const size_t smem = (size_t)cols * sizeof(float) + 64 * (size_t)(cols / 16);
 #define CALL(F)                                                                                             \
     {                                                                                                       \
-        cudaError_t e = set_max_dyn_smem((const void*)scan_exact_pairs_kernel<F>, 64 * 1024);              \
+        cudaError_t e = set_max_dyn_smem((const void*)scan_exact_pairs_kernel<F>, 140 * 1024);              \
         if (e != cudaSuccess) return e;                                                                     \
         scan_exact_pairs_kernel<F><<<grid, 64, smem, st>>>(table, pair_expert, ws0, ws_stride, err);        \
     }

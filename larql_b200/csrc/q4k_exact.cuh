@@ -10,9 +10,12 @@ namespace lq {
 // eight lanes of a 128-bit load phase (chunks 64 floats apart) fall in different banks.
 // IN_SMEM: the row was staged in shared memory (plain loads); otherwise it is read from global memory through
 // the read-only path.
+// The super-block partials of the passes first_pass, first_pass + pass_step, ... of a row (a pass is eight
+// super-blocks, one per group of four lanes) into sb_part[]: super-blocks are independent of each other until the
+// final sum, so several warps may share a row.
 template <bool IN_SMEM = false>
-__device__ __forceinline__ float exact_row_q4k(const uint8_t* __restrict__ row, const float* __restrict__ xs, int nsb,
-                                               float* sb_part /* [nsb] per-warp scratch */, int lane) {
+__device__ __forceinline__ void exact_row_q4k_passes(const uint8_t* __restrict__ row, const float* __restrict__ xs, int nsb,
+                                                     float* sb_part /* [nsb] */, int lane, int first_pass, int pass_step) {
     const int g = lane & 3;
     auto ld16 = [](const uint8_t* p) -> uint4 {
         return IN_SMEM ? *reinterpret_cast<const uint4*>(p) : __ldg(reinterpret_cast<const uint4*>(p));
@@ -20,18 +23,19 @@ __device__ __forceinline__ float exact_row_q4k(const uint8_t* __restrict__ row, 
     // The loads of the next eight super-blocks are issued before the current eight are summed, so the
     // passes of a row overlap their memory latency (the arithmetic and its order are unchanged).
     uint4 n_hdr = make_uint4(0u, 0u, 0u, 0u), n_q0 = n_hdr, n_q1 = n_hdr;
-    if ((lane >> 2) < nsb) {
-        const uint8_t* cell = row + (size_t)(lane >> 2) * 144;
+    const int sb_step = 8 * pass_step;
+    if (8 * first_pass + (lane >> 2) < nsb) {
+        const uint8_t* cell = row + (size_t)(8 * first_pass + (lane >> 2)) * 144;
         n_hdr = ld16(cell);
         n_q0 = ld16(cell + 16 + g * 32);
         n_q1 = ld16(cell + 32 + g * 32);
     }
 #pragma unroll 1
-    for (int s0 = 0; s0 < nsb; s0 += 8) {
+    for (int s0 = 8 * first_pass; s0 < nsb; s0 += sb_step) {
         const int s = s0 + (lane >> 2);
         const uint4 hdr = n_hdr, q0 = n_q0, q1 = n_q1;
-        if (s + 8 < nsb) {
-            const uint8_t* cell = row + (size_t)(s + 8) * 144;
+        if (s + sb_step < nsb) {
+            const uint8_t* cell = row + (size_t)(s + sb_step) * 144;
             n_hdr = ld16(cell);
             n_q0 = ld16(cell + 16 + g * 32);
             n_q1 = ld16(cell + 32 + g * 32);
@@ -76,6 +80,13 @@ __device__ __forceinline__ float exact_row_q4k(const uint8_t* __restrict__ row, 
         }
         if (g == 0 && s < nsb) sb_part[s] = acc;
     }
+}
+
+// The whole row by one warp: all passes, then the partials summed in super-block order (valid on lane 0).
+template <bool IN_SMEM = false>
+__device__ __forceinline__ float exact_row_q4k(const uint8_t* __restrict__ row, const float* __restrict__ xs, int nsb,
+                                               float* sb_part /* [nsb] per-warp scratch */, int lane) {
+    exact_row_q4k_passes<IN_SMEM>(row, xs, nsb, sb_part, lane, 0, 1);
     __syncwarp();
     float total = 0.0f;
     if (lane == 0)

@@ -1112,10 +1112,26 @@ __device__ __noinline__ void phase_select(int l) {
             }
             if (!mbar_wait(sm.ebar(4), band_uses & 1u)) s_ctl[SC_FAILED] = 1;
             band_uses += 1;
+            // A CTA has a few band rows and sixteen warps: up to four warps share a row (each takes every wpr-th pass
+            // of eight super-blocks; the partials of a row are summed in super-block order afterwards).
+            const int passes = (gm.nsb + 7) / 8;
+            const int wpr = (4 * nb <= FW_NWARPS && passes >= 4) ? 4 : ((2 * nb <= FW_NWARPS && passes >= 2) ? 2 : 1);
+            const int groups = FW_NWARPS / wpr;  // rows in flight
 #pragma unroll 1
-            for (int i = warp; i < nb; i += FW_NWARPS) {
-                const float v = exact_row_q4k<true>(stage + (size_t)i * gm.row_bytes, xs, gm.nsb, red + 256 + warp * gm.nsb, lane);
-                if (lane == 0) band_ex[r0 + i] = v;
+            for (int i0 = 0; i0 < nb; i0 += groups) {
+                const int i = i0 + warp / wpr;
+                if (i < nb)
+                    exact_row_q4k_passes<true>(stage + (size_t)i * gm.row_bytes, xs, gm.nsb, red + 256 + (warp / wpr) * gm.nsb,
+                                               lane, warp % wpr, wpr);
+                bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+                if (i < nb && warp % wpr == 0 && lane == 0) {
+                    const float* part = red + 256 + (warp / wpr) * gm.nsb;
+                    float total = 0.0f;
+#pragma unroll 1
+                    for (int sb = 0; sb < gm.nsb; ++sb) total = __fadd_rn(total, part[sb]);
+                    band_ex[r0 + i] = total;
+                }
+                bar_sync(FW_BAR_CONS, FW_CONSUMERS);  // the partial arrays are free for the next rows
             }
         }
     }
