@@ -36,9 +36,13 @@ __device__ __forceinline__ float fp4_lut_lane(int lane) { return e2m1_to_f32((ui
 // Q8_0 an upper estimate plus the fixed-point error term).  c1 covers the roundings of the reference's
 // one running sum over the row and of this evaluation; sum |w x| here is itself rounded, which the 1 %
 // margin in c1 absorbs.
+// xs_pad (optional, FP4 formats): the activation in shared memory, every 32-element block at a stride of 36
+// floats.  A lane reads the 32 (or 16) activations of ITS block: from global memory that is 32 lines per warp load,
+// from an unpadded copy a 32-way bank conflict; at a stride of 36 the eight lanes of a 128-bit load phase fall into
+// different banks.
 template <int FMT>
 __device__ __forceinline__ float fast_row(const FmtMat& m, size_t row, const XPrep& xp, float c1, float& bound, int lane,
-                                          float lut) {
+                                          float lut, const float* xs_pad = nullptr) {
     float acc = 0.0f, bnd = 0.0f;
     if (FMT == LQ_FMT_Q8_0) {
         const int nb = m.cols / 32;
@@ -73,8 +77,9 @@ __device__ __forceinline__ float fast_row(const FmtMat& m, size_t row, const XPr
             for (int j = 0; j < 4; ++j) {
                 float4 x0 = make_float4(0, 0, 0, 0), x1 = x0;
                 if (on) {
-                    x0 = *reinterpret_cast<const float4*>(xp.xn + blk * 32 + 8 * j);
-                    x1 = *reinterpret_cast<const float4*>(xp.xn + blk * 32 + 8 * j + 4);
+                    const float* xsrc = xs_pad ? xs_pad + blk * 36 + 8 * j : xp.xn + blk * 32 + 8 * j;
+                    x0 = *reinterpret_cast<const float4*>(xsrc);
+                    x1 = *reinterpret_cast<const float4*>(xsrc + 4);
                 }
                 const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
 #pragma unroll
@@ -106,8 +111,9 @@ __device__ __forceinline__ float fast_row(const FmtMat& m, size_t row, const XPr
             for (int j = 0; j < 2; ++j) {
                 float4 x0 = make_float4(0, 0, 0, 0), x1 = x0;
                 if (on) {
-                    x0 = *reinterpret_cast<const float4*>(xp.xn + g * 16 + 8 * j);
-                    x1 = *reinterpret_cast<const float4*>(xp.xn + g * 16 + 8 * j + 4);
+                    const float* xsrc = xs_pad ? xs_pad + (g >> 1) * 36 + (g & 1) * 16 + 8 * j : xp.xn + g * 16 + 8 * j;
+                    x0 = *reinterpret_cast<const float4*>(xsrc);
+                    x1 = *reinterpret_cast<const float4*>(xsrc + 4);
                 }
                 const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
 #pragma unroll
@@ -668,9 +674,17 @@ __device__ __forceinline__ void gather_fmt_body(const FmtMat& up, const FmtMat& 
                                                 float* __restrict__ partials) {
     __shared__ float act_s[64];
     __shared__ uint32_t row_s[64];
+    extern __shared__ __align__(16) float xs_pad[];  // FP4 formats: [H / 32][36], see fast_row
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int H = up.cols, nblk = H / 32;
     const float lut = fp4_lut_lane(lane);
+    if (FMT != LQ_FMT_Q8_0) {
+        for (int i = tid; i < H / 4; i += NT) {
+            const float4 v = *reinterpret_cast<const float4*>(xp.xn + 4 * i);
+            *reinterpret_cast<float4*>(xs_pad + ((4 * i) >> 5) * 36 + ((4 * i) & 31)) = v;
+        }
+        __syncthreads();
+    }
     constexpr bool FP4 = FMT != LQ_FMT_Q8_0;
     float acc[FP4 ? 1 : BPT][32];            // Q8_0
     unsigned long long acc2[FP4 ? BPT : 1][16];  // FP4 formats: packed pairs
@@ -690,7 +704,7 @@ __device__ __forceinline__ void gather_fmt_body(const FmtMat& up, const FmtMat& 
         for (int i = warp; i < nh; i += NT / 32) {
             const uint32_t row = hit_idx[c0 + i];
             float b;
-            const float u = fast_row<FMT>(up, row, xp, 0.0f, b, lane, lut);
+            const float u = fast_row<FMT>(up, row, xp, 0.0f, b, lane, lut, FMT != LQ_FMT_Q8_0 ? xs_pad : nullptr);
             if (lane == 0) {
                 const float gs = hit_score[c0 + i];
                 const float sig = __fdiv_rn(1.0f, 1.0f + expf(-gs));
@@ -872,14 +886,21 @@ cudaError_t launch_gather_fmt(const FmtMat& up, const FmtMat& down, const XPrep&
                               int grid, cudaStream_t st) {
     if (up.fmt != down.fmt || up.cols != down.cols || up.cols % 32 != 0 || up.cols > 16384) return cudaErrorInvalidValue;
     const int bpt = (up.cols / 32 + FK_THREADS - 1) / FK_THREADS;  // 32-column blocks per thread: 1 or 2
+    const size_t xsm = up.fmt == LQ_FMT_Q8_0 ? 0 : (size_t)(up.cols / 32) * 36 * sizeof(float);  // padded activation
 #define CALL(F)                                                                                                \
     {                                                                                                          \
         if (bpt <= 1)                                                                                          \
-            gather_fmt_kernel<F, 1><<<grid, FK_THREADS, 0, st>>>(up, down, xp, hit_idx, hit_score, n_hits_dev,  \
-                                                                n_hits_host, partials);                        \
-        else                                                                                                   \
-            gather_fmt_kernel<F, 2><<<grid, FK_THREADS, 0, st>>>(up, down, xp, hit_idx, hit_score, n_hits_dev,  \
-                                                                n_hits_host, partials);                        \
+        {                                                                                                      \
+            cudaError_t e = set_max_dyn_smem((const void*)gather_fmt_kernel<F, 1>, 80 * 1024);                  \
+            if (e != cudaSuccess) return e;                                                                     \
+            gather_fmt_kernel<F, 1><<<grid, FK_THREADS, xsm, st>>>(up, down, xp, hit_idx, hit_score, n_hits_dev, \
+                                                                  n_hits_host, partials);                      \
+        } else {                                                                                               \
+            cudaError_t e = set_max_dyn_smem((const void*)gather_fmt_kernel<F, 2>, 80 * 1024);                  \
+            if (e != cudaSuccess) return e;                                                                     \
+            gather_fmt_kernel<F, 2><<<grid, FK_THREADS, xsm, st>>>(up, down, xp, hit_idx, hit_score, n_hits_dev, \
+                                                                  n_hits_host, partials);                      \
+        }                                                                                                      \
     }
     FMT_DISPATCH(up.fmt, CALL)
 #undef CALL
@@ -910,20 +931,23 @@ cudaError_t launch_gather_fmt_pairs(int fmt, const FmtMat* up_table, const FmtMa
     if (cols % 32 != 0 || cols > 16384) return cudaErrorInvalidValue;
     const int nblk = cols / 32;
     const dim3 grid(grid_x, n_pairs);
+    const size_t xsm = fmt == LQ_FMT_Q8_0 ? 0 : (size_t)nblk * 36 * sizeof(float);  // padded activation
+#define LAUNCH(F, BPT, NT)                                                                                             \
+    {                                                                                                                  \
+        cudaError_t e = set_max_dyn_smem((const void*)gather_fmt_pairs_kernel<F, BPT, NT>, 80 * 1024);                  \
+        if (e != cudaSuccess) return e;                                                                                \
+        gather_fmt_pairs_kernel<F, BPT, NT><<<grid, NT, xsm, st>>>(up_table, down_table, pair_expert, ws0, ws_stride,   \
+                                                                  partials);                                          \
+    }
 #define CALL(F)                                                                                                        \
     {                                                                                                                  \
-        if (nblk <= 128)                                                                                               \
-            gather_fmt_pairs_kernel<F, 1, 128><<<grid, 128, 0, st>>>(up_table, down_table, pair_expert, ws0, ws_stride, \
-                                                                    partials);                                        \
-        else if (nblk <= FK_THREADS)                                                                                   \
-            gather_fmt_pairs_kernel<F, 1, FK_THREADS><<<grid, FK_THREADS, 0, st>>>(up_table, down_table, pair_expert,   \
-                                                                                  ws0, ws_stride, partials);          \
-        else                                                                                                           \
-            gather_fmt_pairs_kernel<F, 2, FK_THREADS><<<grid, FK_THREADS, 0, st>>>(up_table, down_table, pair_expert,   \
-                                                                                  ws0, ws_stride, partials);          \
+        if (nblk <= 128) LAUNCH(F, 1, 128)                                                                             \
+        else if (nblk <= FK_THREADS) LAUNCH(F, 1, FK_THREADS)                                                          \
+        else LAUNCH(F, 2, FK_THREADS)                                                                                  \
     }
     FMT_DISPATCH(fmt, CALL)
 #undef CALL
+#undef LAUNCH
     return cudaGetLastError();
 }
 
