@@ -488,11 +488,21 @@ int enqueue_walk_token_fmt(lq_ctx* ctx, const lq_matrix& gate, const lq_matrix& 
         return LQ_OK;
     }
     CK(launch_scan_exact_fmt(g, w.xn, w.scores, ctx->d_err, st));
-    CK(launch_select(w.scores, N, k, w, ctx->d_err, st));
-    ctx->launches += 2;
-    if (sparse) {
-        CK(launch_final_pick(w, ctx->d_err, st));  // ties at the K-th |score|: the lower rows win
-        ctx->launches += 1;
+    static const bool mc_on = [] { const char* e = getenv("LARQL_B200_SELECT_MC"); return !(e && e[0] == '0'); }();
+    if (sparse && mc_on && N >= 8192 && k > 0) {
+        // many rows: histogram of the exact scores, the threshold bucket's rows as the band (their scores are
+        // exact already), the rest by several CTAs in row order; the final pick settles the bucket
+        CK(launch_hist_abs(w.scores, N, w.hist, st));
+        CK(launch_classify_mc(w.scores, N, k, w, st, 1, 0, 1));
+        CK(launch_final_pick(w, ctx->d_err, st));
+        ctx->launches += 5;
+    } else {
+        CK(launch_select(w.scores, N, k, w, ctx->d_err, st));
+        ctx->launches += 2;
+        if (sparse) {
+            CK(launch_final_pick(w, ctx->d_err, st));  // ties at the K-th |score|: the lower rows win
+            ctx->launches += 1;
+        }
     }
     CK(launch_gather_fmt(u, d, xp, w.hit_idx, w.hit_score, &w.sel->n_sel, k, ctx->partials, fmt_gather_grid(ctx), st));
     CK(launch_finish(ctx->partials, fmt_gather_grid(ctx), H, residual, out, st));

@@ -146,6 +146,10 @@ cudaError_t launch_select(const float* scores, int n, int top_k, TokenWs ws, int
 // Band classification from the scan's coarse histogram (walk path).
 cudaError_t launch_classify(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st,
                             int batch = 1, size_t ws_stride = 0);
+// The same classification by several CTAs per token (launch_classify takes this route for many rows);
+// band_scores: band_exact takes the band rows' scores (they are exact already).
+cudaError_t launch_classify_mc(const float* scores, int n, int top_k, TokenWs ws, cudaStream_t st, int batch,
+                               size_t ws_stride, int band_scores);
 // Stand-alone exact top-K by |score| (ties -> lower index), sorted (|v| desc, idx asc).
 cudaError_t launch_topk_abs_sorted(const float* scores, int n, int top_k, uint32_t* idx_out, float* val_out,
                                    int* count_out, void* scratch, int* err, cudaStream_t st);

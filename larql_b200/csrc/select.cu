@@ -2,6 +2,8 @@
 // final pick kernel, and the stand-alone sorted top-K by |score|.
 #include "select.cuh"
 
+#include <cstdlib>
+
 namespace lq {
 
 namespace {
@@ -168,6 +170,169 @@ classify_kernel(const float* __restrict__ scores_g, int n, int top_k, TokenWs ws
     (void)err;
 }
 
+// ---- the same classification by several CTAs per token ------------------------------------------
+// One CTA needs some 30 us to compact 28672 scores in order.  Here MC_MAX_CTAS CTAs share a token: every CTA finds
+// the threshold bucket from the histogram (the same answer everywhere), counts the certainly-in and the band rows
+// of ITS contiguous chunk of rows (first launch), and, once all counts are known, writes them at the offsets the
+// counts of the chunks before it give (second launch): the lists come out in ascending row order, exactly as one
+// CTA writes them.  Counts and thresholds travel in the spare words of the token's selection page.
+constexpr int MC_T = 256;
+constexpr int MC_MAX_CTAS = 24;  // 2 counts per CTA behind the header and four threshold words: 32 + 16 + 192 <= 256 bytes
+enum { MC_W_BSTAR = 8, MC_W_LO = 9, MC_W_HI = 10, MC_W_B = 11, MC_W_COUNTS = 12 };
+
+struct McSmem {
+    uint32_t wsum[MC_T / 32];
+    int bstar;
+    int wcnt_a[MC_T / 32], wcnt_b[MC_T / 32];
+    int tot[2];
+};
+
+// The bucket of the K-th largest key (every thread gets it).
+__device__ __forceinline__ uint32_t mc_find_bucket(const uint32_t* __restrict__ hist, int top_k, McSmem& sm) {
+    constexpr int PER = LQ_HIST_BINS / MC_T;  // bins per thread, contiguous; higher thread = larger keys
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) sm.bstar = 0;  // top_k above the number of counted scores: bin 0 makes every row a candidate
+    uint32_t own = 0;
+    const uint4* h4 = reinterpret_cast<const uint4*>(hist + tid * PER);
+#pragma unroll 4
+    for (int b = 0; b < PER / 4; ++b) {
+        const uint4 v = __ldcg(h4 + b);
+        own += v.x + v.y + v.z + v.w;
+    }
+    uint32_t suf = own;
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t v = __shfl_down_sync(0xffffffffu, suf, o);
+        if (lane + o < 32) suf += v;
+    }
+    if (lane == 0) sm.wsum[warp] = suf;
+    __syncthreads();
+    uint32_t higher = 0;
+    for (int w = warp + 1; w < MC_T / 32; ++w) higher += sm.wsum[w];
+    suf += higher;
+    const uint32_t above = suf - own;
+    if (above < (uint32_t)top_k && (uint32_t)top_k <= suf) {
+        uint32_t acc = above;
+        int b = PER - 1;
+        for (; b > 0; --b) {
+            const uint32_t v = __ldcg(hist + tid * PER + b);
+            if (acc + v >= (uint32_t)top_k) break;
+            acc += v;
+        }
+        sm.bstar = tid * PER + b;
+    }
+    __syncthreads();
+    return (uint32_t)sm.bstar;
+}
+
+__global__ void __launch_bounds__(MC_T) classify_mc_count_kernel(const float* __restrict__ scores_g, int n, int top_k,
+                                                                TokenWs ws, size_t ws_stride) {
+    ws = ws_at(ws, ws_stride * blockIdx.y);
+    const float* scores = tok_off(scores_g, ws_stride * blockIdx.y);
+    __shared__ McSmem sm;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t bstar = mc_find_bucket(ws.hist, top_k, sm);
+    const float B = __uint_as_float(ws.sel->bound_bits);
+    const float t_lo = __uint_as_float(bstar << LQ_HIST_SHIFT);
+    const uint32_t hi_bits = (bstar + 1u) << LQ_HIST_SHIFT;
+    const float t_hi = __uint_as_float(hi_bits > 0x7F800000u ? 0x7F800000u : hi_bits);
+    const float two_b = __fmul_ru(2.0f, B);
+    const float hi = __fadd_ru(t_hi, two_b), lo = __fadd_rd(t_lo, -two_b);
+    int* words = reinterpret_cast<int*>(ws.sel);
+    const int per = ((n + (int)gridDim.x - 1) / (int)gridDim.x + 31) / 32 * 32;
+    const int beg = blockIdx.x * per, end = min(n, beg + per);
+    int ca = 0, cb = 0;
+    for (int i0 = beg + warp * 32; i0 < end; i0 += MC_T) {
+        const int i = i0 + lane;
+        const float a = i < end ? fabsf(scores[i]) : -1.0f;
+        ca += __popc(__ballot_sync(0xffffffffu, a > hi));
+        cb += __popc(__ballot_sync(0xffffffffu, !(a > hi) && a >= lo));
+    }
+    if (lane == 0) {
+        sm.wcnt_a[warp] = ca;
+        sm.wcnt_b[warp] = cb;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int ta = 0, tb = 0;
+        for (int w = 0; w < MC_T / 32; ++w) {
+            ta += sm.wcnt_a[w];
+            tb += sm.wcnt_b[w];
+        }
+        words[MC_W_COUNTS + 2 * blockIdx.x] = ta;
+        words[MC_W_COUNTS + 2 * blockIdx.x + 1] = tb;
+        if (blockIdx.x == 0) {
+            words[MC_W_BSTAR] = (int)bstar;
+            words[MC_W_LO] = __float_as_int(lo);
+            words[MC_W_HI] = __float_as_int(hi);
+            words[MC_W_B] = __float_as_int(B);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(MC_T) classify_mc_write_kernel(const float* __restrict__ scores_g, int n, int top_k,
+                                                                TokenWs ws, size_t ws_stride, int band_scores) {
+    ws = ws_at(ws, ws_stride * blockIdx.y);
+    const float* scores = tok_off(scores_g, ws_stride * blockIdx.y);
+    __shared__ McSmem sm;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int* words = reinterpret_cast<const int*>(ws.sel);
+    const float lo = __int_as_float(words[MC_W_LO]), hi = __int_as_float(words[MC_W_HI]);
+    int oa = 0, ob = 0, ta = 0, tb = 0;
+    for (int c = 0; c < (int)gridDim.x; ++c) {
+        const int a = words[MC_W_COUNTS + 2 * c], b = words[MC_W_COUNTS + 2 * c + 1];
+        if (c < (int)blockIdx.x) {
+            oa += a;
+            ob += b;
+        }
+        ta += a;
+        tb += b;
+    }
+    const int per = ((n + (int)gridDim.x - 1) / (int)gridDim.x + 31) / 32 * 32;
+    const int beg = blockIdx.x * per, end = min(n, beg + per);
+    // rounds of MC_T rows: warp w of a round holds rows [i0 + 32 w, i0 + 32 w + 32); offsets inside a round from the
+    // warps' ballot counts
+    for (int i0 = beg; i0 < end; i0 += MC_T) {
+        const int i = i0 + warp * 32 + lane;
+        const float v = i < end ? scores[i] : 0.0f;
+        const float a = i < end ? fabsf(v) : -1.0f;
+        const int cls = a > hi ? 1 : (a >= lo ? 2 : 0);
+        const uint32_t ba = __ballot_sync(0xffffffffu, cls == 1), bb = __ballot_sync(0xffffffffu, cls == 2);
+        if (lane == 0) {
+            sm.wcnt_a[warp] = __popc(ba);
+            sm.wcnt_b[warp] = __popc(bb);
+        }
+        __syncthreads();
+        int wa = 0, wb = 0, ra = 0, rb = 0;
+        for (int w = 0; w < MC_T / 32; ++w) {
+            if (w < warp) {
+                wa += sm.wcnt_a[w];
+                wb += sm.wcnt_b[w];
+            }
+            ra += sm.wcnt_a[w];
+            rb += sm.wcnt_b[w];
+        }
+        const uint32_t lt = (1u << lane) - 1u;
+        if (cls == 1) {
+            const int pos = oa + wa + __popc(ba & lt);
+            ws.hit_idx[pos] = (uint32_t)i;
+            ws.hit_score[pos] = v;
+        } else if (cls == 2) {
+            const int pos = ob + wb + __popc(bb & lt);
+            ws.band_idx[pos] = (uint32_t)i;
+            if (band_scores) ws.band_exact[pos] = v;
+        }
+        oa += ra;
+        ob += rb;
+        __syncthreads();
+    }
+    // the histogram is cleared for the next scan (every CTA a slice); the header last
+    for (int i = blockIdx.x * MC_T + tid; i < LQ_HIST_BINS / 4; i += gridDim.x * MC_T)
+        reinterpret_cast<uint4*>(ws.hist)[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (blockIdx.x == 0 && tid == 0)
+        *ws.sel = SelHeader{ta, tb, top_k, top_k - ta, __uint_as_float((uint32_t)words[MC_W_BSTAR] << LQ_HIST_SHIFT),
+                            __int_as_float(words[MC_W_B]), 0, 0u};
+}
+
 __global__ void __launch_bounds__(256) final_pick_kernel(TokenWs ws, int* err, size_t ws_stride) {
     __shared__ SelectSmem<256> sm;
     final_pick_block<256>(ws_at(ws, ws_stride * blockIdx.y), err, sm);
@@ -315,8 +480,24 @@ cudaError_t launch_select(const float* scores, int n, int top_k, TokenWs ws, int
     return cudaGetLastError();
 }
 
+// band_scores: the band rows' entries of band_exact are filled with their (already exact) scores.
+cudaError_t launch_classify_mc(const float* scores, int n, int top_k, TokenWs ws, cudaStream_t st, int batch,
+                               size_t ws_stride, int band_scores) {
+    int g = (n + 1023) / 1024;
+    if (g > MC_MAX_CTAS) g = MC_MAX_CTAS;
+    if (g < 1) g = 1;
+    classify_mc_count_kernel<<<dim3(g, batch), MC_T, 0, st>>>(scores, n, top_k, ws, ws_stride);
+    classify_mc_write_kernel<<<dim3(g, batch), MC_T, 0, st>>>(scores, n, top_k, ws, ws_stride, band_scores);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_classify(const float* scores, int n, int top_k, TokenWs ws, int* err, cudaStream_t st, int batch,
                             size_t ws_stride) {
+    // many rows: several CTAs per token (the lists come out the same)
+    static const bool mc_on = [] { const char* e = getenv("LARQL_B200_SELECT_MC"); return !(e && e[0] == '0'); }();
+    // (many tokens fill the GPU with one CTA each: measured slower with several at batch 64)
+    if (mc_on && n >= 8192 && top_k > 0 && top_k < n && batch <= 16)
+        return launch_classify_mc(scores, n, top_k, ws, st, batch, ws_stride, 0);
     cudaError_t e = set_max_dyn_smem((const void*)classify_kernel, SEL_SMEM_VALS_MAX * 4);
     if (e != cudaSuccess) return e;
     const int use_smem = n <= SEL_SMEM_VALS_MAX;
