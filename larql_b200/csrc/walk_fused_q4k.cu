@@ -1576,11 +1576,25 @@ __device__ __forceinline__ void merge_partials(bool first) {
     const float* out_r = reinterpret_cast<const float*>(sm.ring());
     const int region = gm.G * 65;
     float* dst = sm.cx().a.partials + (size_t)blockIdx.x * hidden;
-    for (int i = tid; i < hidden; i += FW_CONSUMERS) {
-        const int o = (i >> 6) * 65 + (i & 63);
-        float v = out_r[o];
-        for (int p = 1; p < P; ++p) v += out_r[p * region + o];
-        dst[i] = first ? v : dst[i] + v;
+    // four outputs per trip, their loads issued together (the teams' values are added in team order either way)
+    for (int i0 = tid; i0 < hidden; i0 += 4 * FW_CONSUMERS) {
+        float v[4];
+        int o[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = min(i0 + u * FW_CONSUMERS, hidden - 1);
+            o[u] = (i >> 6) * 65 + (i & 63);
+            v[u] = out_r[o[u]];
+        }
+        for (int p = 1; p < P; ++p) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] += out_r[p * region + o[u]];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * FW_CONSUMERS;
+            if (i < hidden) dst[i] = first ? v[u] : dst[i] + v[u];
+        }
     }
     // the merge used the ring with plain loads and stores; order them before the next TMA writes
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1752,11 +1766,10 @@ __device__ __noinline__ void phase_gather(int l) {
             if (base + i < a.top_k) a.hit_out[base + i] = (uint32_t)g2_rows[i];  // (a sharded walk: this rank's own row numbers)
     }
     // the ring is free: the next layer's first tiles may land
-    if (tid == 0 && l + 1 < a.n_layers) {
+    if (tid < cx.n_ahead && l + 1 < a.n_layers) {  // (thread k issues tile k: every stage has its own barrier)
         const FusedLayer nx = a.layers[l + 1];
         const uint32_t it0 = (uint32_t)(l + 1) * (uint32_t)cx.my_count;
-#pragma unroll 1
-        for (int k = 0; k < cx.n_ahead; ++k) issue_tile(sm, nx, k, it0 + k);
+        issue_tile(sm, nx, tid, it0 + tid);
     }
     // housekeeping for the layer after next (nobody reads these before two more grid barriers)
     uint4* hist4 = reinterpret_cast<uint4*>(a.hist + (size_t)(l & 1) * FW_HIST_WORDS);
