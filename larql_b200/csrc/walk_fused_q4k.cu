@@ -1471,6 +1471,22 @@ __device__ __noinline__ void phase_pick(int l) {
             first += share[i];
         }
     }
+    // This CTA's share of the pool is fetched into registers as soon as the share is known (after the barrier that
+    // ends the staging below) and stored once the winners are counted: its round trip to global memory runs
+    // beside the ranking.
+    bool pool_early = false;
+    uint32_t pool_r = 0u;
+    float pool_s = 0.0f;
+    auto pool_src = [&](int j) -> size_t {
+        const int NC = (int)gridDim.x;
+        int sa = 0, sb = NC;  // prefix[sa] <= j < prefix[sb]
+        while (sb - sa > 1) {
+            const int mid = (sa + sb) >> 1;
+            if (prefix[mid] <= j) sa = mid;
+            else sb = mid;
+        }
+        return (size_t)sa * gm.max_slots + (size_t)(j - prefix[sa]);
+    };
     if (!take_all && need > 0) {
         // stage (|v| key, row) of every band entry in the idle ring
         const bool staged = n_band_tot <= FW_PICK_CAP;
@@ -1489,6 +1505,14 @@ __device__ __noinline__ void phase_pick(int l) {
                     }
                 }
             bar_sync(FW_BAR_CONS, FW_CONSUMERS);
+            if (scal[1] <= FW_CONSUMERS) {  // (the last warp's results are in place after the barrier)
+                pool_early = true;
+                if (tid < scal[1]) {
+                    const size_t src = pool_src(scal[0] + tid);
+                    pool_r = __ldcg(&a.pool_row[src]);
+                    pool_s = __ldcg(&a.pool_score[src]);
+                }
+            }
         }
         if (by_rank) {
 #pragma unroll 1
@@ -1534,21 +1558,20 @@ __device__ __noinline__ void phase_pick(int l) {
     }
     bar_sync(FW_BAR_CONS, FW_CONSUMERS);  // winners and the pool assignment are in place
     {
-        const int NC = (int)gridDim.x;
         const int n_win = s_ctl[SC_N_G2];  // own rows and winners so far
         const int my_first = scal[0], n_pool_mine = scal[1];
-#pragma unroll 1
-        for (int i = tid; i < n_pool_mine; i += FW_CONSUMERS) {
-            const int j = my_first + i;
-            int sa = 0, sb = NC;  // prefix[sa] <= j < prefix[sb]
-            while (sb - sa > 1) {
-                const int mid = (sa + sb) >> 1;
-                if (prefix[mid] <= j) sa = mid;
-                else sb = mid;
+        if (pool_early) {
+            if (tid < n_pool_mine) {
+                g2_rows[n_win + tid] = (int)pool_r;
+                g2_scores[n_win + tid] = pool_s;
             }
-            const size_t src = (size_t)sa * gm.max_slots + (size_t)(j - prefix[sa]);
-            g2_rows[n_win + i] = (int)__ldcg(&a.pool_row[src]);
-            g2_scores[n_win + i] = __ldcg(&a.pool_score[src]);
+        } else {
+#pragma unroll 1
+            for (int i = tid; i < n_pool_mine; i += FW_CONSUMERS) {
+                const size_t src = pool_src(my_first + i);
+                g2_rows[n_win + i] = (int)__ldcg(&a.pool_row[src]);
+                g2_scores[n_win + i] = __ldcg(&a.pool_score[src]);
+            }
         }
         bar_sync(FW_BAR_CONS, FW_CONSUMERS);  // (every thread has read the counts above)
         if (tid == 0) s_ctl[SC_N_G2] = n_win + n_pool_mine;
