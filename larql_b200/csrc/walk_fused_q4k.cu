@@ -218,7 +218,14 @@ __device__ __forceinline__ bool line_load(const void* p, uint32_t epoch, uint32_
 }
 // Waits (bounded: about a second, or until another CTA has recorded an error) for a line of this epoch.
 // On failure the words read as zero and DEV_ERR_TMA_TIMEOUT is recorded.
+// (The spin is out of line: it is inlined at dozens of places otherwise, and the sharded kernel's code must stay
+// inside the instruction cache like the one-GPU kernel's.)
+__device__ __noinline__ void line_spin(const void* p, uint32_t epoch, uint32_t& w0, uint32_t& w1, int* err);
 __device__ __forceinline__ void line_wait(const void* p, uint32_t epoch, uint32_t& w0, uint32_t& w1, int* err) {
+    if (line_load(p, epoch, w0, w1)) return;
+    line_spin(p, epoch, w0, w1, err);
+}
+__device__ __noinline__ void line_spin(const void* p, uint32_t epoch, uint32_t& w0, uint32_t& w1, int* err) {
     if (line_load(p, epoch, w0, w1)) return;
     const long long t0 = clock64();
     uint32_t spins = 0;
