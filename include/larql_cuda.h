@@ -360,7 +360,11 @@ LQ_API int lq_dev_shard_hits(lq_ctx* ctx, uint32_t* idx_out_host, size_t cap, si
 /* MoE expert walk (cpu_moe_forward's combine, crates/larql-compute/src/cpu/ops/moe/forward.rs:24-140,
  * over walked experts): out[t] = sum_j w[t,j] * walk(expert idx[t,j], x[t]) with lq_moe_route's
  * selection and lq_walk_ffn's per-expert top_k.  gates/ups/downs_fm: n_experts matrices each.
- * flags: LQ_WALK_FORCE_SPARSE only.  expert_idx_out / expert_w_out may be NULL. */
+ * flags: LQ_WALK_FORCE_SPARSE only.  expert_idx_out / expert_w_out may be NULL.
+ * Experts of one block format (Q8_0 / MXFP4 / NVFP4) and one shape are walked for all (token, expert) pairs at
+ * once, the experts' matrices reached through a table on the device and nothing read back between routing and
+ * the result; Q4_K / Q6_K experts and experts of different shapes pair by pair after one read-back of the routing.
+ * The results are the same either way (the experts' outputs are combined in selection order). */
 LQ_API int lq_moe_walk_ffn(lq_ctx* ctx, const lq_matrix* gates, const lq_matrix* ups, const lq_matrix* downs_fm,
                            size_t n_experts, const float* logits, const float* x, size_t batch, size_t top_e,
                            int renormalise, size_t top_k, uint32_t flags, float* out, uint32_t* expert_idx_out,
